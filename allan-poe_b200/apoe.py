@@ -1,0 +1,314 @@
+"""Python host layer over the C ABI of libapoe.so (ctypes; torch only supplies device memory and streams).
+
+`Index` is the resident index: corpus packed in device memory, graph built on the device or loaded from an
+index.poe file, queries searched in batches.  There is no CPU fallback: importing works without a GPU, every
+compute call needs the CUDA library and a device and raises `ApoeError` otherwise.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+AP_OK = 0
+CREATE_FOR_BUILD = 1
+BUILD_SIMT_JOIN, BUILD_KEEP_KNN = 1, 2
+SEARCH_KEYWORD, SEARCH_KG, SEARCH_RAW_WEIGHTS, SEARCH_UNFUSED_DENSE = 1, 2, 4, 8
+DIM, ROW, DEGREE, KNN, ENTRY_POINTS = 1024, 40, 32, 64, 32
+
+
+class ApoeError(RuntimeError):
+    def __init__(self, code: int, msg: str):
+        super().__init__(f"[{code}] {msg}")
+        self.code = code
+
+
+class _Csr(C.Structure):
+    _fields_ = [("off", C.c_void_p), ("idx", C.c_void_p), ("val", C.c_void_p)]
+
+
+class BuildOpts(C.Structure):
+    _fields_ = [("iterations", C.c_uint32), ("seed", C.c_uint32), ("flags", C.c_uint32), ("dense_scale", C.c_float),
+                ("reserved", C.c_uint32 * 4)]
+
+
+class BuildStats(C.Structure):
+    _fields_ = [("seconds_total", C.c_double), ("seconds_knn", C.c_double), ("seconds_prune", C.c_double),
+                ("distance_evals", C.c_uint64), ("list_updates", C.c_uint64), ("iterations_run", C.c_uint32),
+                ("launches", C.c_uint32), ("reserved", C.c_uint32 * 4)]
+
+
+class SearchOpts(C.Structure):
+    _fields_ = [("cands", C.c_uint32), ("flags", C.c_uint32), ("sparse_weight", C.c_float), ("bm25_weight", C.c_float),
+                ("dense_weight", C.c_float), ("kg_weight", C.c_float), ("arena_bytes", C.c_uint32),
+                ("ctas_per_sm", C.c_uint32), ("reserved", C.c_uint32 * 4)]
+
+
+class Queries(C.Structure):
+    _fields_ = [("nq", C.c_uint32), ("dense", C.c_void_p), ("sparse", _Csr), ("bm25", _Csr), ("ent_off", C.c_void_p),
+                ("ent_idx", C.c_void_p), ("max_sparse_nnz", C.c_uint32), ("max_bm25_nnz", C.c_uint32)]
+
+
+class SearchStats(C.Structure):
+    _fields_ = [("eff_sparse", C.c_float), ("eff_bm25", C.c_float), ("eff_dense", C.c_float), ("path", C.c_uint32),
+                ("kernel_ms", C.c_double), ("total_ms", C.c_double), ("expansions", C.c_uint64),
+                ("evaluations", C.c_uint64), ("gathered_bytes", C.c_uint64), ("launches", C.c_uint32),
+                ("h2d_bytes_lo", C.c_uint32), ("h2d_bytes_hi", C.c_uint32), ("d2h_bytes_lo", C.c_uint32),
+                ("d2h_bytes_hi", C.c_uint32), ("reserved", C.c_uint32 * 3)]
+
+
+def lib_path() -> str:
+    return os.path.join(_HERE, "lib", "libapoe.so")
+
+
+def lib() -> C.CDLL:
+    """The CUDA library.  Raises if it has not been built: there is no other implementation to fall back to."""
+    global _LIB
+    if _LIB is None:
+        p = lib_path()
+        if not os.path.exists(p):
+            raise ApoeError(-1, f"{p} is missing: run `python allan-poe_b200/build.py` (nvcc, sm_100a)")
+        L = C.CDLL(p)
+        L.ap_last_error.restype = C.c_char_p
+        L.ap_ndcg.restype = C.c_double
+        L.ap_index_size.restype = C.c_uint32
+        _LIB = L
+    return _LIB
+
+
+def _check(rc: int) -> None:
+    if rc != AP_OK:
+        raise ApoeError(rc, lib().ap_last_error().decode(errors="replace"))
+
+
+def _np(a, dtype):
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.int32 and dtype == np.uint32:
+        a = a.view(np.uint32)
+    assert a.dtype == dtype, (a.dtype, dtype)
+    return a
+
+
+def _ptr(a) -> C.c_void_p:
+    if a is None:
+        return C.c_void_p(None)
+    if isinstance(a, np.ndarray):
+        return C.c_void_p(a.ctypes.data)
+    return C.c_void_p(a.data_ptr())  # torch tensor
+
+
+def _csr_np(csr):
+    """(off, idx, val) in any of: tuple of arrays, object with .off/.idx/.val (numpy or CPU torch)."""
+    off, idx, val = (csr.off, csr.idx, csr.val) if hasattr(csr, "off") else csr
+    conv = lambda x: x.cpu().numpy() if hasattr(x, "cpu") else np.asarray(x)
+    return _np(conv(off), np.uint32), _np(conv(idx), np.uint32), _np(conv(val), np.float32)
+
+
+class Index:
+    def __init__(self, handle: C.c_void_p, n: int, device: int):
+        self._h, self.n, self.device = handle, n, device
+        self._keep = []
+
+    # ---- creation -------------------------------------------------------------------------------------
+    @classmethod
+    def from_host(cls, dense, sparse, bm25, device: int = 0, for_build: bool = False) -> "Index":
+        dense = _np(dense, np.float32)
+        s, b = _csr_np(sparse), _csr_np(bm25)
+        h = C.c_void_p()
+        _check(lib().ap_index_create_host(C.byref(h), C.c_int(device), C.c_uint32(dense.shape[0]), _ptr(dense),
+                                          _Csr(*map(_ptr, s)), _Csr(*map(_ptr, b)),
+                                          C.c_uint32(CREATE_FOR_BUILD if for_build else 0)))
+        return cls(h, dense.shape[0], device)
+
+    @classmethod
+    def from_device(cls, dense, sparse, bm25, for_build: bool = False) -> "Index":
+        """dense: CUDA float32 [n, 1024]; sparse / bm25: objects with CUDA int32 .off/.idx and float32 .val."""
+        assert dense.is_cuda and dense.is_contiguous()
+        device = dense.device.index or 0
+        h = C.c_void_p()
+        _check(lib().ap_index_create_device(C.byref(h), C.c_int(device), C.c_uint32(dense.shape[0]), _ptr(dense),
+                                            _Csr(_ptr(sparse.off), _ptr(sparse.idx), _ptr(sparse.val)),
+                                            _Csr(_ptr(bm25.off), _ptr(bm25.idx), _ptr(bm25.val)),
+                                            C.c_uint32(CREATE_FOR_BUILD if for_build else 0)))
+        ix = cls(h, dense.shape[0], device)
+        if for_build:
+            ix._keep.append(dense)  # the build may re-read the fp32 rows
+        return ix
+
+    def close(self) -> None:
+        if self._h:
+            lib().ap_index_destroy(self._h)
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    # ---- graph ---------------------------------------------------------------------------------------
+    def set_graph(self, rows, entry_points) -> None:
+        rows, ep = _np(rows, np.uint32), _np(entry_points, np.uint32)
+        assert rows.shape == (self.n, ROW) and ep.shape == (ENTRY_POINTS,)
+        _check(lib().ap_index_set_graph(self._h, _ptr(rows), _ptr(ep)))
+
+    def get_graph(self):
+        rows = np.empty((self.n, ROW), dtype=np.uint32)
+        ep = np.empty(ENTRY_POINTS, dtype=np.uint32)
+        _check(lib().ap_index_get_graph(self._h, _ptr(rows), _ptr(ep)))
+        return rows, ep
+
+    def load_graph(self, path: str) -> None:
+        _check(lib().ap_index_load_graph(self._h, path.encode()))
+
+    def save_graph(self, path: str) -> None:
+        _check(lib().ap_index_save_graph(self._h, path.encode()))
+
+    def build(self, iterations: int = 0, seed: int = 0, flags: int = 0, dense_scale: float = 0.0) -> BuildStats:
+        o = BuildOpts(iterations=iterations, seed=seed, flags=flags, dense_scale=dense_scale)
+        st = BuildStats()
+        _check(lib().ap_index_build(self._h, C.byref(o), C.byref(st)))
+        return st
+
+    def get_knn(self):
+        ids = np.empty((self.n, KNN), dtype=np.uint32)
+        dis = np.empty((self.n, KNN), dtype=np.float32)
+        power = np.empty(self.n, dtype=np.float32)
+        _check(lib().ap_index_get_knn(self._h, _ptr(ids), _ptr(dis), _ptr(power)))
+        return ids, dis, power
+
+    def norms(self) -> np.ndarray:
+        out = np.empty(self.n, dtype=np.float32)
+        _check(lib().ap_index_norms(self._h, _ptr(out)))
+        return out
+
+    def prune(self, knn_ids, knn_dis, power):
+        knn_ids, knn_dis, power = _np(knn_ids, np.uint32), _np(knn_dis, np.float32), _np(power, np.float32)
+        new_list = np.empty((self.n, DEGREE), dtype=np.uint32)
+        kw = np.empty((self.n, 33), dtype=np.uint32)
+        rows = np.empty((self.n, ROW), dtype=np.uint32)
+        _check(lib().ap_index_prune(self._h, _ptr(knn_ids), _ptr(knn_dis), _ptr(power), _ptr(new_list), _ptr(kw),
+                                    _ptr(rows)))
+        return new_list, kw, rows
+
+    def set_kg(self, e2e_off, e2e_idx, e2d_off, e2d_idx) -> None:
+        conv = lambda x: _np(x.cpu().numpy() if hasattr(x, "cpu") else x, np.uint32)
+        a, b, c, d = conv(e2e_off), conv(e2e_idx), conv(e2d_off), conv(e2d_idx)
+        _check(lib().ap_index_set_kg(self._h, C.c_uint32(a.size - 1), _ptr(a), _ptr(b), _ptr(c), _ptr(d)))
+
+    def debug_join_dense(self, plist, pcnt, use_tc: bool):
+        plist, pcnt = _np(plist, np.uint32), _np(pcnt, np.uint32)
+        nodes = plist.shape[0]
+        out = np.zeros((nodes, 64, 32), dtype=np.float32)
+        _check(lib().ap_debug_join_dense(self._h, C.c_uint32(nodes), _ptr(plist), _ptr(pcnt), C.c_int(int(use_tc)),
+                                         _ptr(out)))
+        return out
+
+    # ---- search --------------------------------------------------------------------------------------
+    @staticmethod
+    def _host_queries(qdense, qsparse, qbm25, ent=None):
+        qd = _np(qdense, np.float32)
+        s, b = _csr_np(qsparse), _csr_np(qbm25)
+        q = Queries(nq=qd.shape[0], dense=_ptr(qd), sparse=_Csr(*map(_ptr, s)), bm25=_Csr(*map(_ptr, b)))
+        keep = [qd, s, b]
+        if ent is not None:
+            eo, ei = _np(ent[0], np.uint32), _np(ent[1], np.uint32)
+            q.ent_off, q.ent_idx = _ptr(eo), _ptr(ei)
+            keep += [eo, ei]
+        return q, keep
+
+    def effective_weights(self, qdense, qsparse, qbm25, w_sparse=1.0, w_bm25=1.0, w_dense=1.0):
+        q, keep = self._host_queries(qdense, qsparse, qbm25)
+        ws, wb, wd = C.c_float(w_sparse), C.c_float(w_bm25), C.c_float(w_dense)
+        _check(lib().ap_effective_weights(self._h, C.byref(q), C.byref(ws), C.byref(wb), C.byref(wd)))
+        return ws.value, wb.value, wd.value
+
+    def search(self, qdense, qsparse, qbm25, cands=128, weights=(1.0, 1.0, 1.0), kg_weight=0.0, flags=0, ent=None,
+               arena_bytes=0, ctas_per_sm=0, out=None):
+        """Host buffers in, host results out.  weights = (sparse, bm25, dense).  Returns ids, dis, SearchStats."""
+        q, keep = self._host_queries(qdense, qsparse, qbm25, ent)
+        o = SearchOpts(cands=cands, flags=flags, sparse_weight=weights[0], bm25_weight=weights[1],
+                       dense_weight=weights[2], kg_weight=kg_weight, arena_bytes=arena_bytes, ctas_per_sm=ctas_per_sm)
+        if out is None:
+            ids = np.empty((q.nq, cands), dtype=np.uint32)
+            dis = np.empty((q.nq, cands), dtype=np.float32)
+        else:
+            ids, dis = out
+        st = SearchStats()
+        _check(lib().ap_search_host(self._h, C.byref(q), C.byref(o), _ptr(ids), _ptr(dis), C.byref(st)))
+        return ids, dis, st
+
+    def search_device(self, queries, out_ids, out_dis, cands=128, weights=(1.0, 1.0, 1.0), kg_weight=0.0, flags=0,
+                      ent=None, max_nnz=(0, 0), stream=None, stats=True, arena_bytes=0, ctas_per_sm=0):
+        """Device tensors in and out (queries: object with CUDA .dense and .sparse/.bm25 CSRs).  The weights are
+        used as given: run `effective_weights` on a host copy of the first 100 queries for the normalised ones."""
+        q = Queries(nq=queries.dense.shape[0], dense=_ptr(queries.dense),
+                    sparse=_Csr(_ptr(queries.sparse.off), _ptr(queries.sparse.idx), _ptr(queries.sparse.val)),
+                    bm25=_Csr(_ptr(queries.bm25.off), _ptr(queries.bm25.idx), _ptr(queries.bm25.val)),
+                    max_sparse_nnz=max_nnz[0], max_bm25_nnz=max_nnz[1])
+        if ent is not None:
+            q.ent_off, q.ent_idx = _ptr(ent[0]), _ptr(ent[1])
+        o = SearchOpts(cands=cands, flags=flags | SEARCH_RAW_WEIGHTS, sparse_weight=weights[0], bm25_weight=weights[1],
+                       dense_weight=weights[2], kg_weight=kg_weight, arena_bytes=arena_bytes, ctas_per_sm=ctas_per_sm)
+        st = SearchStats()
+        _check(lib().ap_search_device(self._h, C.byref(q), C.byref(o), _ptr(out_ids), _ptr(out_dis),
+                                      C.c_void_p(stream or 0), C.byref(st) if stats else None))
+        return st
+
+    def fused_distances(self, qdense, qsparse, qbm25, pair_q, pair_d, weights=(1.0, 1.0, 1.0), flags=0):
+        q, keep = self._host_queries(qdense, qsparse, qbm25)
+        pq, pd = _np(pair_q, np.uint32), _np(pair_d, np.uint32)
+        o = SearchOpts(cands=32, flags=flags, sparse_weight=weights[0], bm25_weight=weights[1], dense_weight=weights[2])
+        out = np.empty(pq.size, dtype=np.float32)
+        _check(lib().ap_fused_distances(self._h, C.byref(q), C.byref(o), C.c_size_t(pq.size), _ptr(pq), _ptr(pd),
+                                        _ptr(out)))
+        return out
+
+
+def build_index(dense_path, sparse_path, bm25_path, out_path, device=0, iterations=0, seed=0, flags=0) -> BuildStats:
+    o = BuildOpts(iterations=iterations, seed=seed, flags=flags)
+    st = BuildStats()
+    _check(lib().ap_build_index(dense_path.encode(), sparse_path.encode(), bm25_path.encode(), out_path.encode(),
+                                C.c_int(device), C.byref(o), C.byref(st)))
+    return st
+
+
+def search_index(dense_data_path, dense_query_path, sparse_data_path, sparse_query_path, bm25_data_path,
+                 bm25_query_path, keyword_id_path, knowledge_path, entity2doc_path, query_entity_path, graph_path,
+                 ground_truth_path, top_k, cands, sparse_weight, bm25_weight, dense_weight, kg_weight, device=0,
+                 max_queries=0, nq_hint=None):
+    """File-level search with the results returned (the reference prints nDCG and returns nothing)."""
+    import numpy as _n
+    nq_cap = nq_hint if nq_hint is not None else (os.path.getsize(dense_query_path) // ((DIM + 1) * 4))
+    ids = _n.empty((nq_cap, cands), dtype=_n.uint32)
+    dis = _n.empty((nq_cap, cands), dtype=_n.float32)
+    nq, ndcg, st = C.c_uint32(0), C.c_double(-1.0), SearchStats()
+    e = lambda s: (s or "").encode()
+    _check(lib().ap_search_index(e(dense_data_path), e(dense_query_path), e(sparse_data_path), e(sparse_query_path),
+                                 e(bm25_data_path), e(bm25_query_path), e(keyword_id_path), e(knowledge_path),
+                                 e(entity2doc_path), e(query_entity_path), e(graph_path), e(ground_truth_path),
+                                 C.c_int(top_k), C.c_int(cands), C.c_float(sparse_weight), C.c_float(bm25_weight),
+                                 C.c_float(dense_weight), C.c_float(kg_weight), C.c_int(device),
+                                 C.c_uint32(max_queries), _ptr(ids), _ptr(dis), C.byref(nq), C.byref(ndcg), C.byref(st)))
+    return ids[:nq.value], dis[:nq.value], ndcg.value, st
+
+
+def ndcg(results, top_k, qrels) -> float:
+    results = _np(results, np.uint32)
+    off = np.zeros(len(qrels) + 1, dtype=np.uint32)
+    off[1:] = np.cumsum([len(r) for r in qrels])
+    flat = np.asarray([t for r in qrels for t in r], dtype=np.uint32)
+    return float(lib().ap_ndcg(C.c_uint32(results.shape[0]), _ptr(results), C.c_uint32(results.shape[1]),
+                               C.c_uint32(top_k), _ptr(off), _ptr(flat)))
+
+
+def merge_shard_results(in_ids, in_dis, top_k, out_ids, out_dis, stream=None) -> None:
+    """in_*: CUDA tensors [shards, nq, per_shard] (ids already global); out_*: [nq, top_k]."""
+    shards, nq, per = in_ids.shape
+    _check(lib().ap_merge_shard_results(C.c_int(in_ids.device.index or 0), C.c_uint32(shards), C.c_uint32(nq),
+                                        C.c_uint32(per), _ptr(in_ids), _ptr(in_dis), C.c_uint32(top_k), _ptr(out_ids),
+                                        _ptr(out_dis), C.c_void_p(stream or 0)))

@@ -1,0 +1,1048 @@
+// Index construction on the device: hybrid norms, NN-Descent with a local join, RNG-IP pruning with
+// keyword-aware neighbour recycling, reverse-edge collection, 40-wide row assembly and entry points.
+//
+// What is kept from the reference (src/index.cu): the k-NN list width 64, the hybrid distance
+// 1 - <x, y> with the dense part scaled by 7 and rounded to half, cal_power's arithmetic (:483-534), and the
+// exact semantics of allan_poe (:539-714) and allan_poe_final_graph (:717-807), whose outputs are compared bit
+// for bit with the CPU restatement.  What is new is the k-NN construction: instead of 25 rounds of a
+// 1 x 512 gather-dot per node (:156-376) every round samples new / old neighbours and their reverses, joins
+// the sampled set all-pairs (dense inner products as one 128 x 64 x 1024 tensor-core tile per two nodes, sparse
+// and BM25 inner products by hashing one row and probing with the other), proposes the best partners to every
+// participant and merges proposals into the sorted lists with a warp bitonic sort.
+#include <cub/device/device_radix_sort.cuh>
+
+#include <algorithm>
+#include <chrono>
+#include <cstdio>
+#include <cstring>
+
+#include "apoe_common.cuh"
+
+namespace apoe {
+
+constexpr uint32_t kFull = 0xFFFFFFFFu;
+constexpr int kK = AP_KNN;          // 64
+constexpr int kSample = 16;         // forward / reverse samples per class (new, old)
+constexpr int kPart = 64;           // participants of one local join (the node itself, new, old)
+constexpr int kNewMax = 32;         // "new" rows of a join = columns of its distance tile
+constexpr int kPropCap = 96;        // proposals a node can receive per round
+constexpr int kPropPer = 3;         // best partners proposed to each participant of a join
+constexpr uint32_t kNewFlag = 0x80000000u;
+
+// ---------------------------------------------------------------------------------------------------------
+// norms: ref cal_power, src/index.cu:483-534 -- half squares and half tree sums per 32-chunk of the dense row,
+// float squares / tree sums for the sparse and BM25 values (all added onto chunk slot 0), then a left-to-right
+// float sum of the 32 slots.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void norms_kernel(uint32_t n, const uint64_t *__restrict__ meta, const uint8_t *__restrict__ rec, float *__restrict__ power) {
+    const uint32_t d = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (d >= n) return;
+    const uint64_t m = meta[d];
+    const uint8_t *r = rec + meta_off16(m) * 16ull;
+    const __half *dense = reinterpret_cast<const __half *>(r);
+    float slot = 0.0f;  // lane c keeps chunk c's sum
+    for (int c = 0; c < 32; ++c) {
+        const __half x = dense[c * 32 + lane];
+        __half v = __hmul_rn(x, x);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v = __hadd_rn(v, __shfl_down_sync(kFull, v, o));
+        const float s = __half2float(__shfl_sync(kFull, v, 0));
+        if ((int)lane == c) slot = s;
+    }
+    const uint2 *pairs = reinterpret_cast<const uint2 *>(r + kDenseBytes);
+    const uint32_t ns = meta_ns(m), nb = meta_nb(m);
+    float s0 = __shfl_sync(kFull, slot, 0);
+    for (int w = 0; w < 2; ++w) {
+        const uint2 *p = w == 0 ? pairs : pairs + pad2(ns);
+        const uint32_t cnt = w == 0 ? ns : nb;
+        for (uint32_t base = 0; base < cnt; base += 32) {
+            const float x = base + lane < cnt ? __uint_as_float(p[base + lane].y) : 0.0f;
+            float t = __fmul_rn(x, x);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) t = __fadd_rn(t, __shfl_down_sync(kFull, t, o));
+            s0 = __fadd_rn(s0, __shfl_sync(kFull, t, 0));
+        }
+    }
+    float acc = s0;
+    for (int i = 1; i < 32; ++i) acc = __fadd_rn(acc, __shfl_sync(kFull, slot, i));
+    if (lane == 0) power[d] = acc;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// NN-Descent state
+// ---------------------------------------------------------------------------------------------------------
+struct Knn {
+    uint32_t n;
+    uint32_t *ids;   // n x 64, bit 31 = not yet sampled ("new")
+    float *dis;      // n x 64 ascending
+    uint32_t *samp;  // n x 64: [new fwd 16 | new rev 16 | old fwd 16 | old rev 16]
+    uint32_t *scnt;  // n x 4 counts of the above (reverse counts may exceed the capacity)
+    uint32_t *plist; // n x 64 participants of the node's join (the node first, then new, then old)
+    uint32_t *pcnt;  // n x 2: rows that are new, rows in total
+    uint2 *prop;     // n x kPropCap (distance bits, id)
+    uint32_t *propn; // n
+    unsigned long long *stats;  // [0] distance evaluations, [1] list updates, [2] proposal overflows
+};
+
+__device__ __forceinline__ uint32_t mix32(uint32_t x) {
+    x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
+    return x;
+}
+
+// Random initial lists: 64 distinct ids != v with distance 1e6 and the "new" flag (ref: initialize_graph,
+// src/index.cu:99-106, seeded there from clock(); here from `seed` so a build is repeatable).
+__global__ void knn_init_kernel(Knn k, uint32_t seed) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= k.n * (uint32_t)kK) return;
+    const uint32_t v = i / kK, s = i % kK, n = k.n;
+    uint32_t id;
+    if (n <= (uint32_t)kK + 1) id = (v + 1 + s % (n - 1)) % n;  // tiny corpora: duplicates are unavoidable
+    else {
+        const uint32_t span = n - 1, step_max = span / kK;
+        const uint32_t a = 1 + mix32(seed ^ (v * 2654435761u)) % step_max, b = mix32(seed + 0x9e3779b9u + v) % span;
+        id = (v + 1 + (uint32_t)(((uint64_t)b + (uint64_t)s * a) % span)) % n;
+    }
+    k.ids[i] = id | kNewFlag;
+    k.dis[i] = kInfDis;
+}
+
+// Sampling: the closest 16 unsampled ("new") and the closest 16 sampled ("old") entries of every list, plus the
+// reverse of those choices.  Sampled new entries lose their flag.
+__global__ void knn_sample_kernel(Knn k, uint32_t round) {
+    const uint32_t v = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (v >= k.n) return;
+    uint32_t nn = 0, no = 0;
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t slot = h * 32 + lane;
+        const uint32_t raw = k.ids[(size_t)v * kK + slot];
+        const bool isnew = (raw & kNewFlag) != 0;
+        const uint32_t id = raw & ~kNewFlag;
+        const uint32_t bn = __ballot_sync(kFull, isnew), bo = ~bn;
+        const uint32_t rn = nn + __popc(bn & ((1u << lane) - 1u)), ro = no + __popc(bo & ((1u << lane) - 1u));
+        if (isnew && rn < kSample && id < k.n) {
+            k.samp[(size_t)v * 64 + rn] = id;
+            k.ids[(size_t)v * kK + slot] = id;  // now "old"
+            const uint32_t t = atomicAdd(&k.scnt[(size_t)id * 4 + 1], 1u);
+            if (t < kSample) k.samp[(size_t)id * 64 + 16 + t] = v;
+            else { const uint32_t r = mix32(v ^ (round * 0x9e3779b9u) ^ t) % (t + 1); if (r < kSample) k.samp[(size_t)id * 64 + 16 + r] = v; }
+        }
+        if (!isnew && ro < kSample && id < k.n) {
+            k.samp[(size_t)v * 64 + 32 + ro] = id;
+            const uint32_t t = atomicAdd(&k.scnt[(size_t)id * 4 + 3], 1u);
+            if (t < kSample) k.samp[(size_t)id * 64 + 48 + t] = v;
+            else { const uint32_t r = mix32(v ^ (round * 0x85ebca6bu) ^ t) % (t + 1); if (r < kSample) k.samp[(size_t)id * 64 + 48 + r] = v; }
+        }
+        nn += __popc(bn); no += __popc(bo);
+    }
+    if (lane == 0) { k.scnt[(size_t)v * 4 + 0] = min(nn, (uint32_t)kSample); k.scnt[(size_t)v * 4 + 2] = min(no, (uint32_t)kSample); }
+}
+
+// Participants of v's join: v itself, then the distinct new samples, then the distinct old samples not already
+// present; at most 32 new rows and 64 rows in total.  One warp per node.
+__global__ void knn_plist_kernel(Knn k) {
+    const uint32_t v = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (v >= k.n) return;
+    __shared__ uint32_t sh[8][kPart];
+    uint32_t *pl = sh[(threadIdx.x >> 5)];
+    const uint32_t *sm = k.samp + (size_t)v * 64;
+    const uint32_t c0 = k.scnt[(size_t)v * 4 + 0], c1 = min(k.scnt[(size_t)v * 4 + 1], (uint32_t)kSample);
+    const uint32_t c2 = k.scnt[(size_t)v * 4 + 2], c3 = min(k.scnt[(size_t)v * 4 + 3], (uint32_t)kSample);
+    if (lane == 0) pl[0] = v;
+    __syncwarp();
+    uint32_t cnt = 1, n_new = 1;
+    for (int cls = 0; cls < 2; ++cls) {
+        const uint32_t na = cls == 0 ? c0 : c2, nb = cls == 0 ? c1 : c3, base = cls * 32;
+        const uint32_t cap = cls == 0 ? (uint32_t)kNewMax : (uint32_t)kPart;
+        // lane l < 16: forward sample l, lane l >= 16: reverse sample l - 16
+        const bool have = lane < 16 ? lane < na : (lane - 16) < nb;
+        const uint32_t id = have ? sm[base + lane] : kEmpty;
+        bool ok = have && id < k.n;
+        for (uint32_t j = 0; ok && j < cnt; ++j) ok = pl[j] != id;         // not yet a participant
+        const uint32_t grp = __match_any_sync(kFull, id);
+        ok = ok && (__ffs(grp) - 1) == (int)lane;                          // first of equal ids in this batch
+        const uint32_t bal = __ballot_sync(kFull, ok);
+        const uint32_t pos = cnt + __popc(bal & ((1u << lane) - 1u));
+        if (ok && pos < cap) pl[pos] = id;
+        cnt = min(cnt + __popc(bal), cap);
+        if (cls == 0) n_new = cnt;
+        __syncwarp();
+    }
+    for (uint32_t j = lane; j < kPart; j += 32) k.plist[(size_t)v * kPart + j] = j < cnt ? pl[j] : kEmpty;
+    if (lane == 0) { k.pcnt[(size_t)v * 2] = n_new; k.pcnt[(size_t)v * 2 + 1] = cnt; }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Join, dense part on CUDA cores: D[v][j][i] = <dense(plist[j]), dense(plist[i])>, j < rows, i < n_new, fp32
+// accumulation of half products.  The tensor-core kernel in apoe_join_tc.cu fills the same scratch layout.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256, 2) join_dense_simt_kernel(uint32_t node0, uint32_t nodes, const uint32_t *__restrict__ plist,
+                                                              const uint32_t *__restrict__ pcnt, const uint64_t *__restrict__ meta,
+                                                              const uint8_t *__restrict__ rec, float *__restrict__ D) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    uint4 *newrows = reinterpret_cast<uint4 *>(smem);  // 32 rows x 128 uint4
+    const uint32_t local = blockIdx.x;
+    if (local >= nodes) return;
+    const uint32_t v = node0 + local;
+    const uint32_t n_new = pcnt[(size_t)v * 2], rows = pcnt[(size_t)v * 2 + 1];
+    if (n_new <= 1 && rows <= 1) return;
+    const uint32_t *pl = plist + (size_t)v * kPart;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    for (uint32_t idx = tid; idx < n_new * 128; idx += 256) {
+        const uint32_t i = idx >> 7, c = idx & 127;
+        const uint4 *src = reinterpret_cast<const uint4 *>(rec + meta_off16(meta[pl[i]]) * 16ull);
+        newrows[idx] = __ldg(src + c);
+    }
+    __syncthreads();
+    float *out = D + (size_t)local * kPart * kNewMax;
+    for (uint32_t j = warp; j < rows; j += 8) {
+        const uint4 *src = reinterpret_cast<const uint4 *>(rec + meta_off16(meta[pl[j]]) * 16ull);
+        uint4 a[4];
+#pragma unroll
+        for (int k = 0; k < 4; ++k) a[k] = __ldg(src + lane + 32 * k);
+        float vals[kNewMax];
+#pragma unroll
+        for (int i = 0; i < kNewMax; ++i) {
+            float acc = 0.0f;
+            if ((uint32_t)i < n_new) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    const uint4 b = newrows[i * 128 + lane + 32 * k];
+                    const uint32_t aw[4] = {a[k].x, a[k].y, a[k].z, a[k].w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q) {
+                        const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&aw[q]));
+                        const float2 fb = __half22float2(*reinterpret_cast<const __half2 *>(&bw[q]));
+                        acc = fmaf(fa.x, fb.x, acc); acc = fmaf(fa.y, fb.y, acc);
+                    }
+                }
+            }
+            vals[i] = acc;
+        }
+        // 32 warp sums in 31 shuffles: lane l ends up with the total of vals[l]
+#pragma unroll
+        for (int o = 16, len = 32; o >= 1; o >>= 1, len >>= 1) {
+#pragma unroll
+            for (int q = 0; q < len / 2; ++q) {
+                const bool up = (lane & o) != 0;
+                const float keep = up ? vals[q + len / 2] : vals[q];
+                const float send = up ? vals[q] : vals[q + len / 2];
+                vals[q] = keep + __shfl_xor_sync(kFull, send, o);
+            }
+        }
+        out[(size_t)j * kNewMax + lane] = vals[0];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Join, sparse + BM25 part, distance assembly, partner selection and proposals.  One CTA per node.
+// ---------------------------------------------------------------------------------------------------------
+struct JoinArgs {
+    uint32_t node0, nodes;
+    const uint32_t *plist, *pcnt;
+    const uint64_t *meta;
+    const uint8_t *rec;
+    const float *D;          // nodes x 64 x 32 dense inner products
+    const float *knn_dis;    // n x 64 (kth distance filter)
+    uint2 *prop; uint32_t *propn;
+    unsigned long long *stats;
+    uint32_t *err;
+    uint32_t arena_bytes;    // shared-memory budget for the sparse sections of all participants
+    uint32_t tab_mask, tab_shift, groups;  // hash table of one new row's terms; rows hashed per round
+    uint32_t o_tab, o_dm, o_arena;
+};
+constexpr int kJoinThreads = 256;
+
+__device__ __forceinline__ void jtab_insert(uint2 *tab, uint32_t mask, uint32_t shift, uint32_t key, uint32_t valbits) {
+    uint32_t h = (key * 2654435761u) >> shift;
+    for (uint32_t i = 0; i <= mask; ++i) {
+        const uint32_t old = atomicCAS(&tab[h].x, kEmpty, key);
+        if (old == kEmpty) { tab[h].y = valbits; return; }
+        if (old == key) return;
+        h = (h + 1) & mask;
+    }
+}
+
+__global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const JoinArgs a) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t mbar;
+    __shared__ uint32_t s_off[kPart + 1], s_id[kPart], s_ns[kPart], s_nb[kPart];
+    __shared__ float s_kth[kPart];
+    __shared__ uint32_t s_rows, s_new;
+    uint2 *tab = reinterpret_cast<uint2 *>(smem + a.o_tab);
+    float *dm = reinterpret_cast<float *>(smem + a.o_dm);  // [32][64] distances: new row i x participant j
+    uint8_t *arena = smem + a.o_arena;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const uint32_t local = blockIdx.x;
+    if (local >= a.nodes) return;
+    const uint32_t v = a.node0 + local;
+    uint32_t n_new = a.pcnt[(size_t)v * 2], rows = a.pcnt[(size_t)v * 2 + 1];
+    if (rows <= 1) return;
+    if (tid == 0) { mbar_init(&mbar, 1); mbar_fence_init(); }
+    if (tid < kPart) {
+        const uint32_t id = tid < (int)rows ? a.plist[(size_t)v * kPart + tid] : kEmpty;
+        s_id[tid] = id;
+        uint64_t m = 0;
+        if (id != kEmpty) { m = a.meta[id]; s_kth[tid] = a.knn_dis[(size_t)id * kK + kK - 1]; }
+        s_ns[tid] = meta_ns(m); s_nb[tid] = meta_nb(m);
+    }
+    __syncthreads();
+    if (tid == 0) {
+        // participants are dropped from the end when their sparse sections overflow the arena
+        uint32_t o = 0, r = 0;
+        for (; r < rows; ++r) {
+            const uint32_t sz = 8u * (pad2(s_ns[r]) + pad2(s_nb[r]));
+            if (o + sz > a.arena_bytes) break;
+            s_off[r] = o; o += sz;
+        }
+        s_off[r] = o;
+        s_rows = r; s_new = min(n_new, r);
+        mbar_arrive_expect_tx(&mbar, o);
+    }
+    __syncthreads();
+    rows = s_rows; n_new = s_new;
+    if (tid < (int)rows) {
+        const uint32_t sz = s_off[tid + 1] - s_off[tid];
+        if (sz) bulk_g2s(arena + s_off[tid], a.rec + meta_off16(a.meta[s_id[tid]]) * 16ull + kDenseBytes, sz, &mbar);
+    }
+    for (uint32_t i = tid; i < (a.tab_mask + 1) * a.groups; i += kJoinThreads) tab[i] = make_uint2(kEmpty, 0u);
+    mbar_wait_bounded(&mbar, 0, a.err, 3u);
+    __syncthreads();
+
+    const float *D = a.D + (size_t)local * kPart * kNewMax;
+    unsigned long long evals = 0;
+    for (uint32_t i0 = 0; i0 < n_new; i0 += a.groups) {
+        const uint32_t g_cnt = min(a.groups, n_new - i0);
+        // hash the terms of rows i0 .. i0+g_cnt-1 (BM25 ids get bit 31 so both vocabularies share one table)
+        for (uint32_t g = 0; g < g_cnt; ++g) {
+            const uint32_t i = i0 + g;
+            const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[i]);
+            const uint32_t ns = s_ns[i], nb = s_nb[i], pns = pad2(ns);
+            uint2 *t = tab + (size_t)g * (a.tab_mask + 1);
+            for (uint32_t j = tid; j < ns + nb; j += kJoinThreads) {
+                const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
+                jtab_insert(t, a.tab_mask, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y);
+            }
+        }
+        __syncthreads();
+        // one warp per (row i, participant j) pair: j > i among the new rows, every old row
+        const uint32_t items = g_cnt * rows;
+        for (uint32_t it = warp; it < items; it += kJoinThreads / 32) {
+            const uint32_t g = it / rows, j = it % rows, i = i0 + g;
+            if (j <= i) continue;
+            const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[j]);
+            const uint32_t ns = s_ns[j], nb = s_nb[j], pns = pad2(ns);
+            const uint2 *t = tab + (size_t)g * (a.tab_mask + 1);
+            float acc = 0.0f;
+            for (uint32_t q = lane; q < ns + nb; q += 32) {
+                const uint2 p = q < ns ? pr[q] : pr[pns + (q - ns)];
+                const uint32_t key = q < ns ? p.x : (p.x | 0x80000000u);
+                uint32_t h = (key * 2654435761u) >> a.tab_shift;
+                for (uint32_t s = 0; s <= a.tab_mask; ++s) {
+                    const uint2 e = t[h];
+                    if (e.x == kEmpty) break;
+                    if (e.x == key) { acc = fmaf(__uint_as_float(e.y), __uint_as_float(p.y), acc); break; }
+                    h = (h + 1) & a.tab_mask;
+                }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(kFull, acc, o);
+            if (lane == 0) { dm[i * kPart + j] = 1.0f - D[(size_t)j * kNewMax + i] - acc; ++evals; }
+        }
+        __syncthreads();
+        for (uint32_t q = tid; q < (a.tab_mask + 1) * g_cnt; q += kJoinThreads) tab[q] = make_uint2(kEmpty, 0u);
+        __syncthreads();
+    }
+
+    // partner selection: every participant proposes to itself its kPropPer closest partners of this join
+    if (tid < (int)rows) {
+        const uint32_t p = tid;
+        float bd[kPropPer]; uint32_t bi[kPropPer];
+#pragma unroll
+        for (int q = 0; q < kPropPer; ++q) { bd[q] = s_kth[p]; bi[q] = kEmpty; }
+        const uint32_t lim = p < n_new ? rows : n_new;
+        for (uint32_t j = 0; j < lim; ++j) {
+            if (j == p) continue;
+            const uint32_t lo = min(p, j), hi = max(p, j);
+            const float d = dm[lo * kPart + hi];
+            if (d < bd[kPropPer - 1]) {
+                int q = kPropPer - 1;
+                while (q > 0 && d < bd[q - 1]) { bd[q] = bd[q - 1]; bi[q] = bi[q - 1]; --q; }
+                bd[q] = d; bi[q] = s_id[j];
+            }
+        }
+        const uint32_t me = s_id[p];
+#pragma unroll
+        for (int q = 0; q < kPropPer; ++q)
+            if (bi[q] != kEmpty) {
+                const uint32_t t = atomicAdd(&a.propn[me], 1u);
+                if (t < kPropCap) a.prop[(size_t)me * kPropCap + t] = make_uint2(__float_as_uint(bd[q]), bi[q]);
+                else atomicAdd(a.stats + 2, 1ull);
+            }
+    }
+    if (lane == 0 && evals) atomicAdd(a.stats + 0, evals);
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Merge proposals into the sorted lists: one warp per node, bitonic sorts over 64 + proposals elements held in
+// shared memory (first by id to drop duplicates, then by distance), best 64 written back.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kMergeLen = 256;  // power of two >= 64 + kPropCap
+__device__ __forceinline__ void warp_bitonic_u64(unsigned long long *key, int lane) {
+    for (int size = 2; size <= kMergeLen; size <<= 1)
+        for (int stride = size >> 1; stride > 0; stride >>= 1) {
+            for (int t = lane; t < kMergeLen / 2; t += 32) {
+                const int lo = 2 * t - (t & (stride - 1));
+                const int hi = lo + stride;
+                const bool asc = (lo & size) == 0;
+                const unsigned long long x = key[lo], y = key[hi];
+                if ((x > y) == asc) { key[lo] = y; key[hi] = x; }
+            }
+            __syncwarp();
+        }
+}
+__device__ __forceinline__ uint32_t f2ord(float f) { const uint32_t b = __float_as_uint(f); return (b & 0x80000000u) ? ~b : (b | 0x80000000u); }
+__device__ __forceinline__ float ord2f(uint32_t o) { return __uint_as_float((o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o); }
+
+__global__ void __launch_bounds__(128, 8) knn_merge_kernel(Knn k) {
+    __shared__ unsigned long long keys[4][kMergeLen];
+    const uint32_t v = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (v >= k.n) return;
+    const uint32_t np = min(k.propn[v], (uint32_t)kPropCap);
+    if (np == 0) return;
+    unsigned long long *key = keys[threadIdx.x >> 5];
+    // pass 1 key: id (30 bits) | origin (0 = sampled list entry, 1 = unsampled list entry, 2 = proposal) | distance
+    // order bits -> equal ids become adjacent with the existing entry first
+    for (int t = lane; t < kMergeLen; t += 32) {
+        unsigned long long kk = ~0ull;
+        if (t < kK) {
+            const uint32_t raw = k.ids[(size_t)v * kK + t];
+            kk = ((unsigned long long)(raw & 0x3FFFFFFFu) << 34) | ((unsigned long long)(raw >> 31) << 32) | f2ord(k.dis[(size_t)v * kK + t]);
+        } else if (t - kK < (int)np) {
+            const uint2 p = k.prop[(size_t)v * kPropCap + (t - kK)];
+            if (p.y != v) kk = ((unsigned long long)(p.y & 0x3FFFFFFFu) << 34) | (2ull << 32) | f2ord(__uint_as_float(p.x));
+        }
+        key[t] = kk;
+    }
+    __syncwarp();
+    warp_bitonic_u64(key, lane);
+    // pass 2 key: distance order bits | id | origin, duplicates of an id (all but the first) dropped
+    unsigned long long nk[kMergeLen / 32];
+#pragma unroll
+    for (int q = 0; q < kMergeLen / 32; ++q) {
+        const int t = lane + 32 * q;
+        const unsigned long long kk = key[t];
+        unsigned long long out = ~0ull;
+        if (kk != ~0ull) {
+            const uint32_t id = (uint32_t)(kk >> 34);
+            const bool dup = t > 0 && key[t - 1] != ~0ull && (uint32_t)(key[t - 1] >> 34) == id;
+            if (!dup) out = ((unsigned long long)(uint32_t)kk << 32) | ((unsigned long long)id << 2) | ((kk >> 32) & 3ull);
+        }
+        nk[q] = out;
+    }
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < kMergeLen / 32; ++q) key[lane + 32 * q] = nk[q];
+    __syncwarp();
+    warp_bitonic_u64(key, lane);
+    uint32_t changed = 0;
+    for (int t = lane; t < kK; t += 32) {
+        const unsigned long long kk = key[t];
+        uint32_t id = kEmpty & 0x7FFFFFFFu, fl = 0; float d = kInfDis;
+        if (kk != ~0ull) { id = (uint32_t)(kk >> 2) & 0x3FFFFFFFu; fl = ((uint32_t)kk & 3u) != 0; d = ord2f((uint32_t)(kk >> 32)); }
+        const uint32_t raw = id | (fl << 31);
+        if ((k.ids[(size_t)v * kK + t] & 0x7FFFFFFFu) != id) ++changed;
+        k.ids[(size_t)v * kK + t] = raw;
+        k.dis[(size_t)v * kK + t] = d;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) changed += __shfl_xor_sync(kFull, changed, o);
+    if (lane == 0 && changed) atomicAdd(k.stats + 1, (unsigned long long)changed);
+}
+
+__global__ void knn_finish_kernel(Knn k, uint32_t *out_ids) {  // strip flags; unfilled slots point at a valid id
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= k.n * (uint32_t)kK) return;
+    uint32_t id = k.ids[i] & 0x7FFFFFFFu;
+    if (id >= k.n) id = (i / kK + 1) % k.n;
+    out_ids[i] = id;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Pruning: ref allan_poe, src/index.cu:539-714.  One CTA (8 warps) per node.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kPruneThreads = 256;
+constexpr int kPruneWarps = 8;
+
+struct PruneArgs {
+    uint32_t n;
+    const uint32_t *knn; const float *knn_dis; const float *power;
+    const uint64_t *meta; const uint8_t *rec;
+    uint32_t *new_list;   // n x 32
+    uint32_t *detour;     // n x 32 (detour count riding with slot i, as the reference scatters it)
+    uint32_t *kw_edge;    // n x 33
+    uint32_t tab_mask, tab_shift;   // candidate's term table (sparse ids, BM25 ids | bit 31)
+    uint32_t own_mask, own_shift;   // the node's own BM25 term set
+    uint32_t o_tab, o_own, o_lists;
+    int unfused;
+};
+
+// the reference's shared-memory bitonic network on (key, value) pairs, run by the whole CTA
+__device__ __forceinline__ void block_bitonic_kv(uint32_t *key, uint32_t *val, uint32_t len, int tid, int nthreads) {
+    for (uint32_t stride = 1; stride < len; stride <<= 1)
+        for (uint32_t step = stride; step > 0; step >>= 1) {
+            for (uint32_t k = tid; k < len / 2; k += nthreads) {
+                const uint32_t aa = 2 * step * (k / step), bb = k % step;
+                const uint32_t u = (step == stride) ? (aa + step - 1 - bb) : (aa + bb), d = aa + bb + step;
+                if (d < len && key[u] > key[d]) {
+                    uint32_t t = key[u]; key[u] = key[d]; key[d] = t;
+                    t = val[u]; val[u] = val[d]; val[d] = t;
+                }
+            }
+            __syncthreads();
+        }
+}
+
+__device__ __forceinline__ bool set_contains(const uint32_t *tab, uint32_t mask, uint32_t shift, uint32_t key) {
+    uint32_t h = (key * 2654435761u) >> shift;
+    for (uint32_t i = 0; i <= mask; ++i) {
+        const uint32_t e = tab[h];
+        if (e == kEmpty) return false;
+        if (e == key) return true;
+        h = (h + 1) & mask;
+    }
+    return false;
+}
+
+__global__ void __launch_bounds__(kPruneThreads, 2) prune_kernel(const PruneArgs a) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    __shared__ uint32_t nei0[kK], nei1[kK], nei2[kK + 1], det[kK];
+    __shared__ uint32_t s_tmp_id, s_ipn, s_cur_nei, s_cur_nei2;
+    __shared__ uint32_t vflag[16];
+    uint2 *tab = reinterpret_cast<uint2 *>(smem + a.o_tab);
+    uint32_t *own = reinterpret_cast<uint32_t *>(smem + a.o_own);
+    uint32_t *lists = reinterpret_cast<uint32_t *>(smem + a.o_lists);   // 64 x 64 neighbour ids
+    float *ldis = reinterpret_cast<float *>(lists + kK * kK);          // 64 x 64 neighbour distances
+    const uint32_t bid = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (bid >= a.n) return;
+    const uint32_t *g = a.knn + (size_t)bid * kK;
+
+    if (tid < kK) { nei0[tid] = g[tid]; det[tid] = 0; nei2[tid] = 0; }
+    if (tid == 0) nei2[kK] = 0;
+    if (tid < 16) vflag[tid] = 0;
+    for (uint32_t i = tid; i <= a.own_mask; i += kPruneThreads) own[i] = kEmpty;
+    for (uint32_t i = tid; i <= a.tab_mask; i += kPruneThreads) tab[i] = make_uint2(kEmpty, 0u);
+    __syncthreads();
+    {   // the node's own BM25 terms (ref :559-565)
+        const uint64_t m = a.meta[bid];
+        const uint2 *pr = reinterpret_cast<const uint2 *>(a.rec + meta_off16(m) * 16ull + kDenseBytes) + pad2(meta_ns(m));
+        for (uint32_t j = tid; j < meta_nb(m); j += kPruneThreads) {
+            const uint32_t key = pr[j].x;
+            uint32_t h = (key * 2654435761u) >> a.own_shift;
+            for (uint32_t s = 0; s <= a.own_mask; ++s) {
+                const uint32_t old = atomicCAS(&own[h], kEmpty, key);
+                if (old == kEmpty || old == key) break;
+                h = (h + 1) & a.own_mask;
+            }
+        }
+    }
+    // neighbours' lists for the detour count (ref :572-597)
+    for (uint32_t idx = tid; idx < kK * kK; idx += kPruneThreads) {
+        const uint32_t p = idx >> 6, j = idx & 63;
+        lists[idx] = a.knn[(size_t)nei0[p] * kK + j];
+        ldis[idx] = a.knn_dis[(size_t)nei0[p] * kK + j];
+    }
+    __syncthreads();
+    for (uint32_t pair = tid; pair < kK * kK; pair += kPruneThreads) {
+        const uint32_t p = pair >> 6, t = pair & 63;
+        if (t <= p) continue;
+        const uint32_t key = nei0[t];
+        int r = -1;
+        for (int j = 0; j < kK; ++j) if (lists[p * kK + j] == key) { r = j; break; }
+        if (r >= 0 && ldis[p * kK + r] < a.knn_dis[(size_t)bid * kK + t]) atomicAdd(&det[t], 1u);
+    }
+    __syncthreads();
+    block_bitonic_kv(det, nei0, kK, tid, kPruneThreads);
+    if (tid == 0) { nei1[0] = nei0[0]; s_tmp_id = 1; s_ipn = 1; s_cur_nei = 0; s_cur_nei2 = 0; }
+    __syncthreads();
+
+    // RNG-IP joint pruning (ref :613-676)
+    while (s_ipn < kK) {
+        const uint32_t cn = nei0[s_tmp_id], ipn = s_ipn;
+        const uint64_t cm = a.meta[cn];
+        const uint8_t *crec = a.rec + meta_off16(cm) * 16ull;
+        {   // candidate's terms into the table
+            const uint2 *pr = reinterpret_cast<const uint2 *>(crec + kDenseBytes);
+            const uint32_t ns = meta_ns(cm), nb = meta_nb(cm), pns = pad2(ns);
+            for (uint32_t j = tid; j < ns + nb; j += kPruneThreads) {
+                const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
+                jtab_insert(tab, a.tab_mask, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y);
+            }
+        }
+        uint32_t creg[16];  // candidate's dense row in the reference's lane / chunk association
+        {
+            const uint2 *d = reinterpret_cast<const uint2 *>(crec);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) { const uint2 x = __ldg(d + lane + 32 * k); creg[2 * k] = x.x; creg[2 * k + 1] = x.y; }
+        }
+        const float cpow = a.power[cn];
+        __syncthreads();
+        for (uint32_t i = warp; i < ipn; i += kPruneWarps) {
+            const uint32_t sn = nei1[i];
+            if (sn == kEmpty) continue;
+            const uint64_t sm = a.meta[sn];
+            const uint8_t *srec = a.rec + meta_off16(sm) * 16ull;
+            uint32_t acc = 0;
+            const uint2 *d = reinterpret_cast<const uint2 *>(srec);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const uint2 x = __ldg(d + lane + 32 * k);
+                if (a.unfused) { acc = hadd2_rn(acc, hmul2_rn(creg[2 * k], x.x)); acc = hadd2_rn(acc, hmul2_rn(creg[2 * k + 1], x.y)); }
+                else { acc = hfma2_rn(creg[2 * k], x.x, acc); acc = hfma2_rn(creg[2 * k + 1], x.y, acc); }
+            }
+            const uint2 *pr = reinterpret_cast<const uint2 *>(srec + kDenseBytes);
+            const uint32_t ns = meta_ns(sm), nb = meta_nb(sm), pns = pad2(ns);
+            float sp = 0.0f, bm = 0.0f;
+            uint32_t kw = 0;
+            for (uint32_t j = lane; j < ns; j += 32) {
+                const uint2 p = __ldg(pr + j);
+                uint32_t h = (p.x * 2654435761u) >> a.tab_shift;
+                for (uint32_t s = 0; s <= a.tab_mask; ++s) {
+                    const uint2 e = tab[h];
+                    if (e.x == kEmpty) break;
+                    if (e.x == p.x) { sp = __fmaf_rn(__uint_as_float(e.y), __uint_as_float(p.y), sp); break; }
+                    h = (h + 1) & a.tab_mask;
+                }
+            }
+            for (uint32_t j = lane; j < nb; j += 32) {
+                const uint2 p = __ldg(pr + pns + j);
+                const uint32_t key = p.x | 0x80000000u;
+                uint32_t h = (key * 2654435761u) >> a.tab_shift;
+                bool found = false;
+                for (uint32_t s = 0; s <= a.tab_mask; ++s) {
+                    const uint2 e = tab[h];
+                    if (e.x == kEmpty) break;
+                    if (e.x == key) { bm = __fmaf_rn(__uint_as_float(e.y), __uint_as_float(p.y), bm); found = true; break; }
+                    h = (h + 1) & a.tab_mask;
+                }
+                // a term of s that the candidate lacks but the node owns (ref :144-149)
+                if (!found && set_contains(own, a.own_mask, a.own_shift, p.x)) kw = 1;
+            }
+            float tot = __fadd_rn(sp, bm);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                acc = hadd2_rn(acc, __shfl_down_sync(kFull, acc, o));
+                tot = __fadd_rn(tot, __shfl_down_sync(kFull, tot, o));
+            }
+            kw = __any_sync(kFull, kw != 0);
+            if (lane == 0) {
+                // the reference runs slot i on warp i % 16 and leaves that warp's flag set until the end of the step
+                if (kw) vflag[i & 15] = 1;
+                const float ip = __fadd_rn(half_sum_to_float(acc), tot);
+                if (cpow < ip) s_cur_nei = 1;
+                if (a.power[sn] < ip) nei1[i] = kEmpty;
+                if (vflag[i & 15] != 1) s_cur_nei2 = 1;
+            }
+            __syncwarp();
+        }
+        __syncthreads();
+        if (tid == 0) {
+            uint32_t n2 = ipn;
+            if (s_cur_nei == 0) { nei1[n2] = cn; ++n2; }
+            if (s_cur_nei2 == 0) nei2[n2] = 1;  // written after the increment, as in the reference
+            s_ipn = n2; s_cur_nei = 0; s_cur_nei2 = 0; s_tmp_id = s_tmp_id + 1;
+        }
+        if (tid < 16) vflag[tid] = 0;
+        for (uint32_t i = tid; i <= a.tab_mask; i += kPruneThreads) tab[i] = make_uint2(kEmpty, 0u);
+        __syncthreads();
+        if (s_tmp_id >= kK) break;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t ipn = s_ipn;
+        uint32_t count = 0, i_neis;
+        for (i_neis = 0; i_neis < ipn && count < AP_DEGREE; ++i_neis)
+            if (nei1[i_neis] != kEmpty) nei0[count++] = nei1[i_neis];
+        uint32_t *ke = a.kw_edge + (size_t)bid * 33;
+        uint32_t kc = 0;
+        for (uint32_t i = i_neis; i < ipn; ++i)
+            if (nei2[i] == 1 && nei1[i] != kEmpty && kc < 32) { ke[kc + 1] = nei1[i]; ++kc; }
+        ke[0] = kc;
+        for (uint32_t i = kc + 1; i < 33; ++i) ke[i] = 0;
+    }
+    __syncthreads();
+    if (tid < AP_DEGREE) {
+        a.new_list[(size_t)bid * AP_DEGREE + tid] = nei0[tid];
+        a.detour[(size_t)bid * AP_DEGREE + tid] = det[tid];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Reverse edges and final rows: ref src/index.cu:699-711 (scatter) and :717-807 (allan_poe_final_graph).
+// The reference scatters with atomics from racing blocks; here every edge gets the key
+// (target, source, slot), the keys are radix-sorted, and each target replays its edges in ascending
+// (source, slot) order with the reference's "first 32 fill, later ones replace slot k % 32 when their detour
+// count is smaller" rule.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void rev_keys_kernel(uint32_t n, const uint32_t *__restrict__ new_list, const uint32_t *__restrict__ detour,
+                                unsigned long long *__restrict__ keys, uint32_t *__restrict__ vals, uint32_t *__restrict__ indeg) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n * (uint32_t)AP_DEGREE) return;
+    const uint32_t bid = i / AP_DEGREE, s = i % AP_DEGREE, t = new_list[i];
+    keys[i] = ((unsigned long long)t << 37) | ((unsigned long long)bid << 5) | s;
+    vals[i] = detour[i];
+    atomicAdd(&indeg[t], 1u);
+}
+__global__ void seg_start_kernel(uint32_t total, const unsigned long long *__restrict__ keys, uint32_t *__restrict__ start) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const uint32_t t = (uint32_t)(keys[i] >> 37);
+    if (i == 0 || (uint32_t)(keys[i - 1] >> 37) != t) start[t] = i;
+}
+
+// the reference's bitonic network on up to 32 (key, value) pairs in thread-local arrays
+__device__ __forceinline__ void local_bitonic_kv(uint32_t *key, uint32_t *val, uint32_t len) {
+    for (uint32_t stride = 1; stride < len; stride <<= 1)
+        for (uint32_t step = stride; step > 0; step >>= 1)
+            for (uint32_t k = 0; k < len / 2; ++k) {
+                const uint32_t aa = 2 * step * (k / step), bb = k % step;
+                const uint32_t u = (step == stride) ? (aa + step - 1 - bb) : (aa + bb), d = aa + bb + step;
+                if (d < len && key[u] > key[d]) {
+                    uint32_t t = key[u]; key[u] = key[d]; key[d] = t;
+                    t = val[u]; val[u] = val[d]; val[d] = t;
+                }
+            }
+}
+
+__global__ void final_rows_kernel(uint32_t n, const uint32_t *__restrict__ new_list, const uint32_t *__restrict__ kw_edge,
+                                  const unsigned long long *__restrict__ keys, const uint32_t *__restrict__ vals,
+                                  const uint32_t *__restrict__ start, const uint32_t *__restrict__ indeg,
+                                  uint32_t *__restrict__ graph) {
+    const uint32_t bid = blockIdx.x * blockDim.x + threadIdx.x;
+    if (bid >= n) return;
+    constexpr uint32_t d = AP_DEGREE;
+    uint32_t rid[d], rdt[d];
+    const uint32_t deg = indeg[bid], s0 = deg ? start[bid] : 0;
+    for (uint32_t k = 0; k < deg; ++k) {
+        const uint32_t src = (uint32_t)(keys[s0 + k] >> 5) & 0xFFFFFFFFu, dt = vals[s0 + k], slot = k % d;
+        if (k < d || rdt[slot] > dt) { rid[slot] = src; rdt[slot] = dt; }
+    }
+    const uint32_t rv = min(deg, d);
+    const uint32_t *nl = new_list + (size_t)bid * d;
+    uint32_t *row = graph + (size_t)bid * AP_ROW;
+    for (uint32_t i = 0; i < AP_ROW; ++i) row[i] = 0;
+    local_bitonic_kv(rid, rdt, rv);  // by id
+    uint32_t key2[d];
+    for (uint32_t i = 0; i < rv; ++i) key2[i] = (i > 0 && rid[i] == rid[i - 1]) ? kEmpty : rdt[i];
+    for (uint32_t i = 0; i < d / 2; ++i) row[i] = nl[i];
+    local_bitonic_kv(key2, rid, rv);  // by detour count, repeated ids last
+    uint32_t cur = 0;
+    const uint32_t lim = rv < d / 2 ? d - rv : d / 2;
+    for (uint32_t i = 0; i < rv; ++i) {
+        bool found = false;
+        for (uint32_t j = 0; j < lim; ++j) if (rid[i] == nl[j]) { found = true; break; }
+        if (!found) { const uint32_t t = cur++; if (t < d / 2) row[d / 2 + t] = rid[i]; }
+    }
+    const uint32_t placed = min(cur, d / 2);
+    for (uint32_t i = 0; i < d / 2 - placed; ++i) row[d / 2 + placed + i] = nl[i + d / 2];
+    const uint32_t *ke = kw_edge + (size_t)bid * 33;
+    cur = 0;
+    for (uint32_t i = 0; i < ke[0]; ++i) {
+        bool found = false;
+        for (uint32_t j = d / 2; j < d; ++j) if (row[j] == ke[1 + i]) { found = true; break; }
+        if (!found) { const uint32_t t = cur++; if (t < 7) row[d + t + 1] = ke[1 + i]; }
+    }
+    row[d] = min(cur, 7u);
+}
+
+__global__ void ep_keys_kernel(uint32_t n, const float *__restrict__ power, unsigned long long *__restrict__ keys) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) keys[i] = ((unsigned long long)f2ord(power[i]) << 32) | i;
+}
+__global__ void ep_take_kernel(uint32_t n, const unsigned long long *__restrict__ keys, uint32_t *__restrict__ ep) {
+    const uint32_t i = threadIdx.x;
+    if (i < AP_ENTRY_POINTS) ep[i] = (uint32_t)keys[i < n ? i : n - 1];
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// host drivers
+// ---------------------------------------------------------------------------------------------------------
+static uint32_t pow2_at_least(uint32_t v, uint32_t lo) { uint32_t p = lo; while (p < v) p <<= 1; return p; }
+static uint32_t log2u(uint32_t p) { uint32_t l = 0; while ((1u << l) < p) ++l; return l; }
+
+struct DevBuf {
+    std::vector<void *> ptrs;
+    ~DevBuf() { for (void *p : ptrs) cudaFree(p); }
+    template <class T> int alloc(T **out, size_t count) {
+        void *p = nullptr;
+        cudaError_t e = cudaMalloc(&p, std::max<size_t>(count * sizeof(T), 16));
+        if (e != cudaSuccess) return fail(AP_ERR_CUDA, "cudaMalloc of %zu bytes failed: %s", count * sizeof(T), cudaGetErrorString(e));
+        ptrs.push_back(p); *out = (T *)p; return AP_OK;
+    }
+};
+
+static int sort_u64_pairs(DevBuf &db, unsigned long long *keys, uint32_t *vals, size_t count, int end_bit,
+                          unsigned long long **keys_out, uint32_t **vals_out) {
+    unsigned long long *k2; uint32_t *v2 = nullptr;
+    AP_TRY(db.alloc(&k2, count));
+    if (vals) AP_TRY(db.alloc(&v2, count));
+    size_t tmp_bytes = 0;
+    if (vals) AP_CUDA(cub::DeviceRadixSort::SortPairs(nullptr, tmp_bytes, keys, k2, vals, v2, (int)count, 0, end_bit));
+    else AP_CUDA(cub::DeviceRadixSort::SortKeys(nullptr, tmp_bytes, keys, k2, (int)count, 0, end_bit));
+    uint8_t *tmp; AP_TRY(db.alloc(&tmp, tmp_bytes));
+    if (vals) AP_CUDA(cub::DeviceRadixSort::SortPairs(tmp, tmp_bytes, keys, k2, vals, v2, (int)count, 0, end_bit));
+    else AP_CUDA(cub::DeviceRadixSort::SortKeys(tmp, tmp_bytes, keys, k2, (int)count, 0, end_bit));
+    *keys_out = k2; if (vals_out) *vals_out = v2;
+    return AP_OK;
+}
+
+int norms_run(ap_index *ix, float *d_power) {
+    if (!ix->rec_build) return fail(AP_ERR_STATE, "the index was created without AP_CREATE_FOR_BUILD");
+    norms_kernel<<<(ix->n + 7) / 8, 256>>>(ix->n, ix->meta, ix->rec_build, d_power);
+    AP_CUDA(cudaGetLastError());
+    return AP_OK;
+}
+
+// prune + reverse edges + final rows + entry points, on device k-NN lists; installs the graph.
+int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const float *d_power, uint32_t *d_new_list,
+              uint32_t *d_kw, uint32_t *launches) {
+    const uint32_t n = ix->n;
+    if (n >= (1u << 27)) return fail(AP_ERR_LIMIT, "pruning supports up to 2^27 documents per index");
+    DevBuf db;
+    uint32_t *detour, *nl = d_new_list, *kw = d_kw;
+    AP_TRY(db.alloc(&detour, (size_t)n * AP_DEGREE));
+    if (!nl) AP_TRY(db.alloc(&nl, (size_t)n * AP_DEGREE));
+    if (!kw) AP_TRY(db.alloc(&kw, (size_t)n * 33));
+    PruneArgs a{};
+    a.n = n; a.knn = d_knn; a.knn_dis = d_knn_dis; a.power = d_power; a.meta = ix->meta; a.rec = ix->rec_build;
+    a.new_list = nl; a.detour = detour; a.kw_edge = kw; a.unfused = 0;
+    const uint32_t tabn = pow2_at_least(2 * (ix->max_ns + ix->max_nb), 64), ownn = pow2_at_least(2 * ix->max_nb, 64);
+    a.tab_mask = tabn - 1; a.tab_shift = 32 - log2u(tabn); a.own_mask = ownn - 1; a.own_shift = 32 - log2u(ownn);
+    a.o_tab = 0; a.o_own = 8 * tabn; a.o_lists = a.o_own + 4 * ownn;
+    const size_t smem = a.o_lists + (size_t)kK * kK * 8;
+    if (smem > ix->smem_per_block) return fail(AP_ERR_LIMIT, "pruning needs %zu bytes of shared memory per block", smem);
+    AP_CUDA(cudaFuncSetAttribute(prune_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    prune_kernel<<<n, kPruneThreads, smem>>>(a);
+    AP_CUDA(cudaGetLastError());
+
+    const size_t total = (size_t)n * AP_DEGREE;
+    unsigned long long *keys, *keys_s; uint32_t *vals, *vals_s, *indeg, *start;
+    AP_TRY(db.alloc(&keys, total)); AP_TRY(db.alloc(&vals, total));
+    AP_TRY(db.alloc(&indeg, n)); AP_TRY(db.alloc(&start, n));
+    AP_CUDA(cudaMemsetAsync(indeg, 0, (size_t)n * 4));
+    AP_CUDA(cudaMemsetAsync(start, 0, (size_t)n * 4));
+    rev_keys_kernel<<<(uint32_t)((total + 255) / 256), 256>>>(n, nl, detour, keys, vals, indeg);
+    AP_TRY(sort_u64_pairs(db, keys, vals, total, 64, &keys_s, &vals_s));
+    seg_start_kernel<<<(uint32_t)((total + 255) / 256), 256>>>((uint32_t)total, keys_s, start);
+    if (!ix->graph) AP_CUDA(cudaMalloc(&ix->graph, (size_t)n * AP_ROW * 4));
+    if (!ix->ep) AP_CUDA(cudaMalloc(&ix->ep, AP_ENTRY_POINTS * 4));
+    final_rows_kernel<<<(n + 127) / 128, 128>>>(n, nl, kw, keys_s, vals_s, start, indeg, ix->graph);
+    // entry points: the 32 smallest norms, ties by id (ref src/index.cu:916-925)
+    unsigned long long *ek, *ek_s;
+    AP_TRY(db.alloc(&ek, n));
+    ep_keys_kernel<<<(n + 255) / 256, 256>>>(n, d_power, ek);
+    AP_TRY(sort_u64_pairs(db, ek, nullptr, n, 64, &ek_s, nullptr));
+    ep_take_kernel<<<1, 32>>>(n, ek_s, ix->ep);
+    AP_CUDA(cudaGetLastError());
+    AP_CUDA(cudaDeviceSynchronize());
+    if (launches) *launches += 8;
+    return index_install_graph(ix);
+}
+
+int join_dense_tc_launch(ap_index *ix, uint32_t node0, uint32_t nodes, const uint32_t *plist, const uint32_t *pcnt, float *D,
+                         cudaStream_t stream);  // apoe_join_tc.cu
+
+int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats) {
+    ap_build_opts o{};
+    if (opts_in) o = *opts_in;
+    const uint32_t iters = o.iterations ? o.iterations : 12;
+    const float scale = o.dense_scale != 0.f ? o.dense_scale : 7.0f;
+    const uint32_t n = ix->n;
+    if (n < 2) return fail(AP_ERR_ARG, "a graph needs at least 2 documents");
+    AP_CUDA(cudaSetDevice(ix->device));
+    AP_TRY(ensure_build_copy(ix, scale));
+    const auto t0 = std::chrono::high_resolution_clock::now();
+    DevBuf db;
+    Knn k{};
+    k.n = n;
+    AP_TRY(db.alloc(&k.ids, (size_t)n * kK)); AP_TRY(db.alloc(&k.dis, (size_t)n * kK));
+    AP_TRY(db.alloc(&k.samp, (size_t)n * 64)); AP_TRY(db.alloc(&k.scnt, (size_t)n * 4));
+    AP_TRY(db.alloc(&k.plist, (size_t)n * kPart)); AP_TRY(db.alloc(&k.pcnt, (size_t)n * 2));
+    AP_TRY(db.alloc(&k.prop, (size_t)n * kPropCap)); AP_TRY(db.alloc(&k.propn, n));
+    AP_TRY(db.alloc(&k.stats, 4));
+    AP_CUDA(cudaMemset(k.stats, 0, 32));
+    float *power = ix->power;
+    if (!power) { AP_CUDA(cudaMalloc(&ix->power, (size_t)n * 4)); power = ix->power; }
+    uint32_t launches = 0;
+    AP_TRY(norms_run(ix, power)); ++launches;
+    knn_init_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k, o.seed ? o.seed : 20261125u); ++launches;
+
+    // scratch for the dense tiles, in batches of nodes
+    const uint32_t batch = std::min<uint32_t>(n, 1u << 18);
+    float *D;
+    AP_TRY(db.alloc(&D, (size_t)batch * kPart * kNewMax));
+    uint32_t *err = ix->d_ctl + 1;
+
+    JoinArgs ja{};
+    ja.plist = k.plist; ja.pcnt = k.pcnt; ja.meta = ix->meta; ja.rec = ix->rec_build; ja.D = D; ja.knn_dis = k.dis;
+    ja.prop = k.prop; ja.propn = k.propn; ja.stats = k.stats; ja.err = err;
+    const uint32_t tabn = pow2_at_least(2 * (ix->max_ns + ix->max_nb), 64);
+    ja.tab_mask = tabn - 1; ja.tab_shift = 32 - log2u(tabn);
+    // two CTAs per SM: tables for up to 4 hashed rows, the 32 x 64 distance tile, the rest is arena
+    const size_t per_cta = ix->smem_per_sm / 2 - 1024 - 2048 /* static */;
+    ja.groups = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (per_cta / 4) / (8 * (size_t)tabn)));
+    ja.o_tab = 0; ja.o_dm = 8 * tabn * ja.groups; ja.o_arena = (ja.o_dm + 4 * kNewMax * kPart + 127) / 128 * 128;
+    if (per_cta <= ja.o_arena + 8u * (pad2(ix->max_ns) + pad2(ix->max_nb)) * 2)
+        return fail(AP_ERR_LIMIT, "rows of %u + %u terms leave no room for a local join in shared memory", ix->max_ns, ix->max_nb);
+    ja.arena_bytes = (uint32_t)std::min<size_t>((per_cta - ja.o_arena) / 128 * 128, 512u * 1024u);
+    const size_t join_smem = ja.o_arena + ja.arena_bytes;
+    AP_CUDA(cudaFuncSetAttribute(join_sparse_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)join_smem));
+    const size_t simt_smem = (size_t)kNewMax * kDenseBytes;
+    AP_CUDA(cudaFuncSetAttribute(join_dense_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)simt_smem));
+
+    const uint32_t wblocks = (n + 7) / 8;  // warp-per-node kernels, 256 threads
+    uint32_t it = 0;
+    unsigned long long prev_updates = 0;
+    for (; it < iters; ++it) {
+        AP_CUDA(cudaMemsetAsync(k.scnt, 0, (size_t)n * 16));
+        AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
+        knn_sample_kernel<<<wblocks, 256>>>(k, it);
+        knn_plist_kernel<<<wblocks, 256>>>(k);
+        launches += 2;
+        for (uint32_t node0 = 0; node0 < n; node0 += batch) {
+            const uint32_t nodes = std::min(batch, n - node0);
+            if (o.flags & AP_BUILD_SIMT_JOIN) join_dense_simt_kernel<<<nodes, 256, simt_smem>>>(node0, nodes, k.plist, k.pcnt, ix->meta, ix->rec_build, D);
+            else AP_TRY(join_dense_tc_launch(ix, node0, nodes, k.plist, k.pcnt, D, 0));
+            ja.node0 = node0; ja.nodes = nodes;
+            join_sparse_kernel<<<nodes, kJoinThreads, join_smem>>>(ja);
+            launches += 2;
+        }
+        knn_merge_kernel<<<(n + 3) / 4, 128>>>(k); ++launches;
+        AP_CUDA(cudaGetLastError());
+        unsigned long long st[4];
+        AP_CUDA(cudaMemcpy(st, k.stats, 32, cudaMemcpyDeviceToHost));
+        const unsigned long long upd = st[1] - prev_updates;
+        prev_updates = st[1];
+        if (it >= 3 && upd < (unsigned long long)n * kK / 1000) { ++it; break; }  // < 0.1 % of the entries changed
+    }
+    AP_CUDA(cudaDeviceSynchronize());
+    const auto t1 = std::chrono::high_resolution_clock::now();
+
+    uint32_t *knn_ids = ix->knn_ids;
+    if (!knn_ids) { AP_CUDA(cudaMalloc(&ix->knn_ids, (size_t)n * kK * 4)); knn_ids = ix->knn_ids; }
+    if (!ix->knn_dis) AP_CUDA(cudaMalloc(&ix->knn_dis, (size_t)n * kK * 4));
+    knn_finish_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k, knn_ids); ++launches;
+    AP_CUDA(cudaMemcpyAsync(ix->knn_dis, k.dis, (size_t)n * kK * 4, cudaMemcpyDeviceToDevice));
+    AP_TRY(prune_run(ix, knn_ids, ix->knn_dis, power, nullptr, nullptr, &launches));
+    const auto t2 = std::chrono::high_resolution_clock::now();
+
+    uint32_t ew = 0;
+    AP_CUDA(cudaMemcpy(&ew, err, 4, cudaMemcpyDeviceToHost));
+    if (ew) { cudaMemset(err, 0, 4); return fail(AP_ERR_DEVICE, "a build kernel raised error word %u (a bounded wait ran out)", ew); }
+    if (stats) {
+        unsigned long long st[4];
+        AP_CUDA(cudaMemcpy(st, k.stats, 32, cudaMemcpyDeviceToHost));
+        stats->seconds_knn = std::chrono::duration<double>(t1 - t0).count();
+        stats->seconds_prune = std::chrono::duration<double>(t2 - t1).count();
+        stats->seconds_total = std::chrono::duration<double>(t2 - t0).count();
+        stats->distance_evals = st[0]; stats->list_updates = st[1]; stats->iterations_run = it; stats->launches = launches;
+        stats->reserved[0] = (uint32_t)st[2];
+    }
+    if (!(o.flags & AP_BUILD_KEEP_KNN)) {
+        cudaFree(ix->knn_ids); cudaFree(ix->knn_dis); ix->knn_ids = nullptr; ix->knn_dis = nullptr;
+    }
+    // the build-time copy is no longer needed once the graph exists
+    if (!(o.flags & AP_BUILD_KEEP_KNN)) { cudaFree(ix->rec_build); ix->rec_build = nullptr; ix->build_scale = 0.f; ix->dense_src = nullptr; }
+    return AP_OK;
+}
+
+}  // namespace apoe
+
+using namespace apoe;
+
+extern "C" {
+
+int ap_index_build(ap_index *ix, const ap_build_opts *opts, ap_build_stats *stats) {
+    if (!ix) return fail(AP_ERR_ARG, "null index");
+    return build_run(ix, opts, stats);
+}
+
+int ap_index_get_knn(const ap_index *ix, uint32_t *ids, float *dis, float *power) {
+    if (!ix) return fail(AP_ERR_ARG, "null index");
+    if (!ix->knn_ids || !ix->knn_dis || !ix->power) return fail(AP_ERR_STATE, "no k-NN lists kept: build with AP_BUILD_KEEP_KNN");
+    AP_CUDA(cudaSetDevice(ix->device));
+    if (ids) AP_CUDA(cudaMemcpy(ids, ix->knn_ids, (size_t)ix->n * kK * 4, cudaMemcpyDeviceToHost));
+    if (dis) AP_CUDA(cudaMemcpy(dis, ix->knn_dis, (size_t)ix->n * kK * 4, cudaMemcpyDeviceToHost));
+    if (power) AP_CUDA(cudaMemcpy(power, ix->power, (size_t)ix->n * 4, cudaMemcpyDeviceToHost));
+    return AP_OK;
+}
+
+int ap_index_norms(ap_index *ix, float *out) {
+    if (!ix || !out) return fail(AP_ERR_ARG, "null argument");
+    AP_CUDA(cudaSetDevice(ix->device));
+    AP_TRY(ensure_build_copy(ix, ix->build_scale != 0.f ? ix->build_scale : 7.0f));
+    if (!ix->power) AP_CUDA(cudaMalloc(&ix->power, (size_t)ix->n * 4));
+    AP_TRY(norms_run(ix, ix->power));
+    AP_CUDA(cudaMemcpy(out, ix->power, (size_t)ix->n * 4, cudaMemcpyDeviceToHost));
+    return AP_OK;
+}
+
+int ap_index_prune(ap_index *ix, const uint32_t *knn_ids, const float *knn_dis, const float *power, uint32_t *new_list,
+                   uint32_t *keyword_edges, uint32_t *rows) {
+    if (!ix || !knn_ids || !knn_dis || !power) return fail(AP_ERR_ARG, "null argument");
+    const uint32_t n = ix->n;
+    for (size_t i = 0; i < (size_t)n * kK; ++i)
+        if (knn_ids[i] >= n) return fail(AP_ERR_ARG, "k-NN entry %zu = %u is not a document id", i, knn_ids[i]);
+    AP_CUDA(cudaSetDevice(ix->device));
+    if (!ix->rec_build) return fail(AP_ERR_STATE, "the index was created without AP_CREATE_FOR_BUILD");
+    DevBuf db;
+    uint32_t *d_knn, *d_nl, *d_kw; float *d_dis, *d_pow;
+    AP_TRY(db.alloc(&d_knn, (size_t)n * kK)); AP_TRY(db.alloc(&d_dis, (size_t)n * kK)); AP_TRY(db.alloc(&d_pow, n));
+    AP_TRY(db.alloc(&d_nl, (size_t)n * AP_DEGREE)); AP_TRY(db.alloc(&d_kw, (size_t)n * 33));
+    AP_CUDA(cudaMemcpy(d_knn, knn_ids, (size_t)n * kK * 4, cudaMemcpyHostToDevice));
+    AP_CUDA(cudaMemcpy(d_dis, knn_dis, (size_t)n * kK * 4, cudaMemcpyHostToDevice));
+    AP_CUDA(cudaMemcpy(d_pow, power, (size_t)n * 4, cudaMemcpyHostToDevice));
+    uint32_t launches = 0;
+    AP_TRY(prune_run(ix, d_knn, d_dis, d_pow, d_nl, d_kw, &launches));
+    if (new_list) AP_CUDA(cudaMemcpy(new_list, d_nl, (size_t)n * AP_DEGREE * 4, cudaMemcpyDeviceToHost));
+    if (keyword_edges) AP_CUDA(cudaMemcpy(keyword_edges, d_kw, (size_t)n * 33 * 4, cudaMemcpyDeviceToHost));
+    if (rows) AP_CUDA(cudaMemcpy(rows, ix->graph, (size_t)n * AP_ROW * 4, cudaMemcpyDeviceToHost));
+    return AP_OK;
+}
+
+// Test hook: dense join tiles of the given participant lists, by the tensor-core kernel (use_tc != 0) or the
+// CUDA-core kernel.  plist: nodes x 64 ids, pcnt: nodes x 2 (new rows, rows), both host; out: nodes x 64 x 32 floats
+// (entries outside the lists' extents are left at zero).
+int ap_debug_join_dense(ap_index *ix, uint32_t nodes, const uint32_t *plist, const uint32_t *pcnt, int use_tc, float *out) {
+    if (!ix || !plist || !pcnt || !out || nodes == 0) return fail(AP_ERR_ARG, "null argument");
+    if (!ix->rec_build) return fail(AP_ERR_STATE, "the index was created without AP_CREATE_FOR_BUILD");
+    for (uint32_t v = 0; v < nodes; ++v) {
+        const uint32_t nn = pcnt[2 * v], rows = pcnt[2 * v + 1];
+        if (nn > (uint32_t)kNewMax || rows > (uint32_t)kPart || nn > rows || rows - nn > 32) return fail(AP_ERR_ARG, "bad extents for node %u", v);
+        for (uint32_t j = 0; j < rows; ++j) if (plist[(size_t)v * kPart + j] >= ix->n) return fail(AP_ERR_ARG, "participant out of range");
+    }
+    AP_CUDA(cudaSetDevice(ix->device));
+    DevBuf db;
+    uint32_t *d_pl, *d_pc; float *d_D;
+    AP_TRY(db.alloc(&d_pl, (size_t)nodes * kPart)); AP_TRY(db.alloc(&d_pc, (size_t)nodes * 2));
+    AP_TRY(db.alloc(&d_D, (size_t)nodes * kPart * kNewMax));
+    AP_CUDA(cudaMemcpy(d_pl, plist, (size_t)nodes * kPart * 4, cudaMemcpyHostToDevice));
+    AP_CUDA(cudaMemcpy(d_pc, pcnt, (size_t)nodes * 8, cudaMemcpyHostToDevice));
+    AP_CUDA(cudaMemset(d_D, 0, (size_t)nodes * kPart * kNewMax * 4));
+    // the kernels index plist / pcnt by absolute node id: node0 = 0 here
+    if (use_tc) AP_TRY(join_dense_tc_launch(ix, 0, nodes, d_pl, d_pc, d_D, 0));
+    else {
+        const size_t simt_smem = (size_t)kNewMax * kDenseBytes;
+        AP_CUDA(cudaFuncSetAttribute(join_dense_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)simt_smem));
+        join_dense_simt_kernel<<<nodes, 256, simt_smem>>>(0, nodes, d_pl, d_pc, ix->meta, ix->rec_build, d_D);
+    }
+    AP_CUDA(cudaGetLastError());
+    AP_CUDA(cudaDeviceSynchronize());
+    uint32_t ew = 0;
+    AP_CUDA(cudaMemcpy(&ew, ix->d_ctl + 1, 4, cudaMemcpyDeviceToHost));
+    if (ew) { cudaMemset(ix->d_ctl + 1, 0, 4); return fail(AP_ERR_DEVICE, "join kernel raised error word %u (a bounded wait ran out)", ew); }
+    AP_CUDA(cudaMemcpy(out, d_D, (size_t)nodes * kPart * kNewMax * 4, cudaMemcpyDeviceToHost));
+    return AP_OK;
+}
+
+}  // extern "C"

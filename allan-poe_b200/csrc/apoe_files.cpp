@@ -1,0 +1,306 @@
+// File-level drop-ins: the loaders and writers of the reference's on-disk formats and the two calls behind
+// hybrid_search.build_index / hybrid_search.search_index, implemented over the resident-index C ABI.
+#include <algorithm>
+#include <chrono>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <iostream>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../include/allan_poe.h"
+
+namespace apoe {
+int fail(int code, const char *fmt, ...);
+}
+using apoe::fail;
+
+namespace {
+
+struct CsrHost {
+    std::vector<uint32_t> off, idx;
+    std::vector<float> val;
+    ap_csr view() const { return ap_csr{off.data(), idx.data(), val.data()}; }
+};
+
+bool file_size(const char *path, size_t *out) {
+    std::ifstream in(path, std::ios::binary | std::ios::ate);
+    if (!in.is_open()) return false;
+    *out = (size_t)in.tellg();
+    return true;
+}
+
+// ref: load_data, include/utils.cuh:361-378 -- int32 dim, then per row (int32 dim, dim floats)
+int load_fvecs(const char *path, std::vector<float> &data, uint32_t *num) {
+    size_t fsize;
+    if (!file_size(path, &fsize)) return fail(AP_ERR_IO, "cannot open %s", path);
+    std::ifstream in(path, std::ios::binary);
+    uint32_t dim = 0;
+    in.read((char *)&dim, 4);
+    if (!in || dim != AP_DIM) return fail(AP_ERR_IO, "%s: dimension %u, this index is built for %d", path, dim, AP_DIM);
+    const size_t n = fsize / ((size_t)(dim + 1) * 4);
+    if (n == 0 || n > 0x7FFFFFFFull) return fail(AP_ERR_IO, "%s: %zu rows", path, n);
+    data.resize(n * dim);
+    in.seekg(0, std::ios::beg);
+    std::vector<float> rowbuf((size_t)(dim + 1) * 1024);
+    for (size_t r0 = 0; r0 < n; r0 += 1024) {
+        const size_t rows = std::min<size_t>(1024, n - r0);
+        in.read((char *)rowbuf.data(), rows * (dim + 1) * 4);
+        if (!in) return fail(AP_ERR_IO, "%s: truncated at row %zu", path, r0);
+        for (size_t r = 0; r < rows; ++r) memcpy(&data[(r0 + r) * dim], &rowbuf[r * (dim + 1) + 1], (size_t)dim * 4);
+    }
+    *num = (uint32_t)n;
+    return AP_OK;
+}
+
+// ref: load_sparse_data, include/utils.cuh:380-398 -- u32 nnz | u32 off[rows+1] | u32 idx[nnz] | f32 val[nnz]
+int load_csr(const char *path, uint32_t rows, CsrHost &c) {
+    size_t fsize;
+    if (!file_size(path, &fsize)) return fail(AP_ERR_IO, "cannot open %s", path);
+    std::ifstream in(path, std::ios::binary);
+    uint32_t nnz = 0;
+    in.read((char *)&nnz, 4);
+    const size_t need = 4 + (size_t)(rows + 1) * 4 + (size_t)nnz * 8;
+    if (!in || fsize < need) return fail(AP_ERR_IO, "%s: %zu bytes, %zu needed for %u rows and %u entries", path, fsize, need, rows, nnz);
+    c.off.resize(rows + 1); c.idx.resize(nnz); c.val.resize(nnz);
+    in.read((char *)c.off.data(), (size_t)(rows + 1) * 4);
+    in.read((char *)c.idx.data(), (size_t)nnz * 4);
+    in.read((char *)c.val.data(), (size_t)nnz * 4);
+    if (!in) return fail(AP_ERR_IO, "%s: truncated", path);
+    if (c.off[rows] != nnz) return fail(AP_ERR_IO, "%s: last offset %u differs from the entry count %u", path, c.off[rows], nnz);
+    std::cout << "Non zero num: " << nnz << std::endl;
+    return AP_OK;
+}
+
+// ref: load_kg_graph, src/query.cu:89-108 -- u32 n_off | u32 nnz | u32 off[n_off] | u32 idx[nnz]
+int load_kg(const char *path, std::vector<uint32_t> &off, std::vector<uint32_t> &idx) {
+    size_t fsize;
+    if (!file_size(path, &fsize)) return fail(AP_ERR_IO, "cannot open %s", path);
+    std::ifstream in(path, std::ios::binary);
+    uint32_t n_off = 0, nnz = 0;
+    in.read((char *)&n_off, 4); in.read((char *)&nnz, 4);
+    if (!in || n_off == 0 || fsize < 8 + (size_t)n_off * 4 + (size_t)nnz * 4) return fail(AP_ERR_IO, "%s: malformed CSR header", path);
+    off.resize(n_off); idx.resize(nnz);
+    in.read((char *)off.data(), (size_t)n_off * 4);
+    in.read((char *)idx.data(), (size_t)nnz * 4);
+    if (!in) return fail(AP_ERR_IO, "%s: truncated", path);
+    std::cout << "Entity num: " << n_off << ", Non zero num: " << nnz << std::endl;
+    return AP_OK;
+}
+
+// ref: load_txt, src/query.cu:65-86 -- one line of unsigned ids per query
+int load_id_lines(const char *path, uint32_t rows, std::vector<std::vector<uint32_t>> &out) {
+    std::ifstream in(path);
+    if (!in.is_open()) return fail(AP_ERR_IO, "cannot open %s", path);
+    out.assign(rows, {});
+    std::string line;
+    uint32_t r = 0;
+    while (r < rows && std::getline(in, line)) {
+        std::istringstream iss(line);
+        uint32_t v;
+        while (iss >> v) out[r].push_back(v);
+        ++r;
+    }
+    return AP_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+// ref: cal_precision, src/query.cu:111-145
+double ap_ndcg(uint32_t nq, const uint32_t *results, uint32_t stride, uint32_t top_k, const uint32_t *qrel_off,
+               const uint32_t *qrel_ids) {
+    double total = 0.0;
+    for (uint32_t q = 0; q < nq; ++q) {
+        const uint32_t *rel = qrel_ids + qrel_off[q];
+        const uint32_t nrel = qrel_off[q + 1] - qrel_off[q];
+        float idcg = 0.f;
+        for (uint32_t j = 0; j < nrel; ++j) idcg += 1.f / std::log2((float)(j + 2));
+        float dcg = 0.f;
+        std::vector<uint32_t> a(results + (size_t)q * stride, results + (size_t)q * stride + top_k), b(rel, rel + nrel), common;
+        std::sort(a.begin(), a.end()); std::sort(b.begin(), b.end());
+        std::set_intersection(a.begin(), a.end(), b.begin(), b.end(), std::back_inserter(common));
+        for (uint32_t x : common)
+            for (uint32_t it = 0; it < top_k; ++it)
+                if (results[(size_t)q * stride + it] == x) { dcg += 1.f / std::log2((float)(it + 2)); break; }
+        if (nrel) total += dcg / idcg;
+    }
+    return nq ? total / nq : 0.0;
+}
+
+int ap_index_load_graph(ap_index *ix, const char *path) {
+    if (!ix || !path) return fail(AP_ERR_ARG, "null argument");
+    size_t fsize;
+    if (!file_size(path, &fsize)) return fail(AP_ERR_IO, "cannot open %s", path);
+    std::ifstream in(path, std::ios::binary);
+    uint32_t k = 0, n_ep = 0;
+    in.read((char *)&k, 4); in.read((char *)&n_ep, 4);
+    if (!in || k != AP_ROW || n_ep != AP_ENTRY_POINTS) return fail(AP_ERR_IO, "%s: row width %u / %u entry points, expected %d / %d", path, k, n_ep, AP_ROW, AP_ENTRY_POINTS);
+    const size_t num = (fsize - ((size_t)n_ep + 1) * 4) / ((size_t)k + 1) / 4;  // ref: src/query.cu:46
+    std::cout << "Degree: " << k << "," << "num: " << num << std::endl;
+    if (num != ap_index_size(ix)) return fail(AP_ERR_IO, "%s holds %zu rows, the corpus has %u documents", path, num, ap_index_size(ix));
+    std::vector<uint32_t> ep(n_ep), rows(num * k), buf((size_t)(k + 1) * 4096);
+    in.read((char *)ep.data(), (size_t)n_ep * 4);
+    for (size_t r0 = 0; r0 < num; r0 += 4096) {
+        const size_t cnt = std::min<size_t>(4096, num - r0);
+        in.read((char *)buf.data(), cnt * (k + 1) * 4);
+        if (!in) return fail(AP_ERR_IO, "%s: truncated at row %zu", path, r0);
+        for (size_t r = 0; r < cnt; ++r) memcpy(&rows[(r0 + r) * k], &buf[r * (k + 1) + 1], (size_t)k * 4);
+    }
+    return ap_index_set_graph(ix, rows.data(), ep.data());
+}
+
+// ref: the writer of src/index.cu:928-939 -- u32 40 | u32 32 | u32 ep[32] | n x (u32 40 | u32 row[40])
+int ap_index_save_graph(const ap_index *ix, const char *path) {
+    if (!ix || !path) return fail(AP_ERR_ARG, "null argument");
+    const uint32_t n = ap_index_size(ix);
+    std::vector<uint32_t> rows((size_t)n * AP_ROW), ep(AP_ENTRY_POINTS);
+    int rc = ap_index_get_graph(ix, rows.data(), ep.data());
+    if (rc != AP_OK) return rc;
+    std::ofstream out(path, std::ios::binary | std::ios::out);
+    if (!out.is_open()) return fail(AP_ERR_IO, "cannot create %s", path);
+    const uint32_t w = AP_ROW, ne = AP_ENTRY_POINTS;
+    out.write((const char *)&w, 4); out.write((const char *)&ne, 4);
+    out.write((const char *)ep.data(), (size_t)ne * 4);
+    std::vector<uint32_t> buf((size_t)(w + 1) * 4096);
+    for (size_t r0 = 0; r0 < n; r0 += 4096) {
+        const size_t cnt = std::min<size_t>(4096, n - r0);
+        for (size_t r = 0; r < cnt; ++r) { buf[r * (w + 1)] = w; memcpy(&buf[r * (w + 1) + 1], &rows[(r0 + r) * w], (size_t)w * 4); }
+        out.write((const char *)buf.data(), cnt * (w + 1) * 4);
+    }
+    out.close();
+    if (!out) return fail(AP_ERR_IO, "write to %s failed", path);
+    return AP_OK;
+}
+
+int ap_build_index(const char *dense_data_path, const char *sparse_data_path, const char *bm25_data_path,
+                   const char *output_graph_path, int device, const ap_build_opts *opts, ap_build_stats *stats) {
+    if (!dense_data_path || !sparse_data_path || !bm25_data_path || !output_graph_path) return fail(AP_ERR_ARG, "null path");
+    std::vector<float> dense; uint32_t n = 0;
+    CsrHost sp, bm;
+    std::cout << "Loading dense data from " << dense_data_path << std::endl;
+    int rc = load_fvecs(dense_data_path, dense, &n);
+    if (rc == AP_OK) rc = load_csr(sparse_data_path, n, sp);
+    if (rc == AP_OK) rc = load_csr(bm25_data_path, n, bm);
+    if (rc != AP_OK) return rc;
+    std::cout << "Points: " << n << ", Dim: " << AP_DIM << std::endl;
+    uint32_t ms = 0, mb = 0;
+    for (uint32_t i = 0; i < n; ++i) { ms = std::max(ms, sp.off[i + 1] - sp.off[i]); mb = std::max(mb, bm.off[i + 1] - bm.off[i]); }
+    std::cout << "Max sparse dim: " << ms << ", Max bm25 dim: " << mb << std::endl;
+    ap_index *ix = nullptr;
+    rc = ap_index_create_host(&ix, device, n, dense.data(), sp.view(), bm.view(), AP_CREATE_FOR_BUILD);
+    if (rc != AP_OK) return rc;
+    ap_build_stats st{};
+    rc = ap_index_build(ix, opts, &st);
+    if (rc == AP_OK) {
+        std::cout << "Indexing time: " << (float)st.seconds_total << "s" << std::endl;
+        rc = ap_index_save_graph(ix, output_graph_path);
+    }
+    if (stats) *stats = st;
+    ap_index_destroy(ix);
+    return rc;
+}
+
+int ap_search_index(const char *dense_data_path, const char *dense_query_path, const char *sparse_data_path,
+                    const char *sparse_query_path, const char *bm25_data_path, const char *bm25_query_path,
+                    const char *keyword_id_path, const char *knowledge_path, const char *entity2doc_path,
+                    const char *query_entity_path, const char *graph_path, const char *ground_truth_path, int top_k,
+                    int cands, float sparse_weight, float bm25_weight, float dense_weight, float kg_weight, int device,
+                    uint32_t max_queries, uint32_t *out_ids, float *out_dis, uint32_t *out_nq, double *out_ndcg,
+                    ap_search_stats *stats) {
+    if (!dense_data_path || !dense_query_path || !sparse_data_path || !sparse_query_path || !bm25_data_path ||
+        !bm25_query_path || !graph_path)
+        return fail(AP_ERR_ARG, "null path");
+    if (top_k <= 0 || top_k > cands) return fail(AP_ERR_ARG, "top_k = %d must lie in [1, cands = %d]", top_k, cands);
+    std::vector<float> dense, qdense;
+    uint32_t n = 0, nq_file = 0;
+    CsrHost sp, bm, qsp, qbm;
+    int rc = load_fvecs(dense_data_path, dense, &n);
+    if (rc == AP_OK) rc = load_fvecs(dense_query_path, qdense, &nq_file);
+    if (rc == AP_OK) rc = load_csr(sparse_data_path, n, sp);
+    if (rc == AP_OK) rc = load_csr(bm25_data_path, n, bm);
+    if (rc == AP_OK) rc = load_csr(sparse_query_path, nq_file, qsp);
+    if (rc == AP_OK) rc = load_csr(bm25_query_path, nq_file, qbm);
+    if (rc != AP_OK) return rc;
+    const bool use_kg = knowledge_path && knowledge_path[0];
+    const bool use_kw = keyword_id_path && keyword_id_path[0];
+    std::vector<uint32_t> e2e_off, e2e_idx, e2d_off, e2d_idx, qe_off, qe_idx;
+    if (use_kg) {
+        if (!entity2doc_path || !query_entity_path) return fail(AP_ERR_ARG, "knowledge_path set without entity2doc_path / query_entity_path");
+        rc = load_kg(knowledge_path, e2e_off, e2e_idx);
+        if (rc == AP_OK) rc = load_kg(entity2doc_path, e2d_off, e2d_idx);
+        if (rc == AP_OK) rc = load_kg(query_entity_path, qe_off, qe_idx);
+        if (rc != AP_OK) return rc;
+        if (e2e_off.size() != e2d_off.size()) return fail(AP_ERR_IO, "entity graph has %zu offsets, entity->doc map %zu", e2e_off.size(), e2d_off.size());
+    }
+    uint32_t nq = nq_file;
+    if (max_queries && max_queries < nq) nq = max_queries;
+    if (use_kg && qe_off.size() < (size_t)nq + 1) nq = (uint32_t)qe_off.size() - 1;
+    std::cout << "query num: " << nq << std::endl;
+    if (use_kw) {  // ref: src/query.cu:1828-1843
+        std::vector<std::vector<uint32_t>> kw;
+        rc = load_id_lines(keyword_id_path, nq, kw);
+        if (rc != AP_OK) return rc;
+        uint32_t cnt = 0;
+        for (uint32_t i = 0; i < nq; ++i)
+            for (uint32_t j = qbm.off[i]; j < qbm.off[i + 1]; ++j)
+                for (uint32_t t : kw[i])
+                    if (t == qbm.idx[j]) { qbm.idx[j] |= 0x80000000u; ++cnt; }
+        std::cout << "keywords: " << cnt << std::endl;
+    }
+    std::cout << "Dense weight: " << dense_weight << ", Sparse weight: " << sparse_weight << ", BM25 weight: " << bm25_weight
+              << ", KG weight: " << kg_weight << std::endl;
+    ap_index *ix = nullptr;
+    rc = ap_index_create_host(&ix, device, n, dense.data(), sp.view(), bm.view(), 0);
+    if (rc != AP_OK) return rc;
+    rc = ap_index_load_graph(ix, graph_path);
+    if (rc == AP_OK && use_kg) rc = ap_index_set_kg(ix, (uint32_t)e2e_off.size() - 1, e2e_off.data(), e2e_idx.data(), e2d_off.data(), e2d_idx.data());
+    std::vector<uint32_t> ids((size_t)nq * cands);
+    std::vector<float> dis((size_t)nq * cands);
+    ap_search_stats st{};
+    if (rc == AP_OK) {
+        std::cout << "Points: " << n << ", Dim: " << AP_DIM << std::endl;
+        std::cout << "Query: " << nq << ", Dim: " << AP_DIM << std::endl;
+        ap_queries q{};
+        q.nq = nq; q.dense = qdense.data(); q.sparse = qsp.view(); q.bm25 = qbm.view();
+        if (use_kg) { q.ent_off = qe_off.data(); q.ent_idx = qe_idx.data(); }
+        ap_search_opts o{};
+        o.cands = (uint32_t)cands; o.flags = use_kw ? AP_SEARCH_KEYWORD : 0;
+        o.sparse_weight = sparse_weight; o.bm25_weight = bm25_weight; o.dense_weight = dense_weight;
+        o.kg_weight = use_kg ? kg_weight : 0.f;
+        if (!use_kg && !(kg_weight < 1e-5f)) {  // the reference launches nothing in this case (src/query.cu:2042-2047)
+            rc = fail(AP_ERR_ARG, "kg_weight = %g without a knowledge graph", kg_weight);
+        } else {
+            std::cout << "Begin search" << std::endl;
+            const auto t0 = std::chrono::high_resolution_clock::now();
+            rc = ap_search_host(ix, &q, &o, ids.data(), dis.data(), &st);
+            const auto t1 = std::chrono::high_resolution_clock::now();
+            if (rc == AP_OK) std::cout << "Query time: " << std::chrono::duration<float>(t1 - t0).count() << "s" << std::endl;
+        }
+    }
+    if (rc == AP_OK) {
+        if (out_ids) memcpy(out_ids, ids.data(), ids.size() * 4);
+        if (out_dis) memcpy(out_dis, dis.data(), dis.size() * 4);
+        if (out_nq) *out_nq = nq;
+        if (stats) *stats = st;
+        if (ground_truth_path && ground_truth_path[0]) {
+            std::vector<std::vector<uint32_t>> rel;
+            rc = load_id_lines(ground_truth_path, nq, rel);
+            if (rc == AP_OK) {
+                std::vector<uint32_t> off(nq + 1, 0), flat;
+                for (uint32_t i = 0; i < nq; ++i) { flat.insert(flat.end(), rel[i].begin(), rel[i].end()); off[i + 1] = (uint32_t)flat.size(); }
+                const double v = ap_ndcg(nq, ids.data(), (uint32_t)cands, (uint32_t)top_k, off.data(), flat.data());
+                std::cout << "nDCG@10: " << v << std::endl;
+                if (out_ndcg) *out_ndcg = v;
+            }
+        }
+    }
+    ap_index_destroy(ix);
+    return rc;
+}
+
+}  // extern "C"

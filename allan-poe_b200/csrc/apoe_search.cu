@@ -1,0 +1,895 @@
+// Batched greedy beam search over the hybrid graph (one CTA per query, persistent grid).
+//
+// Behaviour follows the reference search kernels (src/query.cu:277-1268 for the seven weight subsets,
+// :1271-1483 keyword, :1541-1779 knowledge graph): same pool / staging arrays, the same visited-set reset every
+// 4th iteration, the same 32-element bitonic network and the same tie rules in the pool merge, and the same
+// dense arithmetic (fp16 multiply-adds in the reference's lane/chunk association), so the pool contents match
+// it element for element.  What differs is how the work is mapped to the machine:
+//   * every document is one contiguous, 16-byte aligned record (dense halves + interleaved sparse and BM25
+//     pairs); an expansion fetches the records of all unvisited neighbours with cp.async.bulk copies into a
+//     shared-memory arena, all in flight at once, completing on one mbarrier;
+//   * graph rows carry each neighbour's record locator, so an expansion is two dependent memory round trips
+//     (row, records) instead of four (row, CSR offsets, CSR rows / dense row);
+//   * the query's sparse and BM25 rows are hashed into shared memory and probed with the document's terms;
+//   * selection, visited filtering, the 32-wide sort and the copy planning run in one warp on registers and
+//     shuffles; only scoring and the pool merge use the whole CTA.
+#include <algorithm>
+#include <cstdio>
+
+#include "apoe_common.cuh"
+
+namespace apoe {
+
+constexpr int kSearchThreads = 128;
+constexpr int kSearchWarps = kSearchThreads / 32;
+constexpr uint32_t kFull = 0xFFFFFFFFu;
+constexpr int kMaxIter = 1000;    // ref: MAX_ITER, src/query.cu:7
+constexpr int kHashReset = 4;     // ref: HASH_RESET, src/query.cu:16
+constexpr int kKeywordRing = 32;  // ref: KEYWORD, src/query.cu:18
+constexpr int kMergeMax = (AP_MAX_CANDS + 32 + kSearchThreads - 1) / kSearchThreads;
+
+enum : int { PF_DENSE = 1, PF_SPARSE = 2, PF_BM25 = 4, PF_KEYWORD = 8, PF_KG = 16, PF_UNFUSED = 32 };
+enum : int { CTL_QUERY = 0, CTL_SEL = 1, CTL_BATCH = 2, CTL_LAST = 3, CTL_MERGE = 4, CTL_SLOT = 5, CTL_KWNUM = 6, CTL_M = 7 };
+
+struct SearchArgs {
+    const FatEdge *fat;
+    const FatEdge *ep_fat;
+    const uint8_t *rec;
+    const uint64_t *meta;
+    uint32_t n;
+    const float *qdense;
+    const uint32_t *qs_off, *qs_idx;
+    const float *qs_val;
+    const uint32_t *qb_off, *qb_idx;
+    const float *qb_val;
+    const uint32_t *e2e_off, *e2e_idx, *e2d_off, *e2d_idx, *qe_off, *qe_idx;
+    uint32_t nq;
+    float w_sparse, w_bm25, w_dense, kg_weight;
+    uint32_t cands;
+    uint32_t *out_ids;
+    float *out_dis;
+    uint32_t *ctl;            // [0] next query, [1] error word
+    unsigned long long *cnt;  // [0] expansions, [1] evaluations, [2] gathered bytes
+    uint32_t arena_bytes;
+    uint32_t vis_mask;           // visited table size - 1
+    uint32_t sq_mask, sq_shift;  // query sparse hash: size - 1, 32 - log2(size)
+    uint32_t bq_mask, bq_shift;
+    // shared-memory byte offsets
+    uint32_t o_pool_id, o_pool_dis, o_pool_ent, o_pool_hop, o_vis, o_info, o_sq, o_bq, o_kw, o_arena;
+};
+
+struct Ctx {  // per-thread view of the CTA's shared state
+    uint64_t *mbar;
+    volatile uint32_t *ctl;
+    uint32_t *pool_id;
+    float *pool_dis;
+    uint32_t *pool_ent, *pool_hop;
+    uint32_t *vis;
+    uint2 *info;
+    uint2 *sq, *bq;
+    uint32_t *kw_id;
+    float *kw_dis;
+    uint8_t *arena;
+    uint32_t phase;
+    unsigned long long c_exp, c_eval, c_bytes;
+    int tid, lane, warp;
+};
+
+// ---------------------------------------------------------------------------------------------------------
+// small device pieces
+// ---------------------------------------------------------------------------------------------------------
+// Visited set (ref: hash_insert, include/utils.cuh:282-297).  1 = newly inserted, 0 = already present / full.
+__device__ __forceinline__ uint32_t vis_insert(uint32_t *tab, uint32_t mask, uint32_t key) {
+    uint32_t idx = (key ^ (key >> 10)) & mask;
+    for (uint32_t i = 0; i <= mask; ++i) {
+        const uint32_t old = atomicCAS(&tab[idx], kEmpty, key);
+        if (old == kEmpty) return 1;
+        if (old == key) return 0;
+        idx = (idx + 1) & mask;
+    }
+    return 0;
+}
+
+__device__ __forceinline__ void qtab_insert(uint2 *tab, uint32_t mask, uint32_t shift, uint32_t rawkey, float val) {
+    const uint32_t t = rawkey & 0x7FFFFFFFu;
+    uint32_t h = (t * 2654435761u) >> shift;
+    for (uint32_t i = 0; i <= mask; ++i) {
+        const uint32_t old = atomicCAS(&tab[h].x, kEmpty, rawkey);
+        if (old == kEmpty) { tab[h].y = __float_as_uint(val); return; }
+        if ((old & 0x7FFFFFFFu) == t) return;  // duplicate term in a query row: the first one wins
+        h = (h + 1) & mask;
+    }
+}
+
+// Per-lane partial of <doc row, query row>: the lane walks the document's pairs j = lane, lane+32, ... in
+// ascending order and multiply-adds matches in fp32 (ref: cal_sparse_dist / cal_bm25_dist,
+// include/utils.cuh:299-340; the binary search of the reference is replaced by a hash probe, the set of
+// matches and their order are the same).
+__device__ __forceinline__ float sparse_partial(const uint2 *pairs, uint32_t nnz, const uint2 *tab, uint32_t mask,
+                                                uint32_t shift, int lane, uint32_t &key_hit) {
+    float acc = 0.0f;
+    for (uint32_t j = lane; j < nnz; j += 32) {
+        const uint2 p = pairs[j];
+        uint32_t h = (p.x * 2654435761u) >> shift;
+        for (uint32_t i = 0; i <= mask; ++i) {
+            const uint2 e = tab[h];
+            if (e.x == kEmpty) break;
+            if ((e.x & 0x7FFFFFFFu) == p.x) {
+                acc = __fmaf_rn(__uint_as_float(e.y), __uint_as_float(p.y), acc);
+                key_hit |= (e.x >> 31);
+                break;
+            }
+            h = (h + 1) & mask;
+        }
+    }
+    return acc;
+}
+
+// One fused distance, computed by a full warp from a record staged in shared memory.  Valid in lane 0.
+template <int F>
+__device__ __forceinline__ float score_record(const uint8_t *rec, uint32_t ns, uint32_t nb, const uint32_t (&qreg)[16],
+                                              const uint2 *sq, uint32_t sq_mask, uint32_t sq_shift, const uint2 *bq,
+                                              uint32_t bq_mask, uint32_t bq_shift, int lane, uint32_t &key_hit) {
+    constexpr bool D = (F & PF_DENSE) != 0, S = (F & PF_SPARSE) != 0, B = (F & PF_BM25) != 0, UNF = (F & PF_UNFUSED) != 0;
+    uint32_t acc = 0;
+    if (D) {
+        const uint2 *d = reinterpret_cast<const uint2 *>(rec);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            const uint2 v = d[lane + 32 * k];
+            if (UNF) {
+                acc = hadd2_rn(acc, hmul2_rn(qreg[2 * k], v.x));
+                acc = hadd2_rn(acc, hmul2_rn(qreg[2 * k + 1], v.y));
+            } else {
+                acc = hfma2_rn(qreg[2 * k], v.x, acc);
+                acc = hfma2_rn(qreg[2 * k + 1], v.y, acc);
+            }
+        }
+        rec += kDenseBytes;
+    }
+    float tot = 0.0f;
+    if (S) {
+        uint32_t dummy = 0;
+        tot = sparse_partial(reinterpret_cast<const uint2 *>(rec), ns, sq, sq_mask, sq_shift, lane, dummy);
+        rec += 8u * pad2(ns);
+    }
+    if (B) {
+        const float b = sparse_partial(reinterpret_cast<const uint2 *>(rec), nb, bq, bq_mask, bq_shift, lane, key_hit);
+        tot = S ? __fadd_rn(tot, b) : b;
+    }
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) {
+        if (D) acc = hadd2_rn(acc, __shfl_down_sync(kFull, acc, m));
+        if (S || B) tot = __fadd_rn(tot, __shfl_down_sync(kFull, tot, m));
+    }
+    // the reference writes `1.0 - dense - sparse` with a double literal: the subtraction chain runs in double
+    double r = 1.0;
+    if (D) r -= (double)half_sum_to_float(acc);
+    if (S || B) r -= (double)tot;
+    return (float)r;
+}
+
+// The reference's bitonic network on 32 elements held one per lane (include/utils.cuh:147-165 with len = 32):
+// the first step of each stage pairs p with its mirror inside the 2*step block, later steps pair p with
+// p ^ step; the lower position keeps the smaller key and equal keys never swap.
+template <bool EXTRA>
+__device__ __forceinline__ void warp_sort32(float &dis, uint32_t &id, uint32_t &e0, uint32_t &e1, int lane) {
+#pragma unroll
+    for (int stride = 1; stride < 32; stride <<= 1) {
+#pragma unroll
+        for (int step = stride; step > 0; step >>= 1) {
+            const int partner = (step == stride) ? (lane ^ (2 * step - 1)) : (lane ^ step);
+            const float od = __shfl_sync(kFull, dis, partner);
+            const uint32_t oi = __shfl_sync(kFull, id, partner);
+            uint32_t o0 = 0, o1 = 0;
+            if (EXTRA) { o0 = __shfl_sync(kFull, e0, partner); o1 = __shfl_sync(kFull, e1, partner); }
+            const bool lower = lane < partner;
+            const bool take = lower ? (dis > od) : (od > dis);
+            if (take) { dis = od; id = oi; if (EXTRA) { e0 = o0; e1 = o1; } }
+        }
+    }
+}
+
+__device__ __forceinline__ uint32_t count_le(const float *arr, uint32_t n, float v) {  // #{arr[i] <= v}, ascending arr
+    uint32_t lo = 0, hi = n;
+    while (lo < hi) { const uint32_t mid = (lo + hi) >> 1; if (arr[mid] <= v) lo = mid + 1; else hi = mid; }
+    return lo;
+}
+__device__ __forceinline__ uint32_t count_lt(const float *arr, uint32_t n, float v) {  // #{arr[i] < v}
+    uint32_t lo = 0, hi = n;
+    while (lo < hi) { const uint32_t mid = (lo + hi) >> 1; if (arr[mid] < v) lo = mid + 1; else hi = mid; }
+    return lo;
+}
+
+// Score the pool slots [base, base + 32) flagged by `need` (lane j of warp 0 owns slot base + j and that
+// document's locator word).  Warp 0 packs the needed records into the arena in as few batches as fit, issues one
+// bulk copy per record and arms the mbarrier with the batch's byte count; every warp then scores its share.
+// pool_dis[base + j] receives the distance; keyword hits set bit 30 of pool_id[base + j].
+// Called by all threads of the CTA; ends with the CTA synchronised.
+template <int F>
+__device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const uint32_t (&qreg)[16], uint32_t base,
+                                            uint64_t my_meta, bool my_need) {
+    constexpr bool D = (F & PF_DENSE) != 0, S = (F & PF_SPARSE) != 0, B = (F & PF_BM25) != 0, KW = (F & PF_KEYWORD) != 0;
+    uint32_t remaining = 0, pre_start = 0, pre_end = 0, ns = 0, nb = 0;
+    const int lane = c.lane;
+    if (c.warp == 0) {
+        ns = meta_ns(my_meta); nb = meta_nb(my_meta);
+        uint32_t sz = (D ? kDenseBytes : 0u) + (S ? 8u * pad2(ns) : 0u) + (B ? 8u * pad2(nb) : 0u);
+        if (!my_need) sz = 0;
+        uint32_t incl = sz;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
+        pre_end = incl; pre_start = incl - sz;
+        remaining = __ballot_sync(kFull, my_need);
+    }
+    for (;;) {
+        if (c.warp == 0) {
+            uint32_t bm = 0;
+            if (remaining) {
+                const int first = __ffs(remaining) - 1;
+                const uint32_t b0 = __shfl_sync(kFull, pre_start, first);
+                const bool inb = ((remaining >> lane) & 1u) && (pre_end - b0 <= a.arena_bytes);
+                bm = __ballot_sync(kFull, inb);
+                if (bm == 0) {  // a record larger than the arena: the host sizes the arena so this cannot happen
+                    if (lane == 0) atomicExch(a.ctl + 1, 2u);
+                    remaining = 0;
+                } else {
+                    const int hi = 31 - __clz(bm);
+                    const uint32_t total = __shfl_sync(kFull, pre_end, hi) - b0;
+                    if (lane == 0) {
+                        mbar_arrive_expect_tx(c.mbar, total);
+                        c.c_bytes += total;
+                        c.c_eval += __popc(bm);
+                    }
+                    __syncwarp();
+                    if (inb) {
+                        const uint32_t aoff = pre_start - b0;
+                        c.info[lane] = make_uint2(aoff, ns | (nb << 16));
+                        const uint8_t *src = a.rec + meta_off16(my_meta) * 16ull;
+                        uint8_t *dst = c.arena + aoff;
+                        const uint32_t ps = 8u * pad2(ns), pb = 8u * pad2(nb);
+                        if (D && S && B) bulk_g2s(dst, src, kDenseBytes + ps + pb, c.mbar);
+                        else if (D && S) bulk_g2s(dst, src, kDenseBytes + ps, c.mbar);
+                        else if (D && B) { bulk_g2s(dst, src, kDenseBytes, c.mbar); if (pb) bulk_g2s(dst + kDenseBytes, src + kDenseBytes + ps, pb, c.mbar); }
+                        else if (D) bulk_g2s(dst, src, kDenseBytes, c.mbar);
+                        else if (S && B) { if (ps + pb) bulk_g2s(dst, src + kDenseBytes, ps + pb, c.mbar); }
+                        else if (S) { if (ps) bulk_g2s(dst, src + kDenseBytes, ps, c.mbar); }
+                        else { if (pb) bulk_g2s(dst, src + kDenseBytes + ps, pb, c.mbar); }
+                    }
+                    remaining &= ~bm;
+                }
+            }
+            if (lane == 0) { c.ctl[CTL_BATCH] = bm; c.ctl[CTL_LAST] = (remaining == 0) ? 1u : 0u; }
+        }
+        __syncthreads();
+        const uint32_t bm = c.ctl[CTL_BATCH];
+        const bool last = c.ctl[CTL_LAST] != 0;
+        if (bm) {
+            mbar_wait_bounded(c.mbar, c.phase, a.ctl + 1, 1u);
+            c.phase ^= 1u;
+            const int nb_batch = __popc(bm);
+            for (int k = c.warp; k < nb_batch; k += kSearchWarps) {  // warp w takes the (w + 4k)-th slot of the batch
+                const int j = __fns(bm, 0, k + 1);
+                const uint2 inf = c.info[j];
+                uint32_t hit = 0;
+                const float d = score_record<F>(c.arena + inf.x, inf.y & 0xFFFFu, inf.y >> 16, qreg, c.sq, a.sq_mask,
+                                                a.sq_shift, c.bq, a.bq_mask, a.bq_shift, lane, hit);
+                if (KW) hit = __ballot_sync(kFull, hit != 0);
+                if (lane == 0) {
+                    c.pool_dis[base + j] = d;
+                    if (KW && hit) c.pool_id[base + j] |= 0x40000000u;
+                }
+            }
+        }
+        __syncthreads();
+        if (!bm || last) break;
+    }
+}
+
+// Block-wide restatement of the reference's shared-memory bitonic network for an arbitrary length
+// (include/utils.cuh:261-280), used once per query by the KG variant to order the seeded pool prefix.
+__device__ __forceinline__ void block_sort_kg(float *dis, uint32_t *id, uint32_t *ent, uint32_t *hop, uint32_t len, int tid) {
+    for (uint32_t stride = 1; stride < len; stride <<= 1) {
+        for (uint32_t step = stride; step > 0; step >>= 1) {
+            for (uint32_t k = tid; k < len / 2; k += kSearchThreads) {
+                const uint32_t aa = 2 * step * (k / step), bb = k % step;
+                const uint32_t u = (step == stride) ? (aa + step - 1 - bb) : (aa + bb), d = aa + bb + step;
+                if (d < len && dis[u] > dis[d]) {
+                    const float td = dis[u]; dis[u] = dis[d]; dis[d] = td;
+                    uint32_t t = id[u]; id[u] = id[d]; id[d] = t;
+                    t = ent[u]; ent[u] = ent[d]; ent[d] = t;
+                    t = hop[u]; hop[u] = hop[d]; hop[d] = t;
+                }
+            }
+            __syncthreads();
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// the search kernel
+// ---------------------------------------------------------------------------------------------------------
+template <int F>
+__global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchArgs a) {
+    constexpr bool D = (F & PF_DENSE) != 0, S = (F & PF_SPARSE) != 0, B = (F & PF_BM25) != 0;
+    constexpr bool KW = (F & PF_KEYWORD) != 0, KG = (F & PF_KG) != 0;
+    constexpr uint32_t IDMASK = KW ? 0x3FFFFFFFu : 0x7FFFFFFFu;
+
+    extern __shared__ __align__(128) uint8_t smem[];
+    Ctx c;
+    c.mbar = reinterpret_cast<uint64_t *>(smem);
+    c.ctl = reinterpret_cast<volatile uint32_t *>(smem + 16);
+    c.pool_id = reinterpret_cast<uint32_t *>(smem + a.o_pool_id);
+    c.pool_dis = reinterpret_cast<float *>(smem + a.o_pool_dis);
+    c.pool_ent = reinterpret_cast<uint32_t *>(smem + a.o_pool_ent);
+    c.pool_hop = reinterpret_cast<uint32_t *>(smem + a.o_pool_hop);
+    c.vis = reinterpret_cast<uint32_t *>(smem + a.o_vis);
+    c.info = reinterpret_cast<uint2 *>(smem + a.o_info);
+    c.sq = reinterpret_cast<uint2 *>(smem + a.o_sq);
+    c.bq = reinterpret_cast<uint2 *>(smem + a.o_bq);
+    c.kw_id = reinterpret_cast<uint32_t *>(smem + a.o_kw);
+    c.kw_dis = reinterpret_cast<float *>(smem + a.o_kw + 4 * kKeywordRing);
+    c.arena = smem + a.o_arena;
+    c.tid = threadIdx.x; c.lane = c.tid & 31; c.warp = c.tid >> 5;
+    c.phase = 0; c.c_exp = 0; c.c_eval = 0; c.c_bytes = 0;
+    const int tid = c.tid, lane = c.lane, warp = c.warp;
+    const uint32_t topm = a.cands;
+    uint32_t *pool_id = c.pool_id;
+    float *pool_dis = c.pool_dis;
+    uint32_t *stg_id = pool_id + topm;
+    float *stg_dis = pool_dis + topm;
+
+    if (tid == 0) { mbar_init(c.mbar, 1); mbar_fence_init(); }
+    __syncthreads();
+
+    for (;;) {
+        if (tid == 0) c.ctl[CTL_QUERY] = atomicAdd(a.ctl, 1u);
+        __syncthreads();
+        const uint32_t qi = c.ctl[CTL_QUERY];
+        if (qi >= a.nq) break;
+
+        // ---- per-query state -----------------------------------------------------------------------------
+        for (uint32_t i = tid; i <= a.vis_mask; i += kSearchThreads) c.vis[i] = kEmpty;
+        for (uint32_t i = tid; i < topm + 32; i += kSearchThreads) {
+            pool_id[i] = kEmpty; pool_dis[i] = kInfDis;
+            if (KG) { c.pool_ent[i] = kEmpty; c.pool_hop[i] = 0; }
+        }
+        if (S) for (uint32_t i = tid; i <= a.sq_mask; i += kSearchThreads) c.sq[i] = make_uint2(kEmpty, 0u);
+        if (B) for (uint32_t i = tid; i <= a.bq_mask; i += kSearchThreads) c.bq[i] = make_uint2(kEmpty, 0u);
+        if (KW && tid < kKeywordRing) { c.kw_id[tid] = 0x3FFFFFFFu; c.kw_dis[tid] = kInfDis; }
+        if (tid == 0) c.ctl[CTL_KWNUM] = 0;
+        // query: weight folded in fp32, then rounded to half (ref: src/query.cu:1871-1875, 2002)
+        uint32_t qreg[16];
+        if (D) {
+            const float4 *qp = reinterpret_cast<const float4 *>(a.qdense + (size_t)qi * kDim);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float4 f = __ldg(qp + lane + 32 * k);
+                qreg[2 * k] = pack_half2(__fmul_rn(f.x, a.w_dense), __fmul_rn(f.y, a.w_dense));
+                qreg[2 * k + 1] = pack_half2(__fmul_rn(f.z, a.w_dense), __fmul_rn(f.w, a.w_dense));
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 16; ++k) qreg[k] = 0;
+        }
+        __syncthreads();
+        if (S)
+            for (uint32_t j = a.qs_off[qi] + tid; j < a.qs_off[qi + 1]; j += kSearchThreads)
+                qtab_insert(c.sq, a.sq_mask, a.sq_shift, a.qs_idx[j], __fmul_rn(a.qs_val[j], a.w_sparse));
+        if (B)
+            for (uint32_t j = a.qb_off[qi] + tid; j < a.qb_off[qi + 1]; j += kSearchThreads)
+                qtab_insert(c.bq, a.bq_mask, a.bq_shift, a.qb_idx[j], __fmul_rn(a.qb_val[j], a.w_bm25));
+        __syncthreads();
+
+        // ---- seeding -------------------------------------------------------------------------------------
+        if (!KG) {
+            // entry points: all 32 are scored (ref: src/query.cu:440-485)
+            uint64_t meta = 0;
+            if (warp == 0) {
+                const FatEdge e = a.ep_fat[lane];
+                vis_insert(c.vis, a.vis_mask, e.id);
+                stg_id[lane] = e.id;
+                meta = (uint64_t)e.meta_lo | ((uint64_t)e.meta_hi << 32);
+            }
+            score_slots<F>(a, c, qreg, topm, meta, true);
+            if (warp == 0) {
+                float d = stg_dis[lane];
+                uint32_t id = stg_id[lane], e0 = 0, e1 = 0;
+                warp_sort32<false>(d, id, e0, e1, lane);
+                stg_id[lane] = id; stg_dis[lane] = d;
+                pool_id[lane] = id; pool_dis[lane] = d;
+            }
+            __syncthreads();
+        } else {
+            // docs of the query's entities, then entry points, scored and sorted (ref: src/query.cu:1577-1643)
+            if (warp == 0) {
+                uint32_t nfill = 0;
+                if (lane == 0) {
+                    for (uint32_t i = a.qe_off[qi]; i < a.qe_off[qi + 1]; ++i) {
+                        const uint32_t e = a.qe_idx[i];
+                        for (uint32_t j = a.e2d_off[e]; j < a.e2d_off[e + 1]; ++j) {
+                            const uint32_t d = a.e2d_idx[j];
+                            if (vis_insert(c.vis, a.vis_mask, d) != 0 && nfill < topm + 32) {
+                                pool_id[nfill] = d; c.pool_ent[nfill] = e; c.pool_hop[nfill] = 0; ++nfill;
+                            }
+                        }
+                    }
+                }
+                nfill = __shfl_sync(kFull, nfill, 0);
+                if (nfill < topm) {
+                    const uint32_t id = a.ep_fat[lane].id;
+                    const uint32_t grp = __match_any_sync(kFull, id);
+                    const bool leader = (__ffs(grp) - 1) == lane;
+                    const bool isnew = leader && vis_insert(c.vis, a.vis_mask, id) != 0;
+                    const uint32_t bal = __ballot_sync(kFull, isnew);
+                    const uint32_t t = nfill + __popc(bal & ((1u << lane) - 1u));
+                    if (isnew && t < topm + 32) { pool_id[t] = id; c.pool_ent[t] = kEmpty; c.pool_hop[t] = 0; }
+                    nfill += __popc(bal);
+                }
+                if (lane == 0) c.ctl[CTL_M] = min(nfill, topm + 32);
+            }
+            __syncthreads();
+            const uint32_t m = c.ctl[CTL_M];
+            for (uint32_t cb = 0; cb < m; cb += 32) {
+                uint64_t meta = 0; bool need = false;
+                if (warp == 0) {
+                    need = cb + lane < m;
+                    if (need) meta = a.meta[pool_id[cb + lane]];
+                }
+                score_slots<F>(a, c, qreg, cb, meta, need);
+            }
+            for (uint32_t i = tid; i < m; i += kSearchThreads)
+                if (c.pool_ent[i] != kEmpty) pool_dis[i] = __fsub_rn(pool_dis[i], a.kg_weight);
+            __syncthreads();
+            block_sort_kg(pool_dis, pool_id, c.pool_ent, c.pool_hop, m, tid);
+            __syncthreads();
+        }
+
+        // ---- greedy iterations (ref: src/query.cu:488-563) ---------------------------------------------------
+        for (int it = 0; it < kMaxIter; ++it) {
+            if ((it + 1) % kHashReset == 0) {
+                for (uint32_t i = tid; i <= a.vis_mask; i += kSearchThreads) c.vis[i] = kEmpty;
+                __syncthreads();
+                for (uint32_t i = tid; i < topm + 32; i += kSearchThreads) vis_insert(c.vis, a.vis_mask, pool_id[i] & IDMASK);
+                __syncthreads();
+            }
+            // first pool entry whose explored bit is clear
+            if (warp == 0) {
+                uint32_t sel = kEmpty, slot = 0;
+                for (uint32_t b0 = 0; b0 < topm; b0 += 32) {
+                    const uint32_t id = pool_id[b0 + lane];
+                    const uint32_t bal = __ballot_sync(kFull, (id & 0x80000000u) == 0);
+                    if (bal) {
+                        const int f = __ffs(bal) - 1;
+                        sel = __shfl_sync(kFull, id, f);
+                        slot = b0 + f;
+                        if (lane == f) pool_id[b0 + lane] = id | 0x80000000u;
+                        break;
+                    }
+                }
+                if (lane == 0) { c.ctl[CTL_SEL] = sel; c.ctl[CTL_SLOT] = slot; }
+            }
+            __syncthreads();
+            const uint32_t sel = c.ctl[CTL_SEL];
+            if (sel == kEmpty) break;
+            const uint32_t node = sel & IDMASK;
+
+            // stage the row: ids, visited filter, (keyword refill | KG tagging and augmentation)
+            uint64_t my_meta = 0;
+            bool my_need = false;
+            uint32_t my_ent = kEmpty, my_hop = 0;
+            bool my_tag = false;
+            if (warp == 0) {
+                if (lane == 0) { c.c_exp += 1; c.c_bytes += 32 * sizeof(FatEdge); }
+                const FatEdge *row = a.fat + (size_t)node * AP_ROW;
+                const uint4 raw_e = __ldg(reinterpret_cast<const uint4 *>(row) + lane);
+                uint32_t my_id = raw_e.x;
+                my_meta = (uint64_t)raw_e.y | ((uint64_t)raw_e.z << 32);
+                {   // duplicates inside a row: the lowest slot is the one that counts as new
+                    const uint32_t grp = __match_any_sync(kFull, my_id);
+                    const bool leader = (__ffs(grp) - 1) == lane;
+                    my_need = leader && vis_insert(c.vis, a.vis_mask, my_id) != 0;
+                }
+                if (KW) {
+                    // visited slots are refilled from the row's keyword edges (ref: src/query.cu:1413-1425)
+                    const uint32_t visited = __ballot_sync(kFull, !my_need);
+                    const uint32_t t = __popc(visited & ((1u << lane) - 1u));
+                    const uint32_t cnt = __ldg(&row[AP_DEGREE].id);
+                    const bool part = !my_need && t < cnt;
+                    const uint32_t act = __ballot_sync(kFull, part);
+                    if (part) {
+                        const uint4 raw = __ldg(reinterpret_cast<const uint4 *>(row) + AP_DEGREE + 1 + t);
+                        const uint32_t grp = __match_any_sync(act, raw.x);
+                        const bool leader = (__ffs(grp) - 1) == lane;
+                        if (leader && vis_insert(c.vis, a.vis_mask, raw.x) != 0) {
+                            my_id = raw.x; my_meta = (uint64_t)raw.y | ((uint64_t)raw.z << 32); my_need = true;
+                        }
+                    }
+                }
+                stg_id[lane] = my_id;
+                stg_dis[lane] = my_need ? 0.0f : kInfDis;
+                if (KG) {
+                    const uint32_t slot = c.ctl[CTL_SLOT];
+                    const uint32_t hop_cur = c.pool_hop[slot], ent_cur = c.pool_ent[slot];
+                    my_hop = hop_cur + 1;
+                    c.pool_ent[topm + lane] = kEmpty;
+                    c.pool_hop[topm + lane] = my_hop;
+                    __syncwarp();
+                    if (hop_cur < 3 && ent_cur != kEmpty) {
+                        // Logical-edge augmentation (ref: src/query.cu:1697-1735), restated sequentially: docs of
+                        // the KG neighbours of the entity that brought this node are tagged when staged, and
+                        // already-visited slots are replaced by such docs.
+                        if (lane == 0) {
+                            const uint32_t e0 = a.e2e_off[ent_cur], e1 = a.e2e_off[ent_cur + 1];
+                            for (uint32_t j = e0; j < e1; ++j) {
+                                const uint32_t ne = a.e2e_idx[j];
+                                for (uint32_t k = a.e2d_off[ne]; k < a.e2d_off[ne + 1]; ++k) {
+                                    const uint32_t val = a.e2d_idx[k];
+                                    uint32_t tmp = 32, res = 0;
+                                    while (tmp > 1) {  // the reference's halving probe over the (unsorted) staged ids
+                                        const uint32_t half = tmp / 2;
+                                        res += ((stg_id[res + half] & 0x3FFFFFFFu) < val) ? half : 0;
+                                        tmp -= half;
+                                    }
+                                    res += ((stg_id[res] & 0x3FFFFFFFu) < val);
+                                    if (res <= 31 && (stg_id[res] & 0x3FFFFFFFu) == val && stg_dis[res] < 1.0f) {
+                                        stg_dis[res] = 2.0f;
+                                        c.pool_ent[topm + res] = ne;
+                                    }
+                                }
+                            }
+                            uint32_t claimed = 0;
+                            for (int j = 0; j < 32; ++j) {
+                                if (stg_dis[j] > 3.0f) {
+                                    const uint32_t t = claimed++;
+                                    if (t < e1 - e0) {
+                                        const uint32_t ne = a.e2e_idx[e0 + t];
+                                        for (uint32_t k = a.e2d_off[ne]; k < a.e2d_off[ne + 1]; ++k) {
+                                            const uint32_t cand = a.e2d_idx[k];
+                                            if ((sel & 0x3FFFFFFFu) == cand) continue;
+                                            if (vis_insert(c.vis, a.vis_mask, cand) != 0) {
+                                                stg_id[j] = cand; stg_dis[j] = 2.0f;
+                                                c.pool_ent[topm + j] = ne; c.pool_hop[topm + j] = hop_cur + 1;
+                                                break;
+                                            }
+                                        }
+                                    }
+                                }
+                            }
+                        }
+                        __syncwarp();
+                        const uint32_t nid = stg_id[lane];
+                        if (nid != my_id) { my_id = nid; my_meta = a.meta[nid]; }
+                        const float sd = stg_dis[lane];
+                        my_need = sd < 3.0f;
+                        my_tag = sd > 1.0f && my_need;
+                        my_ent = c.pool_ent[topm + lane];
+                    }
+                }
+            }
+            score_slots<F>(a, c, qreg, topm, my_meta, my_need);
+
+            // sort the 32 staged entries, decide whether the pool changes at all
+            if (warp == 0) {
+                float d = stg_dis[lane];
+                uint32_t id = stg_id[lane];
+                if (KG && my_tag) d = __fsub_rn(d, __fdiv_rn(a.kg_weight, (float)my_hop));
+                warp_sort32<KG>(d, id, my_ent, my_hop, lane);
+                stg_id[lane] = id; stg_dis[lane] = d;
+                if (KG) { c.pool_ent[topm + lane] = my_ent; c.pool_hop[topm + lane] = my_hop; }
+                if (lane == 0) c.ctl[CTL_MERGE] = (d <= pool_dis[topm - 1]) ? 1u : 0u;
+            }
+            __syncthreads();
+            if (c.ctl[CTL_MERGE]) {
+                // rank merge (ref: merge_top, src/query.cu:181-224): a pool element moves right by the number of
+                // staged elements <= it, a staged element lands at its index plus the number of pool elements < it
+                uint32_t r_id[kMergeMax], r_pos[kMergeMax], r_e[kMergeMax], r_h[kMergeMax];
+                float r_dis[kMergeMax];
+#pragma unroll
+                for (int e = 0; e < kMergeMax; ++e) {
+                    const uint32_t idx = tid + e * kSearchThreads;
+                    r_pos[e] = kEmpty;
+                    if (idx < topm + 32) {
+                        r_dis[e] = pool_dis[idx]; r_id[e] = pool_id[idx];
+                        if (KG) { r_e[e] = c.pool_ent[idx]; r_h[e] = c.pool_hop[idx]; }
+                        r_pos[e] = idx < topm ? idx + count_le(stg_dis, 32, r_dis[e])
+                                              : (idx - topm) + count_lt(pool_dis, topm, r_dis[e]);
+                    }
+                }
+                if (KW && warp == 0) {
+                    // pool elements pushed out whose id word has bit 0 set go to the side ring, in ascending pool
+                    // index (ref: merge_top_keyword, src/query.cu:244-248, `id & 0x40000000 != 0` parses as `id & 1`)
+                    const uint32_t idx = topm - 32 + lane;
+                    const float v = pool_dis[idx];
+                    const uint32_t id = pool_id[idx];
+                    const bool ev = (idx + count_le(stg_dis, 32, v) >= topm) && (id & 1u);
+                    const uint32_t bal = __ballot_sync(kFull, ev);
+                    const uint32_t kn = c.ctl[CTL_KWNUM];
+                    if (ev) {
+                        const uint32_t s = (kn + __popc(bal & ((1u << lane) - 1u))) % kKeywordRing;
+                        c.kw_id[s] = id & 0x3FFFFFFFu; c.kw_dis[s] = v;
+                    }
+                    __syncwarp();
+                    if (lane == 0) c.ctl[CTL_KWNUM] = kn + __popc(bal);
+                }
+                __syncthreads();
+#pragma unroll
+                for (int e = 0; e < kMergeMax; ++e)
+                    if (r_pos[e] < topm) {
+                        pool_id[r_pos[e]] = r_id[e]; pool_dis[r_pos[e]] = r_dis[e];
+                        if (KG) { c.pool_ent[r_pos[e]] = r_e[e]; c.pool_hop[r_pos[e]] = r_h[e]; }
+                    }
+                __syncthreads();
+            }
+        }
+
+        // ---- results (ref: src/query.cu:566-569; keyword ordering :1465-1481) ---------------------------------
+        if (!KW) {
+            for (uint32_t i = tid; i < topm; i += kSearchThreads) {
+                a.out_ids[(size_t)qi * topm + i] = pool_id[i] & 0x7FFFFFFFu;
+                a.out_dis[(size_t)qi * topm + i] = pool_dis[i];
+            }
+        } else {
+            if (warp == 0) {
+                float d = c.kw_dis[lane];
+                uint32_t id = c.kw_id[lane], e0 = 0, e1 = 0;
+                warp_sort32<false>(d, id, e0, e1, lane);
+                c.kw_id[lane] = id; c.kw_dis[lane] = d;
+                uint32_t nout = 0;  // keyword hits first, in pool order
+                for (uint32_t b0 = 0; b0 < topm; b0 += 32) {
+                    const uint32_t pid = pool_id[b0 + lane];
+                    const bool h = (pid & 0x40000000u) != 0;
+                    const uint32_t bal = __ballot_sync(kFull, h);
+                    if (h) {
+                        const uint32_t o = nout + __popc(bal & ((1u << lane) - 1u));
+                        a.out_ids[(size_t)qi * topm + o] = pid & 0x3FFFFFFFu;
+                        a.out_dis[(size_t)qi * topm + o] = pool_dis[b0 + lane];
+                    }
+                    nout += __popc(bal);
+                }
+                __syncwarp();
+                for (uint32_t i = nout + lane; i < topm; i += 32) {
+                    const uint32_t s = i - nout;
+                    a.out_ids[(size_t)qi * topm + i] = s < kKeywordRing ? (c.kw_id[s] & 0x3FFFFFFFu) : 0x3FFFFFFFu;
+                    a.out_dis[(size_t)qi * topm + i] = s < kKeywordRing ? c.kw_dis[s] : kInfDis;
+                }
+            }
+        }
+        __syncthreads();
+    }
+    if (tid == 0) {
+        atomicAdd(a.cnt + 0, c.c_exp);
+        atomicAdd(a.cnt + 1, c.c_eval);
+        atomicAdd(a.cnt + 2, c.c_bytes);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Distances of explicit (query, doc) pairs with the same scoring code (test hook): one warp per pair.
+// ---------------------------------------------------------------------------------------------------------
+template <int F>
+__global__ void __launch_bounds__(32) distances_kernel(const SearchArgs a, size_t n_pairs, const uint32_t *pair_q,
+                                                       const uint32_t *pair_d, float *out) {
+    constexpr bool D = (F & PF_DENSE) != 0, S = (F & PF_SPARSE) != 0, B = (F & PF_BM25) != 0;
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint2 *sq = reinterpret_cast<uint2 *>(smem + a.o_sq);
+    uint2 *bq = reinterpret_cast<uint2 *>(smem + a.o_bq);
+    uint8_t *arena = smem + a.o_arena;
+    const int lane = threadIdx.x;
+    for (size_t p = blockIdx.x; p < n_pairs; p += gridDim.x) {
+        const uint32_t qi = pair_q[p], x = pair_d[p];
+        if (S) for (uint32_t i = lane; i <= a.sq_mask; i += 32) sq[i] = make_uint2(kEmpty, 0u);
+        if (B) for (uint32_t i = lane; i <= a.bq_mask; i += 32) bq[i] = make_uint2(kEmpty, 0u);
+        uint32_t qreg[16];
+#pragma unroll
+        for (int k = 0; k < 16; ++k) qreg[k] = 0;
+        if (D) {
+            const float4 *qp = reinterpret_cast<const float4 *>(a.qdense + (size_t)qi * kDim);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float4 f = __ldg(qp + lane + 32 * k);
+                qreg[2 * k] = pack_half2(__fmul_rn(f.x, a.w_dense), __fmul_rn(f.y, a.w_dense));
+                qreg[2 * k + 1] = pack_half2(__fmul_rn(f.z, a.w_dense), __fmul_rn(f.w, a.w_dense));
+            }
+        }
+        __syncwarp();
+        if (S)
+            for (uint32_t j = a.qs_off[qi] + lane; j < a.qs_off[qi + 1]; j += 32)
+                qtab_insert(sq, a.sq_mask, a.sq_shift, a.qs_idx[j], __fmul_rn(a.qs_val[j], a.w_sparse));
+        if (B)
+            for (uint32_t j = a.qb_off[qi] + lane; j < a.qb_off[qi + 1]; j += 32)
+                qtab_insert(bq, a.bq_mask, a.bq_shift, a.qb_idx[j], __fmul_rn(a.qb_val[j], a.w_bm25));
+        const uint64_t m = a.meta[x];
+        const uint32_t ns = meta_ns(m), nb = meta_nb(m);
+        const uint4 *src = reinterpret_cast<const uint4 *>(a.rec + meta_off16(m) * 16ull);
+        uint4 *dst = reinterpret_cast<uint4 *>(arena);
+        uint32_t o = 0;
+        if (D) { for (uint32_t i = lane; i < kDenseBytes / 16; i += 32) dst[i] = src[i]; o += kDenseBytes / 16; }
+        if (S) { const uint32_t w = pad2(ns) / 2; for (uint32_t i = lane; i < w; i += 32) dst[o + i] = src[kDenseBytes / 16 + i]; o += w; }
+        if (B) { const uint32_t w = pad2(nb) / 2; for (uint32_t i = lane; i < w; i += 32) dst[o + i] = src[kDenseBytes / 16 + pad2(ns) / 2 + i]; }
+        __syncwarp();
+        uint32_t hit = 0;
+        const float d = score_record<F>(arena, ns, nb, qreg, sq, a.sq_mask, a.sq_shift, bq, a.bq_mask, a.bq_shift, lane, hit);
+        if (lane == 0) out[p] = d;
+        __syncwarp();
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// host side
+// ---------------------------------------------------------------------------------------------------------
+static uint32_t pow2_at_least(uint32_t v) { uint32_t p = 32; while (p < v) p <<= 1; return p; }
+static uint32_t log2u(uint32_t p) { uint32_t l = 0; while ((1u << l) < p) ++l; return l; }
+
+static uint32_t layout(SearchArgs &a, uint32_t cands, uint32_t flags, uint32_t max_qs, uint32_t max_qb) {
+    uint32_t o = 16 + 64;
+    auto take = [&](uint32_t bytes, uint32_t align) { o = (o + align - 1) / align * align; uint32_t r = o; o += bytes; return r; };
+    a.o_pool_id = take(4 * (cands + 32), 16);
+    a.o_pool_dis = take(4 * (cands + 32), 16);
+    a.o_pool_ent = a.o_pool_hop = 0;
+    if (flags & PF_KG) { a.o_pool_ent = take(4 * (cands + 32), 16); a.o_pool_hop = take(4 * (cands + 32), 16); }
+    const uint32_t vis = (cands + 32 + 3 * 32) * 2 <= 1024 ? 1024u : 2048u;
+    a.vis_mask = vis - 1;
+    a.o_vis = take(4 * vis, 16);
+    a.o_info = take(8 * 32, 16);
+    const uint32_t sqn = pow2_at_least(4 * std::max(1u, max_qs)), bqn = pow2_at_least(4 * std::max(1u, max_qb));
+    a.sq_mask = sqn - 1; a.sq_shift = 32 - log2u(sqn);
+    a.bq_mask = bqn - 1; a.bq_shift = 32 - log2u(bqn);
+    a.o_sq = take((flags & PF_SPARSE) ? 8 * sqn : 0, 16);
+    a.o_bq = take((flags & PF_BM25) ? 8 * bqn : 0, 16);
+    a.o_kw = take((flags & PF_KEYWORD) ? 8 * kKeywordRing : 0, 16);
+    a.o_arena = take(0, 128);
+    return a.o_arena;  // fixed bytes before the arena
+}
+
+template <int F>
+static int launch_one(ap_index *ix, SearchArgs &a, uint32_t fixed, uint32_t want_ctas, uint32_t arena_req,
+                      uint32_t need_bytes, cudaStream_t stream) {
+    // arena: as large as lets `want_ctas` CTAs share one SM, never smaller than the largest record
+    uint32_t ctas = want_ctas ? want_ctas : 4;
+    uint32_t arena = 0;
+    for (;; --ctas) {
+        const size_t per = std::min(ix->smem_per_sm / ctas - 1024, ix->smem_per_block);
+        if (per > fixed + need_bytes) { arena = (uint32_t)((per - fixed) / 128 * 128); if (arena >= need_bytes) break; }
+        if (ctas == 1) return fail(AP_ERR_LIMIT, "a document record of %u bytes does not fit the shared-memory arena", need_bytes);
+    }
+    if (arena_req) {
+        arena = std::max(need_bytes, arena_req) / 128 * 128 + ((std::max(need_bytes, arena_req) % 128) ? 128 : 0);
+        if (fixed + arena > ix->smem_per_block) return fail(AP_ERR_LIMIT, "arena of %u bytes exceeds the per-block shared memory", arena);
+    }
+    arena = std::min(arena, 512u * 1024u);  // the mbarrier transaction count is 20 bits wide
+    a.arena_bytes = arena;
+    const size_t smem = fixed + arena;
+    AP_CUDA(cudaFuncSetAttribute(search_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    int occ = 0;
+    AP_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, search_kernel<F>, kSearchThreads, smem));
+    if (occ < 1) return fail(AP_ERR_LIMIT, "search kernel does not fit on an SM (%zu bytes of shared memory)", smem);
+    const uint32_t grid = (uint32_t)std::min<uint64_t>(a.nq, (uint64_t)occ * ix->num_sms);
+    search_kernel<F><<<grid, kSearchThreads, smem, stream>>>(a);
+    AP_CUDA(cudaGetLastError());
+    return AP_OK;
+}
+
+static void fill_args(ap_index *ix, const SearchLaunch &L, SearchArgs &a) {
+    a.fat = ix->fat; a.ep_fat = ix->ep_fat; a.rec = ix->rec; a.meta = ix->meta; a.n = ix->n;
+    a.qdense = L.qdense; a.qs_off = L.qs_off; a.qs_idx = L.qs_idx; a.qs_val = L.qs_val;
+    a.qb_off = L.qb_off; a.qb_idx = L.qb_idx; a.qb_val = L.qb_val;
+    a.e2e_off = ix->e2e_off; a.e2e_idx = ix->e2e_idx; a.e2d_off = ix->e2d_off; a.e2d_idx = ix->e2d_idx;
+    a.qe_off = L.qe_off; a.qe_idx = L.qe_idx;
+    a.nq = L.nq; a.w_sparse = L.w_sparse; a.w_bm25 = L.w_bm25; a.w_dense = L.w_dense; a.kg_weight = L.kg_weight;
+    a.cands = L.cands; a.out_ids = L.out_ids; a.out_dis = L.out_dis;
+    a.ctl = ix->d_ctl; a.cnt = ix->d_cnt;
+}
+
+static int kernel_flags(const SearchLaunch &L) {
+    int f = (int)L.path;
+    if (L.flags & AP_SEARCH_KEYWORD) f |= PF_KEYWORD;
+    if (L.flags & AP_SEARCH_KG) f |= PF_KG;
+    if (L.flags & AP_SEARCH_UNFUSED_DENSE) f |= PF_UNFUSED;
+    return f;
+}
+
+static uint32_t need_bytes_for(const ap_index *ix, int f) {
+    // upper bound of one record's staged size for the active paths
+    return ((f & PF_DENSE) ? kDenseBytes : 0u) + ((f & PF_SPARSE) ? 8u * pad2(ix->max_ns) : 0u) +
+           ((f & PF_BM25) ? 8u * pad2(ix->max_nb) : 0u);
+}
+
+#define AP_SEARCH_CASES(X) \
+    X(1) X(2) X(3) X(4) X(5) X(6) X(7) X(7 | PF_KEYWORD) X(7 | PF_KG) \
+    X(1 | PF_UNFUSED) X(3 | PF_UNFUSED) X(5 | PF_UNFUSED) X(7 | PF_UNFUSED) X(7 | PF_KEYWORD | PF_UNFUSED) X(7 | PF_KG | PF_UNFUSED)
+
+int search_launch(ap_index *ix, const SearchLaunch &L, uint32_t *launches) {
+    SearchArgs a{};
+    fill_args(ix, L, a);
+    int f = kernel_flags(L);
+    if (!(f & PF_DENSE)) f &= ~PF_UNFUSED;
+    const uint32_t fixed = layout(a, L.cands, (uint32_t)f, L.max_qs, L.max_qb);
+    const uint32_t need = std::max(16u, need_bytes_for(ix, f));
+    AP_CUDA(cudaMemsetAsync(ix->d_ctl, 0, 4, L.stream));  // next-query counter; the error word is sticky
+    int rc = AP_ERR_ARG;
+    switch (f) {
+#define X(FL) case (FL): rc = launch_one<(FL)>(ix, a, fixed, L.ctas_per_sm, L.arena_bytes, need, L.stream); break;
+        AP_SEARCH_CASES(X)
+#undef X
+        default: return fail(AP_ERR_ARG, "unsupported search mode 0x%x (keyword and KG search use all three paths)", f);
+    }
+    if (rc == AP_OK && launches) *launches += 1;
+    return rc;
+}
+
+int distances_launch(ap_index *ix, const SearchLaunch &L, size_t n_pairs, const uint32_t *pair_q, const uint32_t *pair_d,
+                     float *out) {
+    SearchArgs a{};
+    fill_args(ix, L, a);
+    int f = kernel_flags(L) & (PF_DENSE | PF_SPARSE | PF_BM25 | PF_UNFUSED);
+    if (!(f & PF_DENSE)) f &= ~PF_UNFUSED;
+    const uint32_t fixed = layout(a, 32, (uint32_t)f, L.max_qs, L.max_qb);
+    const size_t smem = fixed + record_bytes(ix->max_ns, ix->max_nb);
+    const uint32_t grid = (uint32_t)std::min<size_t>(n_pairs, (size_t)ix->num_sms * 16);
+    if (grid == 0) return AP_OK;
+    switch (f) {
+#define X(FL)                                                                                                        \
+    case (FL):                                                                                                       \
+        AP_CUDA(cudaFuncSetAttribute(distances_kernel<(FL)>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); \
+        distances_kernel<(FL)><<<grid, 32, smem, L.stream>>>(a, n_pairs, pair_q, pair_d, out);                       \
+        break;
+        X(1) X(2) X(3) X(4) X(5) X(6) X(7) X(1 | PF_UNFUSED) X(3 | PF_UNFUSED) X(5 | PF_UNFUSED) X(7 | PF_UNFUSED)
+#undef X
+        default: return fail(AP_ERR_ARG, "unsupported distance mode 0x%x", f);
+    }
+    AP_CUDA(cudaGetLastError());
+    return AP_OK;
+}
+
+// ---------------------------------------------------------------------------------------------------------
+// Corpus-sharded search: merge the per-shard result lists of every query into a global top-k.  One warp per
+// query; the k smallest (distance, id) keys are extracted in ascending order, each round taking the smallest key
+// above the previous one (document ids are unique across shards, so keys are distinct).
+// ---------------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t f2ord_s(float f) { const uint32_t b = __float_as_uint(f); return (b & 0x80000000u) ? ~b : (b | 0x80000000u); }
+
+__global__ void merge_shards_kernel(uint32_t shards, uint32_t nq, uint32_t per, const uint32_t *__restrict__ in_ids,
+                                    const float *__restrict__ in_dis, uint32_t top_k, uint32_t *__restrict__ out_ids,
+                                    float *__restrict__ out_dis) {
+    const uint32_t q = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (q >= nq) return;
+    const uint32_t total = shards * per;
+    unsigned long long prev = 0;
+    bool have_prev = false;
+    for (uint32_t r = 0; r < top_k; ++r) {
+        unsigned long long best = ~0ull;
+        float bd = kInfDis;
+        for (uint32_t e = lane; e < total; e += 32) {
+            const uint32_t s = e / per, j = e % per;
+            const size_t at = ((size_t)s * nq + q) * per + j;
+            const float d = in_dis[at];
+            const unsigned long long key = ((unsigned long long)f2ord_s(d) << 32) | in_ids[at];
+            if ((!have_prev || key > prev) && key < best) { best = key; bd = d; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long ob = __shfl_xor_sync(kFull, best, o);
+            const float od = __shfl_xor_sync(kFull, bd, o);
+            if (ob < best) { best = ob; bd = od; }
+        }
+        if (lane == 0) {
+            out_ids[(size_t)q * top_k + r] = best == ~0ull ? kEmpty : (uint32_t)best;
+            out_dis[(size_t)q * top_k + r] = best == ~0ull ? kInfDis : bd;
+        }
+        prev = best; have_prev = true;
+    }
+}
+
+}  // namespace apoe
+
+extern "C" int ap_merge_shard_results(int device, uint32_t shards, uint32_t nq, uint32_t per_shard, const uint32_t *in_ids,
+                                      const float *in_dis, uint32_t top_k, uint32_t *out_ids, float *out_dis, void *stream) {
+    using namespace apoe;
+    if (!in_ids || !in_dis || !out_ids || !out_dis) return fail(AP_ERR_ARG, "null pointer");
+    if (shards == 0 || nq == 0 || per_shard == 0 || top_k == 0) return fail(AP_ERR_ARG, "empty merge");
+    AP_CUDA(cudaSetDevice(device));
+    merge_shards_kernel<<<(nq + 3) / 4, 128, 0, (cudaStream_t)stream>>>(shards, nq, per_shard, in_ids, in_dis, top_k, out_ids, out_dis);
+    AP_CUDA(cudaGetLastError());
+    return AP_OK;
+}

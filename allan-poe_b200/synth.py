@@ -1,0 +1,303 @@
+"""Seeded synthetic corpora, queries, knowledge graphs and keyword files.
+
+The generators follow the shapes and value distributions of the benchmark
+configurations (dense 1024-d unit vectors; learned-sparse rows over a 30 522
+term vocabulary with Zipf(1.1) term ids and log-normal values; BM25 rows over a
+100 000 term vocabulary with Zipf(1.0) ids, tf = 1 + Geometric(0.6) and
+k1 = 1.2, b = 0.75 weights) and write them in the byte formats the reference
+loaders read (include/utils.cuh:361-398, src/query.cu:35-108).
+
+Everything is torch code that runs on CPU (tests) or on a GPU (benchmark), so a
+1M-document corpus can be produced directly in device memory.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass, field
+
+import numpy as np
+import torch
+
+DIM = 1024
+SPARSE_VOCAB = 30522
+BM25_VOCAB = 100000
+MAX_SPARSE = 550   # row capacities of the reference kernels (src/query.cu:13-14)
+MAX_BM25 = 780
+
+
+@dataclass
+class Csr:
+    off: torch.Tensor   # int32 (bit pattern of u32), rows + 1
+    idx: torch.Tensor   # int32
+    val: torch.Tensor   # float32
+
+    @property
+    def rows(self) -> int:
+        return self.off.numel() - 1
+
+    def to(self, device) -> "Csr":
+        return Csr(self.off.to(device), self.idx.to(device), self.val.to(device))
+
+    def slice_rows(self, a: int, b: int) -> "Csr":
+        lo, hi = int(self.off[a]), int(self.off[b])
+        return Csr((self.off[a:b + 1] - lo).contiguous(), self.idx[lo:hi].contiguous(), self.val[lo:hi].contiguous())
+
+
+@dataclass
+class Corpus:
+    dense: torch.Tensor          # [n, 1024] float32, unit rows
+    sparse: Csr
+    bm25: Csr
+    idf: torch.Tensor            # [BM25_VOCAB] float32 (for query weights)
+    extra: dict = field(default_factory=dict)
+
+    @property
+    def n(self) -> int:
+        return self.dense.shape[0]
+
+
+@dataclass
+class Queries:
+    dense: torch.Tensor
+    sparse: Csr
+    bm25: Csr
+
+    @property
+    def nq(self) -> int:
+        return self.dense.shape[0]
+
+    def slice(self, a: int, b: int) -> "Queries":
+        return Queries(self.dense[a:b].contiguous(), self.sparse.slice_rows(a, b), self.bm25.slice_rows(a, b))
+
+
+def _zipf_cdf(vocab: int, s: float, device) -> torch.Tensor:
+    r = torch.arange(1, vocab + 1, dtype=torch.float64, device=device)
+    p = r.pow(-s)
+    return (p.cumsum(0) / p.sum()).to(torch.float64)
+
+
+def _zipf_rows(counts: torch.Tensor, vocab: int, s: float, gen: torch.Generator, oversample: float = 2.5):
+    """Per row, `counts[i]` distinct Zipf-distributed term ids in ascending order.
+
+    Draws `oversample * count + 8` ids with replacement, removes duplicates and
+    keeps a random subset of the requested size (fewer if the draws held fewer
+    distinct ids).  Returns (row_offsets int64 [rows+1], term ids int64).
+    """
+    device = counts.device
+    rows = counts.numel()
+    cdf = _zipf_cdf(vocab, s, device)
+    draws = (counts.to(torch.float64) * oversample).ceil().to(torch.int64) + 8
+    total = int(draws.sum())
+    row_of = torch.repeat_interleave(torch.arange(rows, device=device), draws)
+    u = torch.rand(total, generator=gen, device=device, dtype=torch.float64)
+    term = torch.searchsorted(cdf, u).clamp_(max=vocab - 1)
+    key = torch.unique(row_of * vocab + term)           # sorted (row, term), duplicates removed
+    row_u = key // vocab
+    n_u = torch.bincount(row_u, minlength=rows)
+    # random priority inside each row; keep the `counts[row]` smallest
+    pr = torch.rand(key.numel(), generator=gen, device=device, dtype=torch.float64)
+    order = torch.argsort(row_u.to(torch.float64) + pr * 0.999999)
+    start = torch.cumsum(n_u, 0) - n_u
+    rank = torch.empty_like(order)
+    rank[order] = torch.arange(key.numel(), device=device) - start[row_u[order]]
+    keep = rank < counts[row_u]
+    key = key[keep]
+    row_k = key // vocab
+    n_k = torch.bincount(row_k, minlength=rows)
+    off = torch.zeros(rows + 1, dtype=torch.int64, device=device)
+    off[1:] = torch.cumsum(n_k, 0)
+    return off, key % vocab
+
+
+def _chunks(n: int, step: int):
+    for a in range(0, n, step):
+        yield a, min(n, a + step)
+
+
+def _gen(seed: int, device) -> torch.Generator:
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    return g
+
+
+def make_corpus(n: int, seed: int = 20261125, device="cpu", mean_sparse: float = 120.0, mean_bm25: float = 60.0,
+                chunk: int = 100_000) -> Corpus:
+    device = torch.device(device)
+    g = _gen(seed, device)
+    dense = torch.empty(n, DIM, dtype=torch.float32, device=device)
+    for a, b in _chunks(n, chunk):
+        x = torch.randn(b - a, DIM, generator=g, device=device, dtype=torch.float32)
+        dense[a:b] = x / x.norm(dim=1, keepdim=True)
+
+    def rows(mean, vocab, s, cap):
+        offs, idxs = [], []
+        base = 0
+        for a, b in _chunks(n, chunk):
+            cnt = torch.poisson(torch.full((b - a,), mean, device=device), generator=g).to(torch.int64).clamp_(1, cap)
+            off, idx = _zipf_rows(cnt, vocab, s, g)
+            offs.append(off[:-1] + base)
+            base += int(off[-1])
+            idxs.append(idx)
+        off = torch.cat(offs + [torch.tensor([base], device=device)])
+        return off, torch.cat(idxs)
+
+    s_off, s_idx = rows(mean_sparse, SPARSE_VOCAB, 1.1, MAX_SPARSE)
+    s_val = torch.exp(torch.randn(s_idx.numel(), generator=g, device=device) * 0.8 - 1.0).to(torch.float32)
+    b_off, b_idx = rows(mean_bm25, BM25_VOCAB, 1.0, MAX_BM25)
+    # tf = 1 + Geometric(0.6) failures-before-success
+    uu = torch.rand(b_idx.numel(), generator=g, device=device, dtype=torch.float64).clamp_(min=1e-12)
+    tf = 1.0 + torch.floor(torch.log(uu) / math.log(1.0 - 0.6))
+    row_of = torch.repeat_interleave(torch.arange(n, device=device), (b_off[1:] - b_off[:-1]))
+    length = torch.zeros(n, dtype=torch.float64, device=device).index_add_(0, row_of, tf)
+    avglen = length.mean()
+    df = torch.bincount(b_idx, minlength=BM25_VOCAB).to(torch.float64)
+    idf = torch.log(1.0 + (n - df + 0.5) / (df + 0.5))
+    k1, bb = 1.2, 0.75
+    w = idf[b_idx] * tf * (k1 + 1.0) / (tf + k1 * (1.0 - bb + bb * length[row_of] / avglen))
+    return Corpus(dense,
+                  Csr(s_off.to(torch.int32), s_idx.to(torch.int32), s_val),
+                  Csr(b_off.to(torch.int32), b_idx.to(torch.int32), w.to(torch.float32)),
+                  idf.to(torch.float32))
+
+
+def make_queries(nq: int, corpus_idf: torch.Tensor, seed: int = 20261126, device="cpu", nnz_sparse: int = 30,
+                 nnz_bm25: int = 8) -> Queries:
+    device = torch.device(device)
+    g = _gen(seed, device)
+    x = torch.randn(nq, DIM, generator=g, device=device, dtype=torch.float32)
+    dense = x / x.norm(dim=1, keepdim=True)
+    s_off, s_idx = _zipf_rows(torch.full((nq,), nnz_sparse, dtype=torch.int64, device=device), SPARSE_VOCAB, 1.1, g, 4.0)
+    s_val = torch.exp(torch.randn(s_idx.numel(), generator=g, device=device) * 0.8 - 1.0).to(torch.float32)
+    b_off, b_idx = _zipf_rows(torch.full((nq,), nnz_bm25, dtype=torch.int64, device=device), BM25_VOCAB, 1.0, g, 4.0)
+    b_val = corpus_idf.to(device)[b_idx].to(torch.float32)
+    return Queries(dense, Csr(s_off.to(torch.int32), s_idx.to(torch.int32), s_val),
+                   Csr(b_off.to(torch.int32), b_idx.to(torch.int32), b_val))
+
+
+@dataclass
+class KnowledgeGraph:
+    e2e_off: torch.Tensor   # int32 [entities + 1]
+    e2e_idx: torch.Tensor
+    e2d_off: torch.Tensor
+    e2d_idx: torch.Tensor
+    qe_off: torch.Tensor    # int32 [nq + 1]
+    qe_idx: torch.Tensor
+
+
+def make_kg(n_docs: int, nq: int, entities: int = 500_000, seed: int = 20261127, device="cpu",
+            mean_degree: float = 4.0, alpha: float = 2.1) -> KnowledgeGraph:
+    """Entity graph with power-law out-degree (Pareto tail `alpha`, rescaled to the
+    requested mean), 1-5 uniformly drawn docs per entity, 1-3 seed entities per query."""
+    device = torch.device(device)
+    g = _gen(seed, device)
+    u = torch.rand(entities, generator=g, device=device, dtype=torch.float64).clamp_(min=1e-12)
+    raw = u.pow(-1.0 / (alpha - 1.0))                      # Pareto, x_min = 1
+    deg = torch.floor(raw * (mean_degree / float(raw.clamp(max=1000.0).mean()))).clamp_(0, 1000).to(torch.int64)
+    e2e_off = torch.zeros(entities + 1, dtype=torch.int64, device=device)
+    e2e_off[1:] = torch.cumsum(deg, 0)
+    e2e_idx = torch.randint(0, entities, (int(e2e_off[-1]),), generator=g, device=device)
+    nd = torch.randint(1, 6, (entities,), generator=g, device=device)
+    e2d_off = torch.zeros(entities + 1, dtype=torch.int64, device=device)
+    e2d_off[1:] = torch.cumsum(nd, 0)
+    e2d_idx = torch.randint(0, n_docs, (int(e2d_off[-1]),), generator=g, device=device)
+    ne = torch.randint(1, 4, (nq,), generator=g, device=device)
+    qe_off = torch.zeros(nq + 1, dtype=torch.int64, device=device)
+    qe_off[1:] = torch.cumsum(ne, 0)
+    qe_idx = torch.randint(0, entities, (int(qe_off[-1]),), generator=g, device=device)
+    i32 = lambda t: t.to(torch.int32)
+    return KnowledgeGraph(i32(e2e_off), i32(e2e_idx), i32(e2d_off), i32(e2d_idx), i32(qe_off), i32(qe_idx))
+
+
+def make_keywords(queries: Queries, seed: int = 20261128) -> list[list[int]]:
+    """1-4 required term ids per query, drawn from the query's own BM25 terms."""
+    rng = np.random.default_rng(seed)
+    off = queries.bm25.off.cpu().numpy().astype(np.int64)
+    idx = queries.bm25.idx.cpu().numpy().astype(np.int64)
+    out = []
+    for q in range(queries.nq):
+        row = idx[off[q]:off[q + 1]]
+        k = int(min(len(row), rng.integers(1, 5)))
+        out.append(sorted(int(t) for t in rng.choice(row, size=k, replace=False)))
+    return out
+
+
+# ---------------------------------------------------------------------------
+# File formats of the reference loaders
+# ---------------------------------------------------------------------------
+def write_fvecs(path: str, dense: torch.Tensor) -> None:
+    """Each row: int32 dim, then dim float32 (include/utils.cuh:361-378)."""
+    x = dense.detach().cpu().numpy().astype(np.float32)
+    n, d = x.shape
+    out = np.empty((n, d + 1), dtype=np.float32)
+    out[:, 0] = np.array([d], dtype=np.int32).view(np.float32)[0]
+    out[:, 1:] = x
+    out.tofile(path)
+
+
+def read_fvecs(path: str) -> np.ndarray:
+    raw = np.fromfile(path, dtype=np.float32)
+    d = int(raw[:1].view(np.int32)[0])
+    return raw.reshape(-1, d + 1)[:, 1:].copy()
+
+
+def write_csr(path: str, csr: Csr) -> None:
+    """u32 nnz | u32 off[rows+1] | u32 idx[nnz] | f32 val[nnz] (include/utils.cuh:380-398)."""
+    off = csr.off.cpu().numpy().astype(np.uint32)
+    with open(path, "wb") as f:
+        np.array([off[-1]], dtype=np.uint32).tofile(f)
+        off.tofile(f)
+        csr.idx.cpu().numpy().astype(np.uint32).tofile(f)
+        csr.val.cpu().numpy().astype(np.float32).tofile(f)
+
+
+def read_csr(path: str, rows: int) -> Csr:
+    raw = np.fromfile(path, dtype=np.uint32)
+    nnz = int(raw[0])
+    off = raw[1:rows + 2]
+    idx = raw[rows + 2:rows + 2 + nnz]
+    val = raw[rows + 2 + nnz:rows + 2 + 2 * nnz].view(np.float32)
+    t = lambda a, dt: torch.from_numpy(a.astype(dt))
+    return Csr(t(off, np.int32), t(idx, np.int32), torch.from_numpy(val.copy()))
+
+
+def write_kg_csr(path: str, off: torch.Tensor, idx: torch.Tensor) -> None:
+    """u32 n_off | u32 nnz | u32 off[n_off] | u32 idx[nnz] (src/query.cu:89-108)."""
+    o = off.cpu().numpy().astype(np.uint32)
+    with open(path, "wb") as f:
+        np.array([o.size, int(o[-1])], dtype=np.uint32).tofile(f)
+        o.tofile(f)
+        idx.cpu().numpy().astype(np.uint32).tofile(f)
+
+
+def write_keywords(path: str, kws: list[list[int]]) -> None:
+    with open(path, "w") as f:
+        for row in kws:
+            f.write(" ".join(str(t) for t in row) + "\n")
+
+
+def write_qrels(path: str, ids: np.ndarray) -> None:
+    with open(path, "w") as f:
+        for row in ids:
+            f.write(" ".join(str(int(t)) for t in row) + "\n")
+
+
+def write_poe(path: str, graph: np.ndarray, ep: np.ndarray) -> None:
+    """u32 width | u32 n_ep | u32 ep[n_ep] | n x (u32 width | u32 row[width]) (src/index.cu:928-939)."""
+    n, w = graph.shape
+    rows = np.empty((n, w + 1), dtype=np.uint32)
+    rows[:, 0] = w
+    rows[:, 1:] = graph
+    with open(path, "wb") as f:
+        np.array([w, ep.size], dtype=np.uint32).tofile(f)
+        ep.astype(np.uint32).tofile(f)
+        rows.tofile(f)
+
+
+def read_poe(path: str):
+    """Reader with the tolerance of src/query.cu:35-62."""
+    raw = np.fromfile(path, dtype=np.uint32)
+    w, n_ep = int(raw[0]), int(raw[1])
+    ep = raw[2:2 + n_ep].copy()
+    n = (raw.size - (n_ep + 1)) // (w + 1)   # the reference's own arithmetic (one header word is not subtracted)
+    body = raw[2 + n_ep:2 + n_ep + n * (w + 1)].reshape(n, w + 1)
+    return body[:, 1:].copy(), ep

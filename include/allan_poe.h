@@ -1,0 +1,217 @@
+/*
+ * allan_poe.h -- C ABI of the B200-native Allan-Poe hybrid graph index.
+ *
+ * Plain C: opaque handle, pointers and sizes only.  Every entry point returns
+ * AP_OK or an AP_ERR_* code; ap_last_error() gives the message of the calling
+ * thread's last failure.  Nothing here calls exit(): the reference ends the
+ * process on a missing file or a CUDA error (include/utils.cuh:344,363,382,
+ * src/index.cu:19-28, src/query.cu:23-32), this library reports it.
+ *
+ * "ref:" comments name the reference interface an entry point stands in for
+ * (paths relative to the reference project's root).
+ */
+#ifndef ALLAN_POE_H
+#define ALLAN_POE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define AP_OK 0
+#define AP_ERR_ARG 1    /* bad argument (null pointer, cands not a multiple of 32, ...) */
+#define AP_ERR_IO 2     /* file missing, truncated or malformed */
+#define AP_ERR_CUDA 3   /* CUDA runtime error */
+#define AP_ERR_LIMIT 4  /* a row or a pool exceeds a kernel capacity */
+#define AP_ERR_STATE 5  /* call out of order (search before a graph is set, ...) */
+#define AP_ERR_DEVICE 6 /* a kernel gave up on a bounded wait and raised its error word */
+
+#define AP_DIM 1024          /* dense dimension, ref: include/utils.cuh:31 */
+#define AP_ROW 40            /* index.poe row width, ref: src/index.cu:888,903 */
+#define AP_DEGREE 32         /* graph slots searched per row, ref: src/query.cu:6 */
+#define AP_KNN 64            /* k-NN list width before pruning, ref: src/index.cu:6 */
+#define AP_ENTRY_POINTS 32   /* ref: src/index.cu:923, src/query.cu:440-444 */
+#define AP_MAX_CANDS 512     /* ref: src/query.cu:9 */
+
+typedef struct ap_index ap_index;
+
+/* CSR triple; rows + 1 offsets.  Term ids of a row strictly ascending. */
+typedef struct {
+    const uint32_t *off;
+    const uint32_t *idx;
+    const float *val;
+} ap_csr;
+
+/* flags of ap_index_create_* */
+#define AP_CREATE_FOR_BUILD 1u /* also keep the build-time copy (dense x dense_scale) until the graph is built */
+
+/* ---- build ---------------------------------------------------------- */
+#define AP_BUILD_SIMT_JOIN 1u   /* local join on CUDA cores instead of tcgen05 (debug / cross-check) */
+#define AP_BUILD_KEEP_KNN 2u    /* keep the pre-pruning k-NN lists readable through ap_index_get_knn */
+
+typedef struct {
+    uint32_t iterations;   /* NN-Descent rounds; 0 = library default */
+    uint32_t seed;         /* random initial graph; the reference seeds from clock() (src/index.cu:102) */
+    uint32_t flags;        /* AP_BUILD_* */
+    float dense_scale;     /* build-time dense weight; 0 = 7.0 as in src/index.cu:836-840 */
+    uint32_t reserved[4];
+} ap_build_opts;
+
+typedef struct {
+    double seconds_total;      /* same span as the reference's "Indexing time" (src/index.cu:889-910) */
+    double seconds_knn;        /* NN-Descent part */
+    double seconds_prune;      /* detour count + RNG-IP prune + row assembly */
+    uint64_t distance_evals;   /* hybrid distances evaluated by the local joins */
+    uint64_t list_updates;     /* k-NN list entries replaced */
+    uint32_t iterations_run;
+    uint32_t launches;         /* kernels launched */
+    uint32_t reserved[4];
+} ap_build_stats;
+
+/* ---- search --------------------------------------------------------- */
+#define AP_SEARCH_KEYWORD 1u       /* bit 31 of query BM25 ids marks required terms (ref: src/query.cu:1828-1843,2005-2007) */
+#define AP_SEARCH_KG 2u            /* entity-seeded search with logical-edge augmentation (ref: src/query.cu:2042-2046) */
+#define AP_SEARCH_RAW_WEIGHTS 4u   /* use the weights as given, skip the auto-normalisation of src/query.cu:1847-1869 */
+#define AP_SEARCH_UNFUSED_DENSE 8u /* dense products and sums rounded separately (HMUL2 + HADD2) instead of HFMA2 */
+
+typedef struct {
+    uint32_t cands;        /* pool size, multiple of 32, 32..512 */
+    uint32_t flags;        /* AP_SEARCH_* */
+    float sparse_weight;
+    float bm25_weight;
+    float dense_weight;
+    float kg_weight;
+    uint32_t arena_bytes;  /* per-CTA staging arena for gathered rows; 0 = default */
+    uint32_t ctas_per_sm;  /* 0 = as many as fit */
+    uint32_t reserved[4];
+} ap_search_opts;
+
+typedef struct {
+    uint32_t nq;
+    const float *dense; /* nq x 1024, unscaled */
+    ap_csr sparse;
+    ap_csr bm25;
+    const uint32_t *ent_off; /* query -> entity CSR (KG search only, else NULL) */
+    const uint32_t *ent_idx;
+    uint32_t max_sparse_nnz; /* device-pointer calls: longest query row (0 = let the library read the offsets back) */
+    uint32_t max_bm25_nnz;
+} ap_queries;
+
+typedef struct {
+    float eff_sparse, eff_bm25, eff_dense; /* weights after auto-normalisation */
+    uint32_t path;             /* AP_PATH_* bit set actually searched */
+    double kernel_ms;          /* search kernel, CUDA events on the launch stream */
+    double total_ms;           /* host wall time of the call */
+    uint64_t expansions;       /* graph rows expanded, all queries */
+    uint64_t evaluations;      /* fused distances computed, all queries */
+    uint64_t gathered_bytes;   /* bytes of corpus rows + graph rows the kernel asked for */
+    uint32_t launches;         /* kernels launched by the call */
+    uint32_t h2d_bytes_lo, h2d_bytes_hi, d2h_bytes_lo, d2h_bytes_hi;
+    uint32_t reserved[3];
+} ap_search_stats;
+
+#define AP_PATH_DENSE 1u
+#define AP_PATH_SPARSE 2u
+#define AP_PATH_BM25 4u
+
+/* ---- errors ---------------------------------------------------------- */
+const char *ap_last_error(void);
+int ap_version(void);
+
+/* ---- file-level drop-ins --------------------------------------------- */
+/* ref: build_index_impl, include/hybrid_search.cuh:6-11, src/index.cu:810-941.
+ * Reads the three corpus files, builds the graph on `device`, writes index.poe
+ * (byte layout of src/index.cu:928-939) and prints "Indexing time: <s>s". */
+int ap_build_index(const char *dense_data_path, const char *sparse_data_path, const char *bm25_data_path,
+                   const char *output_graph_path, int device, const ap_build_opts *opts, ap_build_stats *stats);
+
+/* ref: search_index_impl, include/hybrid_search.cuh:14-33, src/query.cu:1781-2080.
+ * Empty string = feature off for keyword_id_path / knowledge_path.  Prints
+ * "Query time: <s>s" and "nDCG@10: <v>".  max_queries = 0 searches every query
+ * in the files (the reference hard-codes 100, src/query.cu:1825).  out_ids /
+ * out_dis (nullable) receive nq x cands results; *out_nq the query count. */
+int ap_search_index(const char *dense_data_path, const char *dense_query_path, const char *sparse_data_path,
+                    const char *sparse_query_path, const char *bm25_data_path, const char *bm25_query_path,
+                    const char *keyword_id_path, const char *knowledge_path, const char *entity2doc_path,
+                    const char *query_entity_path, const char *graph_path, const char *ground_truth_path, int top_k,
+                    int cands, float sparse_weight, float bm25_weight, float dense_weight, float kg_weight, int device,
+                    uint32_t max_queries, uint32_t *out_ids, float *out_dis, uint32_t *out_nq, double *out_ndcg,
+                    ap_search_stats *stats);
+
+/* ---- resident index --------------------------------------------------- */
+/* Corpus in host memory (ref: the uploads of src/query.cu:1901-1934). */
+int ap_index_create_host(ap_index **out, int device, uint32_t n, const float *dense, ap_csr sparse, ap_csr bm25,
+                         uint32_t flags);
+/* Corpus already in device memory of `device` (same layouts). */
+int ap_index_create_device(ap_index **out, int device, uint32_t n, const float *dense, ap_csr sparse, ap_csr bm25,
+                           uint32_t flags);
+int ap_index_destroy(ap_index *ix);
+uint32_t ap_index_size(const ap_index *ix);
+
+/* Graph in, out, to and from index.poe (ref: src/index.cu:928-939, load_graph src/query.cu:35-62). */
+int ap_index_set_graph(ap_index *ix, const uint32_t *rows /* n x 40, host */, const uint32_t *entry_points /* 32 */);
+int ap_index_get_graph(const ap_index *ix, uint32_t *rows, uint32_t *entry_points);
+int ap_index_load_graph(ap_index *ix, const char *path);
+int ap_index_save_graph(const ap_index *ix, const char *path);
+
+/* ref: the kernel sequence of src/index.cu:890-903 (NN-Descent, reverse merge, allan_poe, allan_poe_final_graph)
+ * plus entry-point selection (src/index.cu:916-925).  Needs AP_CREATE_FOR_BUILD. */
+int ap_index_build(ap_index *ix, const ap_build_opts *opts, ap_build_stats *stats);
+
+/* Pre-pruning k-NN lists of the last build (AP_BUILD_KEEP_KNN): n x 64 ids, distances, n norms. */
+int ap_index_get_knn(const ap_index *ix, uint32_t *ids, float *dis, float *power);
+
+/* ref: cal_power, src/index.cu:483-534 (on the build-time copy).  out: n floats, host. */
+int ap_index_norms(ap_index *ix, float *out);
+
+/* ref: allan_poe + allan_poe_final_graph, src/index.cu:539-807, on caller-supplied k-NN lists (host, n x 64 ids
+ * ascending by distance, n x 64 distances, n norms).  Writes the forward lists (n x 32), keyword-edge lists
+ * (n x 33: count + 32 ids) and final rows (n x 40) to host memory; any output may be NULL.  Also installs the rows
+ * and the entry points derived from `power` as the index's graph. */
+int ap_index_prune(ap_index *ix, const uint32_t *knn_ids, const float *knn_dis, const float *power,
+                   uint32_t *new_list, uint32_t *keyword_edges, uint32_t *rows);
+
+/* Knowledge graph for AP_SEARCH_KG (ref: load_kg_graph src/query.cu:89-108 and the uploads of :1963-1980).
+ * Host pointers; entity->entity and entity->doc CSRs over n_entities rows. */
+int ap_index_set_kg(ap_index *ix, uint32_t n_entities, const uint32_t *e2e_off, const uint32_t *e2e_idx,
+                    const uint32_t *e2d_off, const uint32_t *e2d_idx);
+
+/* ref: the weight auto-normalisation of src/query.cu:1847-1869.  Host query buffers.  In/out weights. */
+int ap_effective_weights(const ap_index *ix, const ap_queries *q, float *sparse_weight, float *bm25_weight,
+                         float *dense_weight);
+
+/* ref: one search_index call's kernel phase, src/query.cu:1999-2054, with results returned.
+ * Host query buffers in, host results out (nq x cands ids and fused distances, best first). */
+int ap_search_host(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids, float *out_dis,
+                   ap_search_stats *stats);
+/* Same with every query and result pointer in device memory; `stream` is a cudaStream_t (NULL = default stream).
+ * Weights are used as given unless the host-side normalisation sample is available (see AP_SEARCH_RAW_WEIGHTS).
+ * Asynchronous with respect to the host unless stats != NULL. */
+int ap_search_device(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids, float *out_dis,
+                     void *stream, ap_search_stats *stats);
+
+/* Fused distances of explicit (query, doc) pairs with the search kernel's arithmetic (test hook).
+ * Host buffers; weights are applied as given (no normalisation). */
+int ap_fused_distances(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, size_t n_pairs,
+                       const uint32_t *pair_query, const uint32_t *pair_doc, float *out);
+
+/* ref: cal_precision, src/query.cu:111-145.  results: nq x stride ids (first top_k used); qrels: CSR of relevant ids. */
+double ap_ndcg(uint32_t nq, const uint32_t *results, uint32_t stride, uint32_t top_k, const uint32_t *qrel_off,
+               const uint32_t *qrel_ids);
+
+/* Merge per-shard result lists into a global top-k on the device (corpus-sharded search).
+ * in_ids/in_dis: shards x nq x per_shard (ids already global), device; out: nq x top_k, device. */
+int ap_merge_shard_results(int device, uint32_t shards, uint32_t nq, uint32_t per_shard, const uint32_t *in_ids,
+                           const float *in_dis, uint32_t top_k, uint32_t *out_ids, float *out_dis, void *stream);
+
+/* Test hook for the dense half of the NN-Descent local join: inner products of the dense rows of the given
+ * participant lists (host: nodes x 64 ids; nodes x 2 counts = new rows, rows), computed by the tcgen05 kernel
+ * (use_tc != 0) or by the CUDA-core kernel.  out: nodes x 64 x 32 floats, host.  Needs AP_CREATE_FOR_BUILD. */
+int ap_debug_join_dense(ap_index *ix, uint32_t nodes, const uint32_t *plist, const uint32_t *pcnt, int use_tc, float *out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* ALLAN_POE_H */

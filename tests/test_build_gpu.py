@@ -1,0 +1,124 @@
+"""Build-side parity on the GPU: norms, pruning and row assembly bit-exact against the oracle; the tensor-core
+join against the CUDA-core join; end-to-end build quality."""
+import numpy as np
+import pytest
+
+import apoe
+import apoe_oracle as orc
+import helpers
+import synth
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def bix(tiny):
+    ix = apoe.Index.from_host(tiny.D, tiny.S, tiny.B, for_build=True)
+    yield ix
+    ix.close()
+
+
+def test_norms_match_oracle_bitwise(tiny, bix):
+    got = bix.norms()
+    assert np.array_equal(got.view(np.uint32), tiny.power.view(np.uint32))
+
+
+def test_prune_and_rows_match_oracle_bitwise(tiny, bix):
+    """Same pre-pruning k-NN lists in -> same forward lists, keyword-edge lists and 40-wide rows out."""
+    new_list, kw, rows = bix.prune(tiny.knn, tiny.knn_dis, tiny.power)
+    assert np.array_equal(new_list, tiny.new_list)
+    assert np.array_equal(kw, tiny.kw_edge)
+    assert np.array_equal(rows, tiny.graph)
+    g, ep = bix.get_graph()
+    assert np.array_equal(g, tiny.graph) and np.array_equal(ep, tiny.ep)
+
+
+def test_prune_on_perturbed_lists(tiny, bix):
+    """Lists with repeated ids and ties (what NN-Descent can leave behind) still match the oracle."""
+    rng = np.random.default_rng(1)
+    knn = tiny.knn.copy()
+    dis = tiny.knn_dis.copy()
+    rows = rng.integers(0, tiny.n, 60)
+    knn[rows, 40] = knn[rows, 10]
+    dis[rows, 40] = dis[rows, 39]
+    want = orc.prune(tiny.D7h, tiny.S, tiny.B, knn, dis, tiny.power)
+    got = bix.prune(knn, dis, tiny.power)
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1]) and np.array_equal(got[2], want[2])
+
+
+def _join_lists(n, nodes, rng):
+    plist = np.full((nodes, 64), 0xFFFFFFFF, dtype=np.uint32)
+    pcnt = np.zeros((nodes, 2), dtype=np.uint32)
+    for v in range(nodes):
+        nn = int(rng.integers(1, 33))
+        rows = nn + int(rng.integers(0, 33))
+        plist[v, :rows] = rng.choice(n, size=rows, replace=False)
+        pcnt[v] = (nn, rows)
+    return plist, pcnt
+
+
+def test_dense_join_simt_matches_numpy(tiny, bix):
+    rng = np.random.default_rng(5)
+    plist, pcnt = _join_lists(tiny.n, 37, rng)
+    got = bix.debug_join_dense(plist, pcnt, use_tc=False)
+    X = orc.h2f(tiny.D7h).astype(np.float64)
+    for v in range(plist.shape[0]):
+        nn, rows = pcnt[v]
+        P = X[plist[v, :rows].astype(np.int64)]
+        want = P @ P[:nn].T
+        assert np.allclose(got[v, :rows, :nn], want, rtol=1e-5, atol=1e-4)
+
+
+def test_dense_join_tensor_core_matches_simt(tiny, bix):
+    """tcgen05 tiles against the CUDA-core kernel: exact half products, fp32 accumulation in both."""
+    rng = np.random.default_rng(6)
+    plist, pcnt = _join_lists(tiny.n, 301, rng)   # odd count: the last tile holds one node
+    ref = bix.debug_join_dense(plist, pcnt, use_tc=False)
+    got = bix.debug_join_dense(plist, pcnt, use_tc=True)
+    for v in range(plist.shape[0]):
+        nn, rows = pcnt[v]
+        assert np.allclose(got[v, :rows, :nn], ref[v, :rows, :nn], rtol=1e-5, atol=2e-4), v
+
+
+@pytest.mark.parametrize("simt", [True, False])
+def test_build_quality(simt):
+    """NN-Descent + pruning on 6 000 documents: k-NN recall against exact lists, search recall against brute force."""
+    ds = helpers.make_dataset(6000, 100, seed=21, with_graph=False)
+    ix = apoe.Index.from_host(ds.D, ds.S, ds.B, for_build=True)
+    st = ix.build(flags=apoe.BUILD_KEEP_KNN | (apoe.BUILD_SIMT_JOIN if simt else 0), seed=3)
+    ids, dis, power = ix.get_knn()
+    assert np.all(np.diff(dis, axis=1) >= 0)
+    knn, _ = helpers.exact_knn(ds.D, ds.S, ds.B)
+    rec = np.mean([len(set(ids[i, :32].tolist()) & set(knn[i, :32].tolist())) / 32 for i in range(0, ds.n, 7)])
+    assert rec >= 0.80, rec
+    want_power = orc.cal_power(ds.D7h, ds.S, ds.B)
+    assert np.array_equal(power.view(np.uint32), want_power.view(np.uint32))
+    rows, ep = ix.get_graph()
+    assert np.array_equal(ep, orc.entry_points(want_power))
+    # the rows are what the oracle makes of the same k-NN lists
+    want = orc.prune(ds.D7h, ds.S, ds.B, ids, dis, power)
+    assert np.array_equal(rows, want[2])
+    eff, qdh, qs, qb, qd = helpers.scaled_queries(ds)
+    gt, _, _ = orc.bruteforce(ds.D, ds.S, ds.B, qd, qs, qb, 7, 10)
+    got, _, _ = ix.search(ds.QD, ds.QS, ds.QB, cands=128)
+    assert helpers.recall_at(got, gt) >= 0.80
+    assert st.iterations_run >= 1 and st.distance_evals > 0
+    ix.close()
+
+
+def test_build_index_file_round_trip(tiny, tmp_path):
+    p = lambda s: str(tmp_path / s)
+    synth.write_fvecs(p("d.fvecs"), tiny.corpus.dense)
+    synth.write_csr(p("s.bin"), tiny.corpus.sparse)
+    synth.write_csr(p("b.bin"), tiny.corpus.bm25)
+    st = apoe.build_index(p("d.fvecs"), p("s.bin"), p("b.bin"), p("index.poe"), seed=1)
+    rows, ep = synth.read_poe(p("index.poe"))
+    assert rows.shape == (tiny.n, 40) and ep.shape == (32,)
+    assert rows[:, :32].max() < tiny.n and rows[:, 32].max() <= 7
+    import os
+    assert os.path.getsize(p("index.poe")) == 8 + 128 + tiny.n * 164
+    ix = apoe.Index.from_host(tiny.D, tiny.S, tiny.B)
+    ix.load_graph(p("index.poe"))
+    g2, ep2 = ix.get_graph()
+    assert np.array_equal(g2, rows) and np.array_equal(ep2, ep)
+    ix.close()

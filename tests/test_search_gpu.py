@@ -1,0 +1,189 @@
+"""Search parity on the GPU: the CUDA kernel against the CPU restatement of the reference, bit for bit."""
+import numpy as np
+import pytest
+
+import apoe
+import apoe_oracle as orc
+import helpers
+import synth
+
+pytestmark = pytest.mark.gpu
+
+PATHS = {  # name -> (weights (sparse, bm25, dense), oracle flags)
+    "three": ((1.0, 1.0, 1.0), 7),
+    "dense": ((0.0, 0.0, 1.0), 1),
+    "sparse": ((1.0, 0.0, 0.0), 2),
+    "bm25": ((0.0, 1.0, 0.0), 4),
+    "dense_sparse": ((1.0, 0.0, 1.0), 3),
+    "dense_bm25": ((0.0, 1.0, 1.0), 5),
+    "sparse_bm25": ((1.0, 1.0, 0.0), 6),
+    "skewed": ((1.0, 2.0, 0.5), 7),
+}
+
+
+@pytest.fixture(scope="module")
+def index(small):
+    ix = apoe.Index.from_host(small.D, small.S, small.B)
+    ix.set_graph(small.graph, small.ep)
+    yield ix
+    ix.close()
+
+
+def test_fused_distances_match_oracle_bitwise(small, index):
+    rng = np.random.default_rng(3)
+    pq = rng.integers(0, small.nq, 4000).astype(np.uint32)
+    pd = rng.integers(0, small.n, 4000).astype(np.uint32)
+    for name, (w, flags) in PATHS.items():
+        eff, qdh, qs, qb, _ = helpers.scaled_queries(small, w, normalise=False)
+        want = orc.fused_distances(small.Dh, small.S, small.B, qdh, qs, qb, pq, pd, flags)
+        got = index.fused_distances(small.QD, small.QS, small.QB, pq, pd, weights=w)
+        assert np.array_equal(got.view(np.uint32), want.view(np.uint32)), name
+    # the separately rounded multiply / add variant
+    eff, qdh, qs, qb, _ = helpers.scaled_queries(small, (1.0, 1.0, 1.0), normalise=False)
+    want = orc.fused_distances(small.Dh, small.S, small.B, qdh, qs, qb, pq, pd, 7 | orc.F_UNFUSED_DENSE)
+    got = index.fused_distances(small.QD, small.QS, small.QB, pq, pd, flags=apoe.SEARCH_UNFUSED_DENSE)
+    assert np.array_equal(got.view(np.uint32), want.view(np.uint32))
+
+
+@pytest.mark.parametrize("name", list(PATHS))
+def test_search_matches_oracle_bitwise(small, index, name):
+    """Whole pool (cands ids and distances per query) equal to the oracle's, for every weight subset."""
+    w, flags = PATHS[name]
+    eff, qdh, qs, qb, _ = helpers.scaled_queries(small, w)
+    want_ids, want_dis, cnt = orc.search(small.Dh, small.S, small.B, qdh, qs, qb, small.graph, small.ep, 128, flags)
+    ids, dis, st = index.search(small.QD, small.QS, small.QB, cands=128, weights=w)
+    assert np.allclose([st.eff_sparse, st.eff_bm25, st.eff_dense], eff, rtol=0, atol=0)
+    assert st.path == flags
+    assert np.array_equal(ids, want_ids)
+    assert np.array_equal(dis.view(np.uint32), want_dis.view(np.uint32))
+    assert st.expansions == int(cnt[:, 0].sum()) and st.evaluations == int(cnt[:, 1].sum())
+
+
+@pytest.mark.parametrize("cands", [32, 64, 256, 512])
+def test_pool_sizes(small, index, cands):
+    eff, qdh, qs, qb, _ = helpers.scaled_queries(small, (1.0, 1.0, 1.0))
+    sub = slice(0, 48)
+    want_ids, want_dis, _ = orc.search(small.Dh, small.S, small.B, qdh[sub], orc.CsrNp(*_rows(qs, 48)), orc.CsrNp(*_rows(qb, 48)),
+                                       small.graph, small.ep, cands, 7)
+    q = small.queries.slice(0, 48)
+    ids, dis, _ = index.search(q.dense.numpy(), q.sparse, q.bm25, cands=cands, weights=(eff[0], eff[1], eff[2]),
+                               flags=apoe.SEARCH_RAW_WEIGHTS)
+    assert np.array_equal(ids, want_ids)
+    assert np.array_equal(dis.view(np.uint32), want_dis.view(np.uint32))
+
+
+def _rows(c, k):
+    e = int(c.off[k])
+    return c.off[:k + 1], c.idx[:e], c.val[:e]
+
+
+def test_small_arena_batches_give_same_result(small, index):
+    """Forcing the record gathers through many small arena batches must not change anything."""
+    ids0, dis0, _ = index.search(small.QD, small.QS, small.QB, cands=128)
+    ids1, dis1, _ = index.search(small.QD, small.QS, small.QB, cands=128, arena_bytes=8192, ctas_per_sm=1)
+    assert np.array_equal(ids0, ids1) and np.array_equal(dis0.view(np.uint32), dis1.view(np.uint32))
+
+
+def test_recall_against_exact_bruteforce(small, index):
+    eff, qdh, qs, qb, qd = helpers.scaled_queries(small, (1.0, 1.0, 1.0))
+    gt, _, _ = orc.bruteforce(small.D, small.S, small.B, qd, qs, qb, 7, 10)
+    ids, _, _ = index.search(small.QD, small.QS, small.QB, cands=128)
+    assert helpers.recall_at(ids, gt) >= 0.85
+
+
+def test_keyword_search_matches_oracle(small, index):
+    kws = synth.make_keywords(small.queries, seed=5)
+    qb_idx = small.QB.idx.copy()
+    for q, req in enumerate(kws):
+        for j in range(int(small.QB.off[q]), int(small.QB.off[q + 1])):
+            if int(qb_idx[j]) in req:
+                qb_idx[j] |= np.uint32(0x80000000)
+    QBk = orc.CsrNp(small.QB.off, qb_idx, small.QB.val)
+    ws, wb, wd = orc.effective_weights(small.D, small.S, small.B, small.QD, small.QS, QBk, 1.0, 1.0, 1.0)
+    qd, qs, qb = orc.scale_queries(small.QD, small.QS, QBk, ws, wb, wd)
+    want_ids, want_dis, _ = orc.search(small.Dh, small.S, small.B, orc.f2h(qd), qs, qb, small.graph, small.ep, 128,
+                                       7 | orc.F_KEYWORD)
+    ids, dis, st = index.search(small.QD, small.QS, QBk, cands=128, flags=apoe.SEARCH_KEYWORD)
+    assert np.array_equal(ids, want_ids)
+    assert np.array_equal(dis.view(np.uint32), want_dis.view(np.uint32))
+    # keyword hits come first: every result before the first non-hit contains a required term
+    hit = 0
+    for q in range(small.nq):
+        d = int(ids[q, 0])
+        if d < small.n:
+            terms = set(small.B.idx[small.B.off[d]:small.B.off[d + 1]].tolist())
+            hit += bool(terms & set(kws[q]))
+    assert hit >= small.nq // 2
+
+
+def test_kg_search_matches_oracle(small, index):
+    kg = synth.make_kg(small.n, small.nq, entities=5000, seed=9)
+    index.set_kg(kg.e2e_off, kg.e2e_idx, kg.e2d_off, kg.e2d_idx)
+    eff, qdh, qs, qb, _ = helpers.scaled_queries(small, (1.0, 1.0, 1.0))
+    arrs = [t.numpy().view(np.uint32) for t in (kg.e2e_off, kg.e2e_idx, kg.e2d_off, kg.e2d_idx, kg.qe_off, kg.qe_idx)]
+    want_ids, want_dis, _ = orc.search(small.Dh, small.S, small.B, qdh, qs, qb, small.graph, small.ep, 128, 7 | orc.F_KG,
+                                       kg=arrs, kg_weight=40.0)
+    ids, dis, st = index.search(small.QD, small.QS, small.QB, cands=128, kg_weight=40.0, ent=(arrs[4], arrs[5]))
+    assert np.array_equal(ids, want_ids)
+    assert np.array_equal(dis.view(np.uint32), want_dis.view(np.uint32))
+
+
+def test_device_pointer_path_equals_host_path(small, index):
+    import torch
+    dev = torch.device("cuda:0")
+    q = small.queries
+    qd = synth.Queries(q.dense.to(dev), q.sparse.to(dev), q.bm25.to(dev))
+    eff = index.effective_weights(small.QD, small.QS, small.QB)
+    out_ids = torch.empty(small.nq, 128, dtype=torch.int32, device=dev)
+    out_dis = torch.empty(small.nq, 128, dtype=torch.float32, device=dev)
+    index.search_device(qd, out_ids, out_dis, cands=128, weights=eff, max_nnz=(30, 8))
+    torch.cuda.synchronize()
+    ids, dis, _ = index.search(small.QD, small.QS, small.QB, cands=128)
+    assert np.array_equal(out_ids.cpu().numpy().view(np.uint32), ids)
+    assert np.array_equal(out_dis.cpu().numpy().view(np.uint32), dis.view(np.uint32))
+
+
+def test_argument_errors(small, index):
+    with pytest.raises(apoe.ApoeError) as e:
+        index.search(small.QD, small.QS, small.QB, cands=100)
+    assert e.value.code == 1
+    with pytest.raises(apoe.ApoeError):
+        index.search(small.QD, small.QS, small.QB, cands=128, weights=(0.0, 0.0, 0.0))
+    bad = small.graph.copy()
+    bad[5, 3] = small.n + 10
+    with pytest.raises(apoe.ApoeError):
+        index.set_graph(bad, small.ep)
+    index.set_graph(small.graph, small.ep)
+    ix2 = apoe.Index.from_host(small.D[:100], helpers.orc.CsrNp(*_rows(small.S, 100)), helpers.orc.CsrNp(*_rows(small.B, 100)))
+    with pytest.raises(apoe.ApoeError) as e:
+        ix2.search(small.QD, small.QS, small.QB)
+    assert e.value.code == 5
+    ix2.close()
+
+
+def test_file_level_drop_in(small, tmp_path):
+    """hybrid_search-style call over the reference's file formats gives the same results as the resident index."""
+    p = lambda s: str(tmp_path / s)
+    synth.write_fvecs(p("d.fvecs"), small.corpus.dense)
+    synth.write_fvecs(p("q.fvecs"), small.queries.dense)
+    synth.write_csr(p("s.bin"), small.corpus.sparse)
+    synth.write_csr(p("b.bin"), small.corpus.bm25)
+    synth.write_csr(p("qs.bin"), small.queries.sparse)
+    synth.write_csr(p("qb.bin"), small.queries.bm25)
+    synth.write_poe(p("index.poe"), small.graph, small.ep)
+    eff, qdh, qs, qb, qd = helpers.scaled_queries(small)
+    gt, _, _ = orc.bruteforce(small.D, small.S, small.B, qd, qs, qb, 7, 10)
+    synth.write_qrels(p("qrels.txt"), gt)
+    ids, dis, ndcg, st = apoe.search_index(p("d.fvecs"), p("q.fvecs"), p("s.bin"), p("qs.bin"), p("b.bin"), p("qb.bin"), "",
+                                           "", "", "", p("index.poe"), p("qrels.txt"), 10, 128, 1.0, 1.0, 1.0, 0.0)
+    want_ids, want_dis, _ = orc.search(small.Dh, small.S, small.B, qdh, qs, qb, small.graph, small.ep, 128, 7)
+    assert np.array_equal(ids, want_ids)
+    assert 0.5 < ndcg <= 1.0
+    import build as apoe_build, importlib, sys, os
+    sys.path.insert(0, os.path.dirname(apoe_build.module_path()))
+    hs = importlib.import_module("hybrid_search")
+    hs.search_index(dense_data_path=p("d.fvecs"), dense_query_path=p("q.fvecs"), sparse_data_path=p("s.bin"),
+                    sparse_query_path=p("qs.bin"), bm25_data_path=p("b.bin"), bm25_query_path=p("qb.bin"),
+                    keyword_id_path="", knowledge_path="", entity2doc_path="", query_entity_path="",
+                    graph_path=p("index.poe"), ground_truth_path=p("qrels.txt"), top_k=10, cands=128,
+                    sparse_weight=1.0, bm25_weight=1.0, dense_weight=1.0, kg_weight=0.0)
