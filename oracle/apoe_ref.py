@@ -1,0 +1,77 @@
+"""ctypes binding of oracle/_ref/libapoe_ref.so: the reference's own CUDA kernels behind a small harness.
+
+TEST / BASELINE INFRASTRUCTURE ONLY.  The library is compiled from the reference tree where it is mounted
+(`make -C oracle ref`); on a GPU box only the prebuilt file is used.  It needs a CUDA device.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import os
+
+import numpy as np
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB = None
+
+
+def lib_path() -> str:
+    return os.path.join(_HERE, "_ref", "libapoe_ref.so")
+
+
+def available() -> bool:
+    return os.path.exists(lib_path())
+
+
+def lib() -> C.CDLL:
+    global _LIB
+    if _LIB is None:
+        _LIB = C.CDLL(lib_path())
+    return _LIB
+
+
+def _p(a, dt):
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.int32 and dt == np.uint32:
+        a = a.view(np.uint32)
+    assert a.dtype == dt, (a.dtype, dt)
+    return a, C.c_void_p(a.ctypes.data)
+
+
+def build(dense, s, b):
+    """dense: fp32 [n, 1024] unscaled; s, b: (off, idx, val).  Returns a dict of the reference's build state."""
+    keep = []
+    def arg(a, dt):
+        arr, ptr = _p(a, dt); keep.append(arr); return ptr
+    n = dense.shape[0]
+    out = dict(knn=np.empty((n, 64), np.uint32), knn_dis=np.empty((n, 64), np.float32), power=np.empty(n, np.float32),
+               new_list=np.empty((n, 32), np.uint32), kw=np.empty((n, 33), np.uint32), graph=np.empty((n, 40), np.uint32),
+               ep=np.empty(32, np.uint32))
+    sec = C.c_double(0)
+    rc = lib().ref_build(C.c_uint(n), arg(dense, np.float32), arg(s[0], np.uint32), arg(s[1], np.uint32), arg(s[2], np.float32),
+                         arg(b[0], np.uint32), arg(b[1], np.uint32), arg(b[2], np.float32),
+                         *[C.c_void_p(out[k].ctypes.data) for k in ("knn", "knn_dis", "power", "new_list", "kw", "graph", "ep")],
+                         C.byref(sec))
+    if rc != 0:
+        raise RuntimeError(f"ref_build failed with {rc}")
+    out["seconds"] = sec.value
+    return out
+
+
+def search(dense, s, b, qdense_scaled, qs, qb, graph, ep, cands, mode):
+    """Queries already scaled by the effective weights (fp32).  Returns ids, dis, seconds_total, seconds_search."""
+    keep = []
+    def arg(a, dt):
+        arr, ptr = _p(a, dt); keep.append(arr); return ptr
+    n, nq = dense.shape[0], qdense_scaled.shape[0]
+    ids = np.empty((nq, cands), np.uint32)
+    dis = np.empty((nq, cands), np.float32)
+    t_all, t_search = C.c_double(0), C.c_double(0)
+    rc = lib().ref_search(C.c_uint(n), arg(dense, np.float32), arg(s[0], np.uint32), arg(s[1], np.uint32), arg(s[2], np.float32),
+                          arg(b[0], np.uint32), arg(b[1], np.uint32), arg(b[2], np.float32), C.c_uint(nq),
+                          arg(qdense_scaled, np.float32), arg(qs[0], np.uint32), arg(qs[1], np.uint32), arg(qs[2], np.float32),
+                          arg(qb[0], np.uint32), arg(qb[1], np.uint32), arg(qb[2], np.float32), arg(graph, np.uint32),
+                          arg(ep, np.uint32), C.c_uint(cands), C.c_int(mode), C.c_void_p(ids.ctypes.data),
+                          C.c_void_p(dis.ctypes.data), C.byref(t_all), C.byref(t_search))
+    if rc != 0:
+        raise RuntimeError(f"ref_search failed with {rc}")
+    return ids, dis, t_all.value, t_search.value

@@ -1,0 +1,89 @@
+// TEST / BASELINE INFRASTRUCTURE ONLY.
+//
+// Drives the reference's own search kernels, compiled unmodified from the reference tree (`#include "query.cu"`),
+// and returns what they compute -- the reference's search_index_impl prints an nDCG figure and discards the
+// results (src/query.cu:2053-2080) and searches only the first 100 queries (src/query.cu:1825).  The device phase
+// below is the one of src/query.cu:1901-2054: fp32 uploads, f2h of corpus and queries inside the timed region, one
+// kernel of <<<queries, (32, 6)>>>.  Queries arrive already weight-scaled (src/query.cu:1871-1881 is host code that
+// the caller reproduces).  The knowledge-graph kernel is not reachable from here: it indexes shared memory with a
+// variable that is never assigned (kg_cur_id, src/query.cu:1559,1694) and must not be run on a shared GPU.
+#include "query.cu"
+
+// mode: bit 0 dense, bit 1 sparse, bit 2 bm25 (which of the reference's seven subset kernels), bit 3 keyword kernel
+extern "C" int ref_search(unsigned points_num, const float *data_load, const unsigned *sparse_off, const unsigned *sparse_idx,
+                          const float *sparse_val, const unsigned *bm25_off, const unsigned *bm25_idx, const float *bm25_val,
+                          unsigned query_num, const float *query_load, const unsigned *sparse_off_query,
+                          const unsigned *sparse_idx_query, const float *sparse_val_query, const unsigned *bm25_off_query,
+                          const unsigned *bm25_idx_query, const float *bm25_val_query, const unsigned *graph /* n x 40 */,
+                          const unsigned *ent_pts /* 32 */, unsigned cands, int mode, unsigned *out_ids, float *out_dis,
+                          double *seconds_total, double *seconds_search_only) {
+    if (cands > MAX_CAND_POOL || cands % 32 != 0 || cands == 0) return 1;
+    const unsigned dim = DIM, non_zero_num = sparse_off[points_num], bm25_non_zero = bm25_off[points_num];
+    const unsigned query_non_zero_num = sparse_off_query[query_num], query_bm25_non_zero = bm25_off_query[query_num];
+    unsigned *graph_dev, *ent_pts_dev, *sparse_off_dev, *sparse_idx_dev, *bm25_off_dev, *bm25_idx_dev;
+    unsigned *sparse_off_query_dev, *sparse_idx_query_dev, *bm25_off_query_dev, *bm25_idx_query_dev, *query_results_dev;
+    float *data_dev, *sparse_val_dev, *bm25_val_dev, *query_data_dev, *sparse_val_query_dev, *bm25_val_query_dev, *query_dis_dev;
+    half *data_half_dev, *query_data_half_dev;
+#define UP(dst, src, count, type)                                   \
+    cudaMalloc((void **)&dst, std::max<size_t>((size_t)(count), 1) * sizeof(type)); \
+    cudaMemcpy(dst, src, (size_t)(count) * sizeof(type), cudaMemcpyHostToDevice);
+    UP(graph_dev, graph, (size_t)points_num * (K + KEYEDGE), unsigned)
+    UP(ent_pts_dev, ent_pts, K, unsigned)
+    UP(data_dev, data_load, (size_t)points_num * dim, float)
+    cudaMalloc((void **)&data_half_dev, (size_t)points_num * dim * sizeof(half));
+    UP(sparse_off_dev, sparse_off, points_num + 1, unsigned)
+    UP(sparse_idx_dev, sparse_idx, non_zero_num, unsigned)
+    UP(sparse_val_dev, sparse_val, non_zero_num, float)
+    UP(bm25_off_dev, bm25_off, points_num + 1, unsigned)
+    UP(bm25_idx_dev, bm25_idx, bm25_non_zero, unsigned)
+    UP(bm25_val_dev, bm25_val, bm25_non_zero, float)
+    UP(query_data_dev, query_load, (size_t)query_num * dim, float)
+    cudaMalloc((void **)&query_data_half_dev, (size_t)query_num * dim * sizeof(half));
+    UP(sparse_off_query_dev, sparse_off_query, query_num + 1, unsigned)
+    UP(sparse_idx_query_dev, sparse_idx_query, query_non_zero_num, unsigned)
+    UP(sparse_val_query_dev, sparse_val_query, query_non_zero_num, float)
+    UP(bm25_off_query_dev, bm25_off_query, query_num + 1, unsigned)
+    UP(bm25_idx_query_dev, bm25_idx_query, query_bm25_non_zero, unsigned)
+    UP(bm25_val_query_dev, bm25_val_query, query_bm25_non_zero, float)
+#undef UP
+    cudaMalloc((void **)&query_results_dev, (size_t)query_num * cands * sizeof(unsigned));
+    cudaMalloc((void **)&query_dis_dev, (size_t)query_num * cands * sizeof(float));
+    if (cudaGetLastError() != cudaSuccess) return 2;
+    dim3 grid_s(query_num, 1, 1), block_s(32, 6, 1);
+    cudaDeviceSynchronize();
+    auto start = std::chrono::high_resolution_clock::now();
+    f2h<<<points_num, 256>>>(data_dev, data_half_dev, points_num);
+    f2h<<<query_num, 256>>>(query_data_dev, query_data_half_dev, query_num);
+    cudaDeviceSynchronize();
+    auto mid = std::chrono::high_resolution_clock::now();
+#define ARGS graph_dev, data_half_dev, query_data_half_dev, query_results_dev, query_dis_dev, ent_pts_dev, sparse_off_dev, sparse_idx_dev, \
+             sparse_val_dev, bm25_off_dev, bm25_idx_dev, bm25_val_dev, sparse_off_query_dev, sparse_idx_query_dev, sparse_val_query_dev,   \
+             bm25_off_query_dev, bm25_idx_query_dev, bm25_val_query_dev, cands
+    int rc = 0;
+    switch (mode) {
+        case 8 | 7: search_with_keyword<<<grid_s, block_s>>>(ARGS); break;
+        case 7: search_with_three_paths<<<grid_s, block_s>>>(ARGS); break;
+        case 3: search_with_dense_and_sparse<<<grid_s, block_s>>>(ARGS); break;
+        case 5: search_with_bm25_and_dense<<<grid_s, block_s>>>(ARGS); break;
+        case 6: search_with_sparse_and_bm25<<<grid_s, block_s>>>(ARGS); break;
+        case 2: search_with_sparse<<<grid_s, block_s>>>(ARGS); break;
+        case 4: search_with_bm25<<<grid_s, block_s>>>(ARGS); break;
+        case 1: search_with_dense<<<grid_s, block_s>>>(graph_dev, data_half_dev, query_data_half_dev, query_results_dev, query_dis_dev, ent_pts_dev, cands); break;
+        default: rc = 1;
+    }
+#undef ARGS
+    cudaDeviceSynchronize();
+    auto end = std::chrono::high_resolution_clock::now();
+    if (seconds_total) *seconds_total = std::chrono::duration<double>(end - start).count();
+    if (seconds_search_only) *seconds_search_only = std::chrono::duration<double>(end - mid).count();
+    if (rc == 0 && cudaGetLastError() != cudaSuccess) rc = 3;
+    if (rc == 0) {
+        cudaMemcpy(out_ids, query_results_dev, (size_t)query_num * cands * sizeof(unsigned), cudaMemcpyDeviceToHost);
+        cudaMemcpy(out_dis, query_dis_dev, (size_t)query_num * cands * sizeof(float), cudaMemcpyDeviceToHost);
+    }
+    void *bufs[] = {graph_dev, ent_pts_dev, data_dev, data_half_dev, sparse_off_dev, sparse_idx_dev, sparse_val_dev, bm25_off_dev,
+                    bm25_idx_dev, bm25_val_dev, query_data_dev, query_data_half_dev, sparse_off_query_dev, sparse_idx_query_dev,
+                    sparse_val_query_dev, bm25_off_query_dev, bm25_idx_query_dev, bm25_val_query_dev, query_results_dev, query_dis_dev};
+    for (void *p : bufs) cudaFree(p);
+    return rc;
+}
