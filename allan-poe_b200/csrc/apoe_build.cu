@@ -25,8 +25,8 @@ constexpr int kK = AP_KNN;          // 64
 constexpr int kSample = 16;         // forward / reverse samples per class (new, old)
 constexpr int kPart = 64;           // participants of one local join (the node itself, new, old)
 constexpr int kNewMax = 32;         // "new" rows of a join = columns of its distance tile
-constexpr int kPropCap = 96;        // proposals a node can receive per round
-constexpr int kPropPer = 3;         // best partners proposed to each participant of a join
+constexpr int kPropCap = 192;       // proposals a node can receive per round (64 + 192 = one 256-wide merge sort)
+constexpr int kPropPerMax = 8;      // upper bound of the partners proposed to each participant of a join
 constexpr uint32_t kNewFlag = 0x80000000u;
 
 // ---------------------------------------------------------------------------------------------------------
@@ -248,6 +248,7 @@ struct JoinArgs {
     uint32_t *err;
     uint32_t arena_bytes;    // shared-memory budget for the sparse sections of all participants
     uint32_t tab_mask, tab_shift, groups;  // hash table of one new row's terms; rows hashed per round
+    uint32_t prop_per;                     // partners proposed to each participant (<= kPropPerMax)
     uint32_t o_tab, o_dm, o_arena;
 };
 constexpr int kJoinThreads = 256;
@@ -356,24 +357,27 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     // partner selection: every participant proposes to itself its kPropPer closest partners of this join
     if (tid < (int)rows) {
         const uint32_t p = tid;
-        float bd[kPropPer]; uint32_t bi[kPropPer];
+        float bd[kPropPerMax]; uint32_t bi[kPropPerMax];
+        const int kPropPer = (int)a.prop_per;
 #pragma unroll
-        for (int q = 0; q < kPropPer; ++q) { bd[q] = s_kth[p]; bi[q] = kEmpty; }
+        for (int q = 0; q < kPropPerMax; ++q) { bd[q] = s_kth[p]; bi[q] = kEmpty; }
         const uint32_t lim = p < n_new ? rows : n_new;
         for (uint32_t j = 0; j < lim; ++j) {
             if (j == p) continue;
             const uint32_t lo = min(p, j), hi = max(p, j);
             const float d = dm[lo * kPart + hi];
             if (d < bd[kPropPer - 1]) {
-                int q = kPropPer - 1;
-                while (q > 0 && d < bd[q - 1]) { bd[q] = bd[q - 1]; bi[q] = bi[q - 1]; --q; }
-                bd[q] = d; bi[q] = s_id[j];
+                // insertion into the ascending top list (fully unrolled so the arrays stay in registers)
+                float cd = d; uint32_t ci = s_id[j];
+#pragma unroll
+                for (int q = 0; q < kPropPerMax; ++q)
+                    if (q < kPropPer && cd < bd[q]) { const float td = bd[q]; const uint32_t ti = bi[q]; bd[q] = cd; bi[q] = ci; cd = td; ci = ti; }
             }
         }
         const uint32_t me = s_id[p];
 #pragma unroll
-        for (int q = 0; q < kPropPer; ++q)
-            if (bi[q] != kEmpty) {
+        for (int q = 0; q < kPropPerMax; ++q)
+            if (q < kPropPer && bi[q] != kEmpty) {
                 const uint32_t t = atomicAdd(&a.propn[me], 1u);
                 if (t < kPropCap) a.prop[(size_t)me * kPropCap + t] = make_uint2(__float_as_uint(bd[q]), bi[q]);
                 else atomicAdd(a.stats + 2, 1ull);
@@ -386,7 +390,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
 // Merge proposals into the sorted lists: one warp per node, bitonic sorts over 64 + proposals elements held in
 // shared memory (first by id to drop duplicates, then by distance), best 64 written back.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kMergeLen = 256;  // power of two >= 64 + kPropCap
+constexpr int kMergeLen = 256;  // = 64 + kPropCap
 __device__ __forceinline__ void warp_bitonic_u64(unsigned long long *key, int lane) {
     for (int size = 2; size <= kMergeLen; size <<= 1)
         for (int stride = size >> 1; stride > 0; stride >>= 1) {
@@ -886,6 +890,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     JoinArgs ja{};
     ja.plist = k.plist; ja.pcnt = k.pcnt; ja.meta = ix->meta; ja.rec = ix->rec_build; ja.D = D; ja.knn_dis = k.dis;
     ja.prop = k.prop; ja.propn = k.propn; ja.stats = k.stats; ja.err = err;
+    ja.prop_per = std::min<uint32_t>(kPropPerMax, o.reserved[0] ? o.reserved[0] : 4);
     const uint32_t tabn = pow2_at_least(2 * (ix->max_ns + ix->max_nb), 64);
     ja.tab_mask = tabn - 1; ja.tab_shift = 32 - log2u(tabn);
     // two CTAs per SM: tables for up to 4 hashed rows, the 32 x 64 distance tile, the rest is arena
@@ -901,30 +906,40 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     AP_CUDA(cudaFuncSetAttribute(join_dense_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)simt_smem));
 
     const uint32_t wblocks = (n + 7) / 8;  // warp-per-node kernels, 256 threads
+    cudaEvent_t ev[5];
+    for (auto &e : ev) AP_CUDA(cudaEventCreate(&e));
+    float phase_ms[4] = {0, 0, 0, 0};  // sample + lists, dense tiles, sparse + proposals, merge
     uint32_t it = 0;
     unsigned long long prev_updates = 0;
     for (; it < iters; ++it) {
         AP_CUDA(cudaMemsetAsync(k.scnt, 0, (size_t)n * 16));
         AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
+        AP_CUDA(cudaEventRecord(ev[0]));
         knn_sample_kernel<<<wblocks, 256>>>(k, it);
         knn_plist_kernel<<<wblocks, 256>>>(k);
         launches += 2;
+        AP_CUDA(cudaEventRecord(ev[1]));
         for (uint32_t node0 = 0; node0 < n; node0 += batch) {
             const uint32_t nodes = std::min(batch, n - node0);
             if (o.flags & AP_BUILD_SIMT_JOIN) join_dense_simt_kernel<<<nodes, 256, simt_smem>>>(node0, nodes, k.plist, k.pcnt, ix->meta, ix->rec_build, D);
             else AP_TRY(join_dense_tc_launch(ix, node0, nodes, k.plist, k.pcnt, D, 0));
+            if (node0 == 0) AP_CUDA(cudaEventRecord(ev[2]));
             ja.node0 = node0; ja.nodes = nodes;
             join_sparse_kernel<<<nodes, kJoinThreads, join_smem>>>(ja);
             launches += 2;
         }
+        AP_CUDA(cudaEventRecord(ev[3]));
         knn_merge_kernel<<<(n + 3) / 4, 128>>>(k); ++launches;
+        AP_CUDA(cudaEventRecord(ev[4]));
         AP_CUDA(cudaGetLastError());
         unsigned long long st[4];
         AP_CUDA(cudaMemcpy(st, k.stats, 32, cudaMemcpyDeviceToHost));
+        for (int ph = 0; ph < 4; ++ph) { float ms = 0.f; cudaEventElapsedTime(&ms, ev[ph], ev[ph + 1]); phase_ms[ph] += ms; }
         const unsigned long long upd = st[1] - prev_updates;
         prev_updates = st[1];
         if (it >= 3 && upd < (unsigned long long)n * kK / 1000) { ++it; break; }  // < 0.1 % of the entries changed
     }
+    for (auto &e : ev) cudaEventDestroy(e);
     AP_CUDA(cudaDeviceSynchronize());
     const auto t1 = std::chrono::high_resolution_clock::now();
 
@@ -947,6 +962,8 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
         stats->seconds_total = std::chrono::duration<double>(t2 - t0).count();
         stats->distance_evals = st[0]; stats->list_updates = st[1]; stats->iterations_run = it; stats->launches = launches;
         stats->reserved[0] = (uint32_t)st[2];
+        // phase times in 10 us units: sample + lists, dense tiles (first batch), sparse + proposals, merge
+        for (int ph = 0; ph < 3; ++ph) stats->reserved[1 + ph] = (uint32_t)(phase_ms[ph == 0 ? 1 : (ph == 1 ? 2 : 3)] * 100.f);
     }
     if (!(o.flags & AP_BUILD_KEEP_KNN)) {
         cudaFree(ix->knn_ids); cudaFree(ix->knn_dis); ix->knn_ids = nullptr; ix->knn_dis = nullptr;
