@@ -106,18 +106,26 @@ __global__ void knn_init_kernel(Knn k, uint32_t seed) {
     k.dis[i] = kInfDis;
 }
 
-// Sampling: the closest 16 unsampled ("new") and the closest 16 sampled ("old") entries of every list, plus the
-// reverse of those choices.  Sampled new entries lose their flag.
+// Sampling: the closest 16 unsampled ("new") entries and a random 16 of the sampled ("old") entries of every list,
+// plus the reverse of those choices.  Sampled new entries lose their flag.  Old entries are drawn at random so
+// that over the rounds every old neighbour meets the new ones.
 __global__ void knn_sample_kernel(Knn k, uint32_t round) {
     const uint32_t v = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (v >= k.n) return;
+    uint32_t raw[2];
+    raw[0] = k.ids[(size_t)v * kK + lane];
+    raw[1] = k.ids[(size_t)v * kK + 32 + lane];
+    const uint32_t bn0 = __ballot_sync(kFull, (raw[0] & kNewFlag) != 0), bn1 = __ballot_sync(kFull, (raw[1] & kNewFlag) != 0);
+    const uint32_t n_old = 64 - __popc(bn0) - __popc(bn1);
+    // keep an old entry with probability 16 / n_old (hash of node, round and slot)
+    const uint32_t thresh = n_old <= (uint32_t)kSample ? 0xFFFFFFFFu : (uint32_t)(((unsigned long long)kSample << 32) / n_old);
     uint32_t nn = 0, no = 0;
     for (int h = 0; h < 2; ++h) {
         const uint32_t slot = h * 32 + lane;
-        const uint32_t raw = k.ids[(size_t)v * kK + slot];
-        const bool isnew = (raw & kNewFlag) != 0;
-        const uint32_t id = raw & ~kNewFlag;
-        const uint32_t bn = __ballot_sync(kFull, isnew), bo = ~bn;
+        const bool isnew = (raw[h] & kNewFlag) != 0;
+        const uint32_t id = raw[h] & ~kNewFlag;
+        const bool oldpick = !isnew && mix32((v * 64u + slot) ^ (round * 0x9e3779b9u) ^ 0x5bd1e995u) <= thresh;
+        const uint32_t bn = h == 0 ? bn0 : bn1, bo = __ballot_sync(kFull, oldpick);
         const uint32_t rn = nn + __popc(bn & ((1u << lane) - 1u)), ro = no + __popc(bo & ((1u << lane) - 1u));
         if (isnew && rn < kSample && id < k.n) {
             k.samp[(size_t)v * 64 + rn] = id;
@@ -126,7 +134,7 @@ __global__ void knn_sample_kernel(Knn k, uint32_t round) {
             if (t < kSample) k.samp[(size_t)id * 64 + 16 + t] = v;
             else { const uint32_t r = mix32(v ^ (round * 0x9e3779b9u) ^ t) % (t + 1); if (r < kSample) k.samp[(size_t)id * 64 + 16 + r] = v; }
         }
-        if (!isnew && ro < kSample && id < k.n) {
+        if (oldpick && ro < kSample && id < k.n) {
             k.samp[(size_t)v * 64 + 32 + ro] = id;
             const uint32_t t = atomicAdd(&k.scnt[(size_t)id * 4 + 3], 1u);
             if (t < kSample) k.samp[(size_t)id * 64 + 48 + t] = v;
