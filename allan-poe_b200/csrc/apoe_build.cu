@@ -333,29 +333,62 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
             }
         }
         __syncthreads();
-        // one warp per (row i, participant j) pair: j > i among the new rows, every old row
-        const uint32_t items = g_cnt * rows;
-        for (uint32_t it = warp; it < items; it += kJoinThreads / 32) {
-            const uint32_t g = it / rows, j = it % rows, i = i0 + g;
-            if (j <= i) continue;
+        // One warp per participant j: its terms are read into registers once (6 per lane per 192-term chunk, slot
+        // indices precomputed -- every table uses the same hash) and probed against each hashed row i < j of the
+        // group with all first probes in flight together; the rare collision chains are walked afterwards.
+        for (uint32_t j = warp; j < rows; j += kJoinThreads / 32) {
+            if (j <= i0) continue;
             const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[j]);
-            const uint32_t ns = s_ns[j], nb = s_nb[j], pns = pad2(ns);
-            const uint2 *t = tab + (size_t)g * (a.tab_mask + 1);
-            float acc = 0.0f;
-            for (uint32_t q = lane; q < ns + nb; q += 32) {
-                const uint2 p = q < ns ? pr[q] : pr[pns + (q - ns)];
-                const uint32_t key = q < ns ? p.x : (p.x | 0x80000000u);
-                uint32_t h = (key * 2654435761u) >> a.tab_shift;
-                for (uint32_t s = 0; s <= a.tab_mask; ++s) {
-                    const uint2 e = t[h];
-                    if (e.x == kEmpty) break;
-                    if (e.x == key) { acc = fmaf(__uint_as_float(e.y), __uint_as_float(p.y), acc); break; }
-                    h = (h + 1) & a.tab_mask;
+            const uint32_t ns = s_ns[j], nb = s_nb[j], pns = pad2(ns), nt = ns + nb;
+            float acc[4] = {0.f, 0.f, 0.f, 0.f};
+            for (uint32_t base = 0; base < nt; base += 192) {
+                uint32_t key[6], hs[6]; float val[6];
+#pragma unroll
+                for (int t = 0; t < 6; ++t) {
+                    const uint32_t q = base + t * 32 + lane;
+                    uint2 p = make_uint2(kEmpty, 0u);   // padding: matches only an empty slot, whose value is 0
+                    if (q < nt) { p = q < ns ? pr[q] : pr[pns + (q - ns)]; if (q >= ns) p.x |= 0x80000000u; }
+                    key[t] = p.x; val[t] = __uint_as_float(p.y);
+                    hs[t] = (p.x * 2654435761u) >> a.tab_shift;
+                }
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                    if ((uint32_t)g < g_cnt) {
+                        const uint2 *t2 = tab + (size_t)g * (a.tab_mask + 1);
+                        uint2 e[6];
+#pragma unroll
+                        for (int t = 0; t < 6; ++t) e[t] = t2[hs[t]];
+#pragma unroll
+                        for (int t = 0; t < 6; ++t) {
+                            if (e[t].x == key[t]) acc[g] = fmaf(__uint_as_float(e[t].y), val[t], acc[g]);
+                            else if (e[t].x != kEmpty) {
+                                uint32_t h = (hs[t] + 1) & a.tab_mask;
+                                for (uint32_t s2 = 0; s2 < a.tab_mask; ++s2) {
+                                    const uint2 e2 = t2[h];
+                                    if (e2.x == kEmpty) break;
+                                    if (e2.x == key[t]) { acc[g] = fmaf(__uint_as_float(e2.y), val[t], acc[g]); break; }
+                                    h = (h + 1) & a.tab_mask;
+                                }
+                            }
+                        }
+                    }
                 }
             }
-#pragma unroll
-            for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(kFull, acc, o);
-            if (lane == 0) { dm[i * kPart + j] = 1.0f - D[(size_t)j * kNewMax + i] - acc; ++evals; }
+            // four warp sums in 2 + 1 + 3 shuffles: after two halving exchanges lane l holds the partial of row
+            // g = (l >> 3) & 3 over its 8-lane class, the remaining three butterflies finish it
+            {
+                const bool up4 = (lane & 16) != 0;
+                const float k0 = up4 ? acc[2] : acc[0], k1 = up4 ? acc[3] : acc[1];
+                const float s0 = up4 ? acc[0] : acc[2], s1 = up4 ? acc[1] : acc[3];
+                const float a0 = k0 + __shfl_xor_sync(kFull, s0, 16), a1 = k1 + __shfl_xor_sync(kFull, s1, 16);
+                const bool up3 = (lane & 8) != 0;
+                float r = (up3 ? a1 : a0) + __shfl_xor_sync(kFull, up3 ? a0 : a1, 8);
+                r += __shfl_xor_sync(kFull, r, 4);
+                r += __shfl_xor_sync(kFull, r, 2);
+                r += __shfl_xor_sync(kFull, r, 1);
+                const uint32_t g = (lane >> 3) & 3u, i = i0 + g;
+                if ((lane & 7) == 0 && g < g_cnt && i < j) { dm[i * kPart + j] = 1.0f - D[(size_t)j * kNewMax + i] - r; ++evals; }
+            }
         }
         __syncthreads();
         for (uint32_t q = tid; q < (a.tab_mask + 1) * g_cnt; q += kJoinThreads) tab[q] = make_uint2(kEmpty, 0u);
@@ -391,7 +424,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
                 else atomicAdd(a.stats + 2, 1ull);
             }
     }
-    if (lane == 0 && evals) atomicAdd(a.stats + 0, evals);
+    if (evals) atomicAdd(a.stats + 0, evals);
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -528,6 +561,8 @@ __device__ __forceinline__ bool set_contains(const uint32_t *tab, uint32_t mask,
 __global__ void __launch_bounds__(kPruneThreads, 2) prune_kernel(const PruneArgs a) {
     extern __shared__ __align__(16) uint8_t smem[];
     __shared__ uint32_t nei0[kK], nei1[kK], nei2[kK + 1], det[kK];
+    __shared__ uint64_t meta0[kK], sel_meta[kK];   // locator words of the detour-ordered candidates / of the selected ones
+    __shared__ float pow0[kK], sel_pow[kK];
     __shared__ uint32_t s_tmp_id, s_ipn, s_cur_nei, s_cur_nei2;
     __shared__ uint32_t vflag[16];
     uint2 *tab = reinterpret_cast<uint2 *>(smem + a.o_tab);
@@ -575,13 +610,15 @@ __global__ void __launch_bounds__(kPruneThreads, 2) prune_kernel(const PruneArgs
     }
     __syncthreads();
     block_bitonic_kv(det, nei0, kK, tid, kPruneThreads);
-    if (tid == 0) { nei1[0] = nei0[0]; s_tmp_id = 1; s_ipn = 1; s_cur_nei = 0; s_cur_nei2 = 0; }
+    if (tid < kK) { meta0[tid] = a.meta[nei0[tid]]; pow0[tid] = a.power[nei0[tid]]; }
+    __syncthreads();
+    if (tid == 0) { nei1[0] = nei0[0]; sel_meta[0] = meta0[0]; sel_pow[0] = pow0[0]; s_tmp_id = 1; s_ipn = 1; s_cur_nei = 0; s_cur_nei2 = 0; }
     __syncthreads();
 
     // RNG-IP joint pruning (ref :613-676)
     while (s_ipn < kK) {
         const uint32_t cn = nei0[s_tmp_id], ipn = s_ipn;
-        const uint64_t cm = a.meta[cn];
+        const uint64_t cm = meta0[s_tmp_id];
         const uint8_t *crec = a.rec + meta_off16(cm) * 16ull;
         {   // candidate's terms into the table
             const uint2 *pr = reinterpret_cast<const uint2 *>(crec + kDenseBytes);
@@ -597,12 +634,12 @@ __global__ void __launch_bounds__(kPruneThreads, 2) prune_kernel(const PruneArgs
 #pragma unroll
             for (int k = 0; k < 8; ++k) { const uint2 x = __ldg(d + lane + 32 * k); creg[2 * k] = x.x; creg[2 * k + 1] = x.y; }
         }
-        const float cpow = a.power[cn];
+        const float cpow = pow0[s_tmp_id];
         __syncthreads();
         for (uint32_t i = warp; i < ipn; i += kPruneWarps) {
             const uint32_t sn = nei1[i];
             if (sn == kEmpty) continue;
-            const uint64_t sm = a.meta[sn];
+            const uint64_t sm = sel_meta[i];
             const uint8_t *srec = a.rec + meta_off16(sm) * 16ull;
             uint32_t acc = 0;
             const uint2 *d = reinterpret_cast<const uint2 *>(srec);
@@ -652,7 +689,7 @@ __global__ void __launch_bounds__(kPruneThreads, 2) prune_kernel(const PruneArgs
                 if (kw) vflag[i & 15] = 1;
                 const float ip = __fadd_rn(half_sum_to_float(acc), tot);
                 if (cpow < ip) s_cur_nei = 1;
-                if (a.power[sn] < ip) nei1[i] = kEmpty;
+                if (sel_pow[i] < ip) nei1[i] = kEmpty;
                 if (vflag[i & 15] != 1) s_cur_nei2 = 1;
             }
             __syncwarp();
@@ -660,7 +697,7 @@ __global__ void __launch_bounds__(kPruneThreads, 2) prune_kernel(const PruneArgs
         __syncthreads();
         if (tid == 0) {
             uint32_t n2 = ipn;
-            if (s_cur_nei == 0) { nei1[n2] = cn; ++n2; }
+            if (s_cur_nei == 0) { nei1[n2] = cn; sel_meta[n2] = cm; sel_pow[n2] = cpow; ++n2; }
             if (s_cur_nei2 == 0) nei2[n2] = 1;  // written after the increment, as in the reference
             s_ipn = n2; s_cur_nei = 0; s_cur_nei2 = 0; s_tmp_id = s_tmp_id + 1;
         }
