@@ -317,7 +317,15 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     mbar_wait_bounded(&mbar, 0, a.err, 3u);
     __syncthreads();
 
-    const float *D = a.D + (size_t)local * kPart * kNewMax;
+    // the dense tile of this join, staged once (coalesced) instead of one global read per pair
+    __shared__ float s_D[kPart * kNewMax];
+    {
+        const float4 *src = reinterpret_cast<const float4 *>(a.D + (size_t)local * kPart * kNewMax);
+        float4 *dst = reinterpret_cast<float4 *>(s_D);
+        for (uint32_t q = tid; q < rows * kNewMax / 4; q += kJoinThreads) dst[q] = __ldg(src + q);
+    }
+    __syncthreads();
+    const float *D = s_D;
     unsigned long long evals = 0;
     for (uint32_t i0 = 0; i0 < n_new; i0 += a.groups) {
         const uint32_t g_cnt = min(a.groups, n_new - i0);
@@ -358,16 +366,28 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
                         uint2 e[6];
 #pragma unroll
                         for (int t = 0; t < 6; ++t) e[t] = t2[hs[t]];
+                        uint32_t chain = 0;   // terms whose first slot holds another key
 #pragma unroll
                         for (int t = 0; t < 6; ++t) {
-                            if (e[t].x == key[t]) acc[g] = fmaf(__uint_as_float(e[t].y), val[t], acc[g]);
-                            else if (e[t].x != kEmpty) {
-                                uint32_t h = (hs[t] + 1) & a.tab_mask;
-                                for (uint32_t s2 = 0; s2 < a.tab_mask; ++s2) {
-                                    const uint2 e2 = t2[h];
-                                    if (e2.x == kEmpty) break;
-                                    if (e2.x == key[t]) { acc[g] = fmaf(__uint_as_float(e2.y), val[t], acc[g]); break; }
-                                    h = (h + 1) & a.tab_mask;
+                            acc[g] = fmaf(e[t].x == key[t] ? __uint_as_float(e[t].y) : 0.0f, val[t], acc[g]);
+                            chain |= (e[t].x != key[t] && e[t].x != kEmpty) ? (1u << t) : 0u;
+                        }
+                        if (__any_sync(kFull, chain != 0)) {
+                            // second slot for every term at once (no divergence), longer chains one by one
+#pragma unroll
+                            for (int t = 0; t < 6; ++t) e[t] = t2[(hs[t] + 1) & a.tab_mask];
+#pragma unroll
+                            for (int t = 0; t < 6; ++t) {
+                                const bool live = (chain >> t) & 1u;
+                                acc[g] = fmaf((live && e[t].x == key[t]) ? __uint_as_float(e[t].y) : 0.0f, val[t], acc[g]);
+                                if (live && e[t].x != key[t] && e[t].x != kEmpty) {
+                                    uint32_t h = (hs[t] + 2) & a.tab_mask;
+                                    for (uint32_t s2 = 0; s2 < a.tab_mask; ++s2) {
+                                        const uint2 e2 = t2[h];
+                                        if (e2.x == kEmpty) break;
+                                        if (e2.x == key[t]) { acc[g] = fmaf(__uint_as_float(e2.y), val[t], acc[g]); break; }
+                                        h = (h + 1) & a.tab_mask;
+                                    }
                                 }
                             }
                         }
@@ -939,7 +959,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     const uint32_t tabn = pow2_at_least(2 * (ix->max_ns + ix->max_nb), 64);
     ja.tab_mask = tabn - 1; ja.tab_shift = 32 - log2u(tabn);
     // two CTAs per SM: tables for up to 4 hashed rows, the 32 x 64 distance tile, the rest is arena
-    const size_t per_cta = ix->smem_per_sm / 2 - 1024 - 2048 /* static */;
+    const size_t per_cta = ix->smem_per_sm / 2 - 1024 - 10240 /* static: dense tile + bookkeeping */;
     ja.groups = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (per_cta / 4) / (8 * (size_t)tabn)));
     ja.o_tab = 0; ja.o_dm = 8 * tabn * ja.groups; ja.o_arena = (ja.o_dm + 4 * kNewMax * kPart + 127) / 128 * 128;
     if (per_cta <= ja.o_arena + 8u * (pad2(ix->max_ns) + pad2(ix->max_nb)) * 2)
