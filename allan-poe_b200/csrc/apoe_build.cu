@@ -318,7 +318,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     __syncthreads();
 
     // the dense tile of this join, staged once (coalesced) instead of one global read per pair
-    __shared__ float s_D[kPart * kNewMax];
+    __shared__ __align__(16) float s_D[kPart * kNewMax];
     {
         const float4 *src = reinterpret_cast<const float4 *>(a.D + (size_t)local * kPart * kNewMax);
         float4 *dst = reinterpret_cast<float4 *>(s_D);
