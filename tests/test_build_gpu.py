@@ -101,7 +101,12 @@ def test_build_quality(simt):
     eff, qdh, qs, qb, qd = helpers.scaled_queries(ds)
     gt, _, _ = orc.bruteforce(ds.D, ds.S, ds.B, qd, qs, qb, 7, 10)
     got, _, _ = ix.search(ds.QD, ds.QS, ds.QB, cands=128)
-    assert helpers.recall_at(got, gt) >= 0.80
+    built_recall = helpers.recall_at(got, gt)
+    # yardstick: the same search over the graph pruned from the *exact* k-NN lists (the synthetic corpus itself caps
+    # recall well below 1: its dense component is structureless and carries a large normalised weight)
+    ix.prune(knn, helpers.exact_knn(ds.D, ds.S, ds.B)[1], power)
+    ref, _, _ = ix.search(ds.QD, ds.QS, ds.QB, cands=128)
+    assert built_recall >= helpers.recall_at(ref, gt) - 0.05, (built_recall, helpers.recall_at(ref, gt))
     assert st.iterations_run >= 1 and st.distance_evals > 0
     ix.close()
 
