@@ -260,6 +260,11 @@ class Index:
                                       C.c_void_p(stream or 0), C.byref(st) if stats else None))
         return st
 
+    def debug_counters(self):
+        out = np.zeros(8, dtype=np.uint64)
+        _check(lib().ap_debug_counters(self._h, _ptr(out)))
+        return out
+
     def fused_distances(self, qdense, qsparse, qbm25, pair_q, pair_d, weights=(1.0, 1.0, 1.0), flags=0):
         q, keep = self._host_queries(qdense, qsparse, qbm25)
         pq, pd = _np(pair_q, np.uint32), _np(pair_d, np.uint32)

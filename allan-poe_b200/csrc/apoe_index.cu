@@ -500,7 +500,7 @@ int ap_search_host(ap_index *ix, const ap_queries *q, const ap_search_opts *opts
     L.cands = cands; L.flags = (opts->flags & ~(AP_SEARCH_KEYWORD | AP_SEARCH_KG)) | mode; L.path = path;
     L.arena_bytes = opts->arena_bytes; L.ctas_per_sm = opts->ctas_per_sm; L.stream = st;
     uint32_t launches = 0;
-    AP_CUDA(cudaMemsetAsync(ix->d_cnt, 0, 24, st));
+    AP_CUDA(cudaMemsetAsync(ix->d_cnt, 0, 64, st));
     AP_CUDA(cudaEventRecord(ix->ev0, st));
     AP_TRY(search_launch(ix, L, &launches));
     AP_CUDA(cudaEventRecord(ix->ev1, st));
@@ -550,7 +550,7 @@ int ap_search_device(ap_index *ix, const ap_queries *q, const ap_search_opts *op
     L.arena_bytes = opts->arena_bytes; L.ctas_per_sm = opts->ctas_per_sm; L.stream = st;
     L.out_ids = out_ids; L.out_dis = out_dis;
     uint32_t launches = 0;
-    AP_CUDA(cudaMemsetAsync(ix->d_cnt, 0, 24, st));
+    AP_CUDA(cudaMemsetAsync(ix->d_cnt, 0, 64, st));
     if (stats) AP_CUDA(cudaEventRecord(ix->ev0, st));
     AP_TRY(search_launch(ix, L, &launches));
     if (stats) {
@@ -601,6 +601,16 @@ int ap_fused_distances(ap_index *ix, const ap_queries *q, const ap_search_opts *
     L.cands = 32; L.flags = opts->flags & AP_SEARCH_UNFUSED_DENSE; L.path = path; L.stream = 0;
     AP_TRY(distances_launch(ix, L, n_pairs, dq, dd, dout));
     AP_CUDA(cudaMemcpy(out, dout, n_pairs * 4, cudaMemcpyDeviceToHost));
+    return AP_OK;
+}
+
+// Test / profiling hook: the counters of the last search on this index: expansions, evaluations, gathered bytes, then
+// clock cycles thread 0 of every CTA spent in: control (select, row staging, copy planning), waiting for copies,
+// scoring, the 32-wide sort, the pool merge (summed over CTAs).
+int ap_debug_counters(ap_index *ix, uint64_t *out8) {
+    if (!ix || !out8) return fail(AP_ERR_ARG, "null argument");
+    AP_CUDA(cudaSetDevice(ix->device));
+    AP_CUDA(cudaMemcpy(out8, ix->d_cnt, 64, cudaMemcpyDeviceToHost));
     return AP_OK;
 }
 

@@ -72,6 +72,7 @@ struct Ctx {  // per-thread view of the CTA's shared state
     uint8_t *arena;
     uint32_t phase;
     unsigned long long c_exp, c_eval, c_bytes;
+    long long t_wait, t_score, t_ctl, t_sort, t_merge, t_mark;   // clock64 phase totals (thread 0)
     int tid, lane, warp;
 };
 
@@ -265,8 +266,13 @@ __device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const u
         const uint32_t bm = c.ctl[CTL_BATCH];
         const bool last = c.ctl[CTL_LAST] != 0;
         if (bm) {
-            mbar_wait_bounded(c.mbar, c.phase, a.ctl + 1, 1u);
+            // warp 0 alone polls the mbarrier; the other warps park on the CTA barrier (no spinning instructions)
+            long long tw0 = 0;
+            if (c.warp == 0) { tw0 = clock64(); mbar_wait_bounded(c.mbar, c.phase, a.ctl + 1, 1u); }
             c.phase ^= 1u;
+            __syncthreads();
+            long long tw1 = 0;
+            if (c.tid == 0) { tw1 = clock64(); c.t_wait += tw1 - tw0; }
             const int nb_batch = __popc(bm);
             for (int k = c.warp; k < nb_batch; k += kSearchWarps) {  // warp w takes the (w + 4k)-th slot of the batch
                 const int j = __fns(bm, 0, k + 1);
@@ -280,6 +286,7 @@ __device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const u
                     if (KW && hit) c.pool_id[base + j] |= 0x40000000u;
                 }
             }
+            if (c.tid == 0) c.t_score += clock64() - tw1;
         }
         __syncthreads();
         if (!bm || last) break;
@@ -332,6 +339,7 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
     c.arena = smem + a.o_arena;
     c.tid = threadIdx.x; c.lane = c.tid & 31; c.warp = c.tid >> 5;
     c.phase = 0; c.c_exp = 0; c.c_eval = 0; c.c_bytes = 0;
+    c.t_wait = c.t_score = c.t_ctl = c.t_sort = c.t_merge = c.t_mark = 0;
     const int tid = c.tid, lane = c.lane, warp = c.warp;
     const uint32_t topm = a.cands;
     uint32_t *pool_id = c.pool_id;
@@ -447,6 +455,7 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
 
         // ---- greedy iterations (ref: src/query.cu:488-563) ---------------------------------------------------
         for (int it = 0; it < kMaxIter; ++it) {
+            if (tid == 0) c.t_mark = clock64();
             if ((it + 1) % kHashReset == 0) {
                 for (uint32_t i = tid; i <= a.vis_mask; i += kSearchThreads) c.vis[i] = kEmpty;
                 __syncthreads();
@@ -567,7 +576,9 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
                     }
                 }
             }
+            if (tid == 0) { const long long t = clock64(); c.t_ctl += t - c.t_mark; }
             score_slots<F>(a, c, qreg, topm, my_meta, my_need);
+            if (tid == 0) c.t_mark = clock64();
 
             // sort the 32 staged entries, decide whether the pool changes at all
             if (warp == 0) {
@@ -580,6 +591,7 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
                 if (lane == 0) c.ctl[CTL_MERGE] = (d <= pool_dis[topm - 1]) ? 1u : 0u;
             }
             __syncthreads();
+            if (tid == 0) { const long long t = clock64(); c.t_sort += t - c.t_mark; c.t_mark = t; }
             if (c.ctl[CTL_MERGE]) {
                 // rank merge (ref: merge_top, src/query.cu:181-224): a pool element moves right by the number of
                 // staged elements <= it, a staged element lands at its index plus the number of pool elements < it
@@ -620,6 +632,7 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
                         if (KG) { c.pool_ent[r_pos[e]] = r_e[e]; c.pool_hop[r_pos[e]] = r_h[e]; }
                     }
                 __syncthreads();
+                if (tid == 0) c.t_merge += clock64() - c.t_mark;
             }
         }
 
@@ -661,6 +674,11 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
         atomicAdd(a.cnt + 0, c.c_exp);
         atomicAdd(a.cnt + 1, c.c_eval);
         atomicAdd(a.cnt + 2, c.c_bytes);
+        atomicAdd(a.cnt + 3, (unsigned long long)c.t_ctl);
+        atomicAdd(a.cnt + 4, (unsigned long long)c.t_wait);
+        atomicAdd(a.cnt + 5, (unsigned long long)c.t_score);
+        atomicAdd(a.cnt + 6, (unsigned long long)c.t_sort);
+        atomicAdd(a.cnt + 7, (unsigned long long)c.t_merge);
     }
 }
 

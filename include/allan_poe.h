@@ -211,6 +211,10 @@ int ap_merge_shard_results(int device, uint32_t shards, uint32_t nq, uint32_t pe
  * (use_tc != 0) or by the CUDA-core kernel.  out: nodes x 64 x 32 floats, host.  Needs AP_CREATE_FOR_BUILD. */
 int ap_debug_join_dense(ap_index *ix, uint32_t nodes, const uint32_t *plist, const uint32_t *pcnt, int use_tc, float *out);
 
+/* Profiling hook: counters of the last search on this index -- expansions, evaluations, gathered bytes, then clock
+ * cycles (thread 0 of every CTA, summed) spent in control, waiting for copies, scoring, sorting, merging. */
+int ap_debug_counters(ap_index *ix, uint64_t *out8);
+
 #ifdef __cplusplus
 }
 #endif
