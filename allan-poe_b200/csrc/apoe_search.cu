@@ -52,10 +52,9 @@ struct SearchArgs {
     unsigned long long *cnt;  // [0] expansions, [1] evaluations, [2] gathered bytes
     uint32_t arena_bytes;
     uint32_t vis_mask;           // visited table size - 1
-    uint32_t sq_mask, sq_shift;  // query sparse hash: size - 1, 32 - log2(size)
-    uint32_t bq_mask, bq_shift;
+    uint32_t cap_s, cap_b;       // per-record match scratch: pad2(longest sparse row), pad2(longest BM25 row) floats
     // shared-memory byte offsets
-    uint32_t o_pool_id, o_pool_dis, o_pool_ent, o_pool_hop, o_vis, o_info, o_sq, o_bq, o_kw, o_arena;
+    uint32_t o_pool_id, o_pool_dis, o_pool_ent, o_pool_hop, o_vis, o_info, o_sq, o_bq, o_mv, o_kw, o_arena;
 };
 
 struct Ctx {  // per-thread view of the CTA's shared state
@@ -66,7 +65,9 @@ struct Ctx {  // per-thread view of the CTA's shared state
     uint32_t *pool_ent, *pool_hop;
     uint32_t *vis;
     uint2 *info;
-    uint2 *sq, *bq;
+    uint2 *sq, *bq;     // the query's sparse / BM25 terms (id, weighted value), as given
+    float *mv;          // this warp's match scratch, kScoreBatch x (cap_s + cap_b) floats, all zero between uses
+    uint32_t nqs, nqb;
     uint32_t *kw_id;
     float *kw_dis;
     uint8_t *arena;
@@ -91,83 +92,125 @@ __device__ __forceinline__ uint32_t vis_insert(uint32_t *tab, uint32_t mask, uin
     return 0;
 }
 
-__device__ __forceinline__ void qtab_insert(uint2 *tab, uint32_t mask, uint32_t shift, uint32_t rawkey, float val) {
-    const uint32_t t = rawkey & 0x7FFFFFFFu;
-    uint32_t h = (t * 2654435761u) >> shift;
-    for (uint32_t i = 0; i <= mask; ++i) {
-        const uint32_t old = atomicCAS(&tab[h].x, kEmpty, rawkey);
-        if (old == kEmpty) { tab[h].y = __float_as_uint(val); return; }
-        if ((old & 0x7FFFFFFFu) == t) return;  // duplicate term in a query row: the first one wins
-        h = (h + 1) & mask;
-    }
-}
+constexpr int kScoreBatch = 2;  // records a warp scores side by side (independent instruction streams)
 
-// Per-lane partial of <doc row, query row>: the lane walks the document's pairs j = lane, lane+32, ... in
-// ascending order and multiply-adds matches in fp32 (ref: cal_sparse_dist / cal_bm25_dist,
-// include/utils.cuh:299-340; the binary search of the reference is replaced by a hash probe, the set of
-// matches and their order are the same).
-__device__ __forceinline__ float sparse_partial(const uint2 *pairs, uint32_t nnz, const uint2 *tab, uint32_t mask,
-                                                uint32_t shift, int lane, uint32_t &key_hit) {
-    float acc = 0.0f;
-    for (uint32_t j = lane; j < nnz; j += 32) {
-        const uint2 p = pairs[j];
-        uint32_t h = (p.x * 2654435761u) >> shift;
-        for (uint32_t i = 0; i <= mask; ++i) {
-            const uint2 e = tab[h];
-            if (e.x == kEmpty) break;
-            if ((e.x & 0x7FFFFFFFu) == p.x) {
-                acc = __fmaf_rn(__uint_as_float(e.y), __uint_as_float(p.y), acc);
-                key_hit |= (e.x >> 31);
-                break;
-            }
-            h = (h + 1) & mask;
-        }
-    }
-    return acc;
-}
-
-// One fused distance, computed by a full warp from a record staged in shared memory.  Valid in lane 0.
-template <int F>
-__device__ __forceinline__ float score_record(const uint8_t *rec, uint32_t ns, uint32_t nb, const uint32_t (&qreg)[16],
-                                              const uint2 *sq, uint32_t sq_mask, uint32_t sq_shift, const uint2 *bq,
-                                              uint32_t bq_mask, uint32_t bq_shift, int lane, uint32_t &key_hit) {
+// Fused distances of R records staged in shared memory, computed by a full warp.  Valid in lane 0.
+//   dense : HFMA2 in the reference's lane / chunk association (src/query.cu:538-554);
+//   sparse: every query term (one per lane) finds its position in the document's ascending id list by a
+//           branch-free binary search and drops its weighted value into a per-record scratch row; each lane then
+//           walks the document's pairs j = lane, lane + 32, ... in ascending order and multiply-adds
+//           scratch[j] * value[j] in fp32 -- unmatched positions hold 0 and leave the sum unchanged, so the per-lane
+//           sums are exactly those of cal_sparse_dist / cal_bm25_dist (include/utils.cuh:299-340);
+//   then the reference's shfl_down trees and its double-precision `1.0 - dense - sparse`.
+template <int F, int R>
+__device__ __forceinline__ void score_records(const uint8_t *const (&rec)[R], const uint32_t (&ns)[R], const uint32_t (&nb)[R],
+                                              const uint32_t (&qreg)[16], const uint2 *qs, uint32_t nqs, const uint2 *qb,
+                                              uint32_t nqb, float *mv, uint32_t cap_s, uint32_t cap_b, int lane,
+                                              float (&out)[R], uint32_t (&hit)[R]) {
     constexpr bool D = (F & PF_DENSE) != 0, S = (F & PF_SPARSE) != 0, B = (F & PF_BM25) != 0, UNF = (F & PF_UNFUSED) != 0;
-    uint32_t acc = 0;
+    uint32_t acc[R];
+    const uint8_t *p[R];
+    float tot[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) { acc[r] = 0; p[r] = rec[r]; tot[r] = 0.0f; hit[r] = 0; }
     if (D) {
-        const uint2 *d = reinterpret_cast<const uint2 *>(rec);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
-            const uint2 v = d[lane + 32 * k];
-            if (UNF) {
-                acc = hadd2_rn(acc, hmul2_rn(qreg[2 * k], v.x));
-                acc = hadd2_rn(acc, hmul2_rn(qreg[2 * k + 1], v.y));
-            } else {
-                acc = hfma2_rn(qreg[2 * k], v.x, acc);
-                acc = hfma2_rn(qreg[2 * k + 1], v.y, acc);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint2 v = reinterpret_cast<const uint2 *>(p[r])[lane + 32 * k];
+                if (UNF) {
+                    acc[r] = hadd2_rn(acc[r], hmul2_rn(qreg[2 * k], v.x));
+                    acc[r] = hadd2_rn(acc[r], hmul2_rn(qreg[2 * k + 1], v.y));
+                } else {
+                    acc[r] = hfma2_rn(qreg[2 * k], v.x, acc[r]);
+                    acc[r] = hfma2_rn(qreg[2 * k + 1], v.y, acc[r]);
+                }
             }
         }
-        rec += kDenseBytes;
+#pragma unroll
+        for (int r = 0; r < R; ++r) p[r] += kDenseBytes;
     }
-    float tot = 0.0f;
-    if (S) {
-        uint32_t dummy = 0;
-        tot = sparse_partial(reinterpret_cast<const uint2 *>(rec), ns, sq, sq_mask, sq_shift, lane, dummy);
-        rec += 8u * pad2(ns);
-    }
-    if (B) {
-        const float b = sparse_partial(reinterpret_cast<const uint2 *>(rec), nb, bq, bq_mask, bq_shift, lane, key_hit);
-        tot = S ? __fadd_rn(tot, b) : b;
+    // one pass for the sparse section, one for the BM25 section
+#pragma unroll
+    for (int sec = 0; sec < 2; ++sec) {
+        if ((sec == 0 && !S) || (sec == 1 && !B)) continue;
+        const uint2 *q = sec == 0 ? qs : qb;
+        const uint32_t nq = sec == 0 ? nqs : nqb;
+        const uint2 *pr[R];
+        float *m[R];
+        uint32_t cnt[R], nmax = 0;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            pr[r] = reinterpret_cast<const uint2 *>(p[r]);
+            m[r] = mv + r * (cap_s + cap_b) + (sec == 0 ? 0u : cap_s);
+            cnt[r] = sec == 0 ? ns[r] : nb[r];
+            nmax = max(nmax, cnt[r]);
+        }
+        for (uint32_t t0 = 0; t0 < nq; t0 += 32) {
+            const uint32_t t = t0 + lane;
+            const bool on = t < nq;
+            const uint2 qt = on ? q[t] : make_uint2(kEmpty, 0u);
+            const uint32_t key = sec == 0 ? qt.x : (on ? (qt.x & 0x7FFFFFFFu) : kEmpty);
+            const bool first = on && (t == 0 || (q[t - 1].x & (sec == 0 ? 0xFFFFFFFFu : 0x7FFFFFFFu)) != key);
+            uint32_t base[R], n[R];
+#pragma unroll
+            for (int r = 0; r < R; ++r) { base[r] = 0; n[r] = cnt[r]; }
+            for (uint32_t span = nmax; span > 1; span -= span >> 1) {
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                    if (n[r] > 1) {
+                        const uint32_t half = n[r] >> 1;
+                        base[r] += (pr[r][base[r] + half].x < key) ? half : 0u;
+                        n[r] -= half;
+                    }
+            }
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                if (cnt[r]) {
+                    uint32_t b = base[r];
+                    b += (pr[r][b].x < key) ? 1u : 0u;
+                    if (first && b < cnt[r] && pr[r][b].x == key) {
+                        m[r][b] = __uint_as_float(qt.y);
+                        if (sec == 1) hit[r] |= qt.x >> 31;
+                    }
+                }
+        }
+        __syncwarp();
+        float part[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r) part[r] = 0.0f;
+        for (uint32_t j = lane; j < nmax; j += 32) {
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+                if (j < cnt[r]) {
+                    part[r] = __fmaf_rn(m[r][j], __uint_as_float(pr[r][j].y), part[r]);
+                    m[r][j] = 0.0f;
+                }
+        }
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            tot[r] = (sec == 1 && S) ? __fadd_rn(tot[r], part[r]) : part[r];
+            p[r] += 8u * pad2(cnt[r]);
+        }
+        __syncwarp();
     }
 #pragma unroll
-    for (int m = 16; m > 0; m >>= 1) {
-        if (D) acc = hadd2_rn(acc, __shfl_down_sync(kFull, acc, m));
-        if (S || B) tot = __fadd_rn(tot, __shfl_down_sync(kFull, tot, m));
+    for (int mm = 16; mm > 0; mm >>= 1) {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+            if (D) acc[r] = hadd2_rn(acc[r], __shfl_down_sync(kFull, acc[r], mm));
+            if (S || B) tot[r] = __fadd_rn(tot[r], __shfl_down_sync(kFull, tot[r], mm));
+        }
     }
-    // the reference writes `1.0 - dense - sparse` with a double literal: the subtraction chain runs in double
-    double r = 1.0;
-    if (D) r -= (double)half_sum_to_float(acc);
-    if (S || B) r -= (double)tot;
-    return (float)r;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+        // the reference writes `1.0 - dense - sparse` with a double literal: the subtraction chain runs in double
+        double v = 1.0;
+        if (D) v -= (double)half_sum_to_float(acc[r]);
+        if (S || B) v -= (double)tot[r];
+        out[r] = (float)v;
+    }
 }
 
 // The reference's bitonic network on 32 elements held one per lane (include/utils.cuh:147-165 with len = 32):
@@ -274,16 +317,27 @@ __device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const u
             long long tw1 = 0;
             if (c.tid == 0) { tw1 = clock64(); c.t_wait += tw1 - tw0; }
             const int nb_batch = __popc(bm);
-            for (int k = c.warp; k < nb_batch; k += kSearchWarps) {  // warp w takes the (w + 4k)-th slot of the batch
-                const int j = __fns(bm, 0, k + 1);
-                const uint2 inf = c.info[j];
-                uint32_t hit = 0;
-                const float d = score_record<F>(c.arena + inf.x, inf.y & 0xFFFFu, inf.y >> 16, qreg, c.sq, a.sq_mask,
-                                                a.sq_shift, c.bq, a.bq_mask, a.bq_shift, lane, hit);
-                if (KW) hit = __ballot_sync(kFull, hit != 0);
-                if (lane == 0) {
-                    c.pool_dis[base + j] = d;
-                    if (KW && hit) c.pool_id[base + j] |= 0x40000000u;
+            for (int g = c.warp; g * kScoreBatch < nb_batch; g += kSearchWarps) {  // groups of records, round-robin over warps
+                const uint8_t *rec[kScoreBatch];
+                uint32_t rns[kScoreBatch], rnb[kScoreBatch], hit[kScoreBatch];
+                int slot[kScoreBatch];
+                float d[kScoreBatch];
+#pragma unroll
+                for (int r = 0; r < kScoreBatch; ++r) {
+                    const int k = g * kScoreBatch + r;
+                    const bool valid = k < nb_batch;
+                    slot[r] = valid ? __fns(bm, 0, k + 1) : -1;
+                    const uint2 inf = valid ? c.info[slot[r]] : make_uint2(0u, 0u);
+                    rec[r] = c.arena + inf.x; rns[r] = inf.y & 0xFFFFu; rnb[r] = inf.y >> 16;
+                }
+                score_records<F, kScoreBatch>(rec, rns, rnb, qreg, c.sq, c.nqs, c.bq, c.nqb, c.mv, a.cap_s, a.cap_b, lane, d, hit);
+#pragma unroll
+                for (int r = 0; r < kScoreBatch; ++r) {
+                    const uint32_t h = KW ? __ballot_sync(kFull, hit[r] != 0) : 0u;
+                    if (lane == 0 && slot[r] >= 0) {
+                        c.pool_dis[base + slot[r]] = d[r];
+                        if (KW && h) c.pool_id[base + slot[r]] |= 0x40000000u;
+                    }
                 }
             }
             if (c.tid == 0) c.t_score += clock64() - tw1;
@@ -334,6 +388,7 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
     c.info = reinterpret_cast<uint2 *>(smem + a.o_info);
     c.sq = reinterpret_cast<uint2 *>(smem + a.o_sq);
     c.bq = reinterpret_cast<uint2 *>(smem + a.o_bq);
+    c.nqs = c.nqb = 0;
     c.kw_id = reinterpret_cast<uint32_t *>(smem + a.o_kw);
     c.kw_dis = reinterpret_cast<float *>(smem + a.o_kw + 4 * kKeywordRing);
     c.arena = smem + a.o_arena;
@@ -347,6 +402,8 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
     uint32_t *stg_id = pool_id + topm;
     float *stg_dis = pool_dis + topm;
 
+    c.mv = reinterpret_cast<float *>(smem + a.o_mv) + (size_t)c.warp * kScoreBatch * (a.cap_s + a.cap_b);
+    for (uint32_t i = tid; i < kSearchWarps * kScoreBatch * (a.cap_s + a.cap_b); i += kSearchThreads) reinterpret_cast<float *>(smem + a.o_mv)[i] = 0.0f;
     if (tid == 0) { mbar_init(c.mbar, 1); mbar_fence_init(); }
     __syncthreads();
 
@@ -362,8 +419,6 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
             pool_id[i] = kEmpty; pool_dis[i] = kInfDis;
             if (KG) { c.pool_ent[i] = kEmpty; c.pool_hop[i] = 0; }
         }
-        if (S) for (uint32_t i = tid; i <= a.sq_mask; i += kSearchThreads) c.sq[i] = make_uint2(kEmpty, 0u);
-        if (B) for (uint32_t i = tid; i <= a.bq_mask; i += kSearchThreads) c.bq[i] = make_uint2(kEmpty, 0u);
         if (KW && tid < kKeywordRing) { c.kw_id[tid] = 0x3FFFFFFFu; c.kw_dis[tid] = kInfDis; }
         if (tid == 0) c.ctl[CTL_KWNUM] = 0;
         // query: weight folded in fp32, then rounded to half (ref: src/query.cu:1871-1875, 2002)
@@ -381,12 +436,18 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
             for (int k = 0; k < 16; ++k) qreg[k] = 0;
         }
         __syncthreads();
-        if (S)
-            for (uint32_t j = a.qs_off[qi] + tid; j < a.qs_off[qi + 1]; j += kSearchThreads)
-                qtab_insert(c.sq, a.sq_mask, a.sq_shift, a.qs_idx[j], __fmul_rn(a.qs_val[j], a.w_sparse));
-        if (B)
-            for (uint32_t j = a.qb_off[qi] + tid; j < a.qb_off[qi + 1]; j += kSearchThreads)
-                qtab_insert(c.bq, a.bq_mask, a.bq_shift, a.qb_idx[j], __fmul_rn(a.qb_val[j], a.w_bm25));
+        if (S) {
+            const uint32_t o = a.qs_off[qi];
+            c.nqs = a.qs_off[qi + 1] - o;
+            for (uint32_t j = tid; j < c.nqs; j += kSearchThreads)
+                c.sq[j] = make_uint2(a.qs_idx[o + j], __float_as_uint(__fmul_rn(a.qs_val[o + j], a.w_sparse)));
+        }
+        if (B) {
+            const uint32_t o = a.qb_off[qi];
+            c.nqb = a.qb_off[qi + 1] - o;
+            for (uint32_t j = tid; j < c.nqb; j += kSearchThreads)
+                c.bq[j] = make_uint2(a.qb_idx[o + j], __float_as_uint(__fmul_rn(a.qb_val[o + j], a.w_bm25)));
+        }
         __syncthreads();
 
         // ---- seeding -------------------------------------------------------------------------------------
@@ -692,12 +753,12 @@ __global__ void __launch_bounds__(32) distances_kernel(const SearchArgs a, size_
     extern __shared__ __align__(128) uint8_t smem[];
     uint2 *sq = reinterpret_cast<uint2 *>(smem + a.o_sq);
     uint2 *bq = reinterpret_cast<uint2 *>(smem + a.o_bq);
+    float *mv = reinterpret_cast<float *>(smem + a.o_mv);
     uint8_t *arena = smem + a.o_arena;
     const int lane = threadIdx.x;
+    for (uint32_t i = lane; i < a.cap_s + a.cap_b; i += 32) mv[i] = 0.0f;
     for (size_t p = blockIdx.x; p < n_pairs; p += gridDim.x) {
         const uint32_t qi = pair_q[p], x = pair_d[p];
-        if (S) for (uint32_t i = lane; i <= a.sq_mask; i += 32) sq[i] = make_uint2(kEmpty, 0u);
-        if (B) for (uint32_t i = lane; i <= a.bq_mask; i += 32) bq[i] = make_uint2(kEmpty, 0u);
         uint32_t qreg[16];
 #pragma unroll
         for (int k = 0; k < 16; ++k) qreg[k] = 0;
@@ -711,12 +772,17 @@ __global__ void __launch_bounds__(32) distances_kernel(const SearchArgs a, size_
             }
         }
         __syncwarp();
-        if (S)
-            for (uint32_t j = a.qs_off[qi] + lane; j < a.qs_off[qi + 1]; j += 32)
-                qtab_insert(sq, a.sq_mask, a.sq_shift, a.qs_idx[j], __fmul_rn(a.qs_val[j], a.w_sparse));
-        if (B)
-            for (uint32_t j = a.qb_off[qi] + lane; j < a.qb_off[qi + 1]; j += 32)
-                qtab_insert(bq, a.bq_mask, a.bq_shift, a.qb_idx[j], __fmul_rn(a.qb_val[j], a.w_bm25));
+        uint32_t nqs = 0, nqb = 0;
+        if (S) {
+            const uint32_t o = a.qs_off[qi];
+            nqs = a.qs_off[qi + 1] - o;
+            for (uint32_t j = lane; j < nqs; j += 32) sq[j] = make_uint2(a.qs_idx[o + j], __float_as_uint(__fmul_rn(a.qs_val[o + j], a.w_sparse)));
+        }
+        if (B) {
+            const uint32_t o = a.qb_off[qi];
+            nqb = a.qb_off[qi + 1] - o;
+            for (uint32_t j = lane; j < nqb; j += 32) bq[j] = make_uint2(a.qb_idx[o + j], __float_as_uint(__fmul_rn(a.qb_val[o + j], a.w_bm25)));
+        }
         const uint64_t m = a.meta[x];
         const uint32_t ns = meta_ns(m), nb = meta_nb(m);
         const uint4 *src = reinterpret_cast<const uint4 *>(a.rec + meta_off16(m) * 16ull);
@@ -726,9 +792,12 @@ __global__ void __launch_bounds__(32) distances_kernel(const SearchArgs a, size_
         if (S) { const uint32_t w = pad2(ns) / 2; for (uint32_t i = lane; i < w; i += 32) dst[o + i] = src[kDenseBytes / 16 + i]; o += w; }
         if (B) { const uint32_t w = pad2(nb) / 2; for (uint32_t i = lane; i < w; i += 32) dst[o + i] = src[kDenseBytes / 16 + pad2(ns) / 2 + i]; }
         __syncwarp();
-        uint32_t hit = 0;
-        const float d = score_record<F>(arena, ns, nb, qreg, sq, a.sq_mask, a.sq_shift, bq, a.bq_mask, a.bq_shift, lane, hit);
-        if (lane == 0) out[p] = d;
+        const uint8_t *rec[1] = {arena};
+        const uint32_t rns[1] = {ns}, rnb[1] = {nb};
+        uint32_t hit[1];
+        float d[1];
+        score_records<F, 1>(rec, rns, rnb, qreg, sq, nqs, bq, nqb, mv, a.cap_s, a.cap_b, lane, d, hit);
+        if (lane == 0) out[p] = d[0];
         __syncwarp();
     }
 }
@@ -739,7 +808,9 @@ __global__ void __launch_bounds__(32) distances_kernel(const SearchArgs a, size_
 static uint32_t pow2_at_least(uint32_t v) { uint32_t p = 32; while (p < v) p <<= 1; return p; }
 static uint32_t log2u(uint32_t p) { uint32_t l = 0; while ((1u << l) < p) ++l; return l; }
 
-static uint32_t layout(SearchArgs &a, uint32_t cands, uint32_t flags, uint32_t max_qs, uint32_t max_qb) {
+static uint32_t layout(SearchArgs &a, const ap_index *ix, uint32_t warps, uint32_t cands, uint32_t flags, uint32_t max_qs, uint32_t max_qb) {
+    a.cap_s = (flags & PF_SPARSE) ? pad2(ix->max_ns) : 0u;
+    a.cap_b = (flags & PF_BM25) ? pad2(ix->max_nb) : 0u;
     uint32_t o = 16 + 64;
     auto take = [&](uint32_t bytes, uint32_t align) { o = (o + align - 1) / align * align; uint32_t r = o; o += bytes; return r; };
     a.o_pool_id = take(4 * (cands + 32), 16);
@@ -750,11 +821,9 @@ static uint32_t layout(SearchArgs &a, uint32_t cands, uint32_t flags, uint32_t m
     a.vis_mask = vis - 1;
     a.o_vis = take(4 * vis, 16);
     a.o_info = take(8 * 32, 16);
-    const uint32_t sqn = pow2_at_least(4 * std::max(1u, max_qs)), bqn = pow2_at_least(4 * std::max(1u, max_qb));
-    a.sq_mask = sqn - 1; a.sq_shift = 32 - log2u(sqn);
-    a.bq_mask = bqn - 1; a.bq_shift = 32 - log2u(bqn);
-    a.o_sq = take((flags & PF_SPARSE) ? 8 * sqn : 0, 16);
-    a.o_bq = take((flags & PF_BM25) ? 8 * bqn : 0, 16);
+    a.o_sq = take((flags & PF_SPARSE) ? 8 * std::max(1u, max_qs) : 0, 16);
+    a.o_bq = take((flags & PF_BM25) ? 8 * std::max(1u, max_qb) : 0, 16);
+    a.o_mv = take(4 * warps * kScoreBatch * (a.cap_s + a.cap_b), 16);
     a.o_kw = take((flags & PF_KEYWORD) ? 8 * kKeywordRing : 0, 16);
     a.o_arena = take(0, 128);
     return a.o_arena;  // fixed bytes before the arena
@@ -822,7 +891,7 @@ int search_launch(ap_index *ix, const SearchLaunch &L, uint32_t *launches) {
     fill_args(ix, L, a);
     int f = kernel_flags(L);
     if (!(f & PF_DENSE)) f &= ~PF_UNFUSED;
-    const uint32_t fixed = layout(a, L.cands, (uint32_t)f, L.max_qs, L.max_qb);
+    const uint32_t fixed = layout(a, ix, kSearchWarps, L.cands, (uint32_t)f, L.max_qs, L.max_qb);
     const uint32_t need = std::max(16u, need_bytes_for(ix, f));
     AP_CUDA(cudaMemsetAsync(ix->d_ctl, 0, 4, L.stream));  // next-query counter; the error word is sticky
     int rc = AP_ERR_ARG;
@@ -842,7 +911,7 @@ int distances_launch(ap_index *ix, const SearchLaunch &L, size_t n_pairs, const 
     fill_args(ix, L, a);
     int f = kernel_flags(L) & (PF_DENSE | PF_SPARSE | PF_BM25 | PF_UNFUSED);
     if (!(f & PF_DENSE)) f &= ~PF_UNFUSED;
-    const uint32_t fixed = layout(a, 32, (uint32_t)f, L.max_qs, L.max_qb);
+    const uint32_t fixed = layout(a, ix, 1, 32, (uint32_t)f, L.max_qs, L.max_qb);
     const size_t smem = fixed + record_bytes(ix->max_ns, ix->max_nb);
     const uint32_t grid = (uint32_t)std::min<size_t>(n_pairs, (size_t)ix->num_sms * 16);
     if (grid == 0) return AP_OK;
