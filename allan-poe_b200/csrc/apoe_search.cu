@@ -641,15 +641,35 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
             score_slots<F>(a, c, qreg, topm, my_meta, my_need);
             if (tid == 0) c.t_mark = clock64();
 
-            // sort the 32 staged entries, decide whether the pool changes at all
+            // Order the staged entries for the merge.  Only entries that can enter the pool (distance <= the pool's
+            // last) are observable afterwards: the rest is dropped by the merge and overwritten by the next expansion
+            // (the visited-set reset uses the staged ids as a set).  No such entry: nothing to do.  Otherwise, when
+            // their distances are all different, the reference's bitonic network leaves them in ascending order at the
+            // front, which a rank count reproduces; with ties its exact compare-exchange sequence is replayed.
             if (warp == 0) {
                 float d = stg_dis[lane];
                 uint32_t id = stg_id[lane];
                 if (KG && my_tag) d = __fsub_rn(d, __fdiv_rn(a.kg_weight, (float)my_hop));
-                warp_sort32<KG>(d, id, my_ent, my_hop, lane);
-                stg_id[lane] = id; stg_dis[lane] = d;
-                if (KG) { c.pool_ent[topm + lane] = my_ent; c.pool_hop[topm + lane] = my_hop; }
-                if (lane == 0) c.ctl[CTL_MERGE] = (d <= pool_dis[topm - 1]) ? 1u : 0u;
+                const bool q = d <= pool_dis[topm - 1];
+                const uint32_t qm = __ballot_sync(kFull, q);
+                if (qm != 0) {
+                    uint32_t less = 0, eq = 0;
+                    for (uint32_t m = qm; m; m &= m - 1) {
+                        const float dk = __shfl_sync(kFull, d, __ffs(m) - 1);
+                        less += dk < d; eq += dk == d;
+                    }
+                    if (__any_sync(kFull, q && eq > 1)) {
+                        warp_sort32<KG>(d, id, my_ent, my_hop, lane);
+                        stg_id[lane] = id; stg_dis[lane] = d;
+                        if (KG) { c.pool_ent[topm + lane] = my_ent; c.pool_hop[topm + lane] = my_hop; }
+                    } else {
+                        const uint32_t pos = q ? less : __popc(qm) + __popc(~qm & ((1u << lane) - 1u));
+                        __syncwarp();
+                        stg_id[pos] = id; stg_dis[pos] = q ? d : 3.0e38f;
+                        if (KG) { c.pool_ent[topm + pos] = my_ent; c.pool_hop[topm + pos] = my_hop; }
+                    }
+                }
+                if (lane == 0) c.ctl[CTL_MERGE] = qm != 0 ? 1u : 0u;
             }
             __syncthreads();
             if (tid == 0) { const long long t = clock64(); c.t_sort += t - c.t_mark; c.t_mark = t; }
