@@ -29,7 +29,7 @@ constexpr int kKeywordRing = 32;  // ref: KEYWORD, src/query.cu:18
 constexpr int kMergeMax = (AP_MAX_CANDS + 32 + kSearchThreads - 1) / kSearchThreads;
 
 enum : int { PF_DENSE = 1, PF_SPARSE = 2, PF_BM25 = 4, PF_KEYWORD = 8, PF_KG = 16, PF_UNFUSED = 32 };
-enum : int { CTL_QUERY = 0, CTL_SEL = 1, CTL_BATCH = 2, CTL_LAST = 3, CTL_MERGE = 4, CTL_SLOT = 5, CTL_KWNUM = 6, CTL_M = 7 };
+enum : int { CTL_QUERY = 0, CTL_SEL = 1, CTL_BATCH = 2, CTL_LAST = 3, CTL_MERGE = 4, CTL_SLOT = 5, CTL_KWNUM = 6, CTL_M = 7, CTL_MULT_S = 8, CTL_MULT_B = 9 };
 
 struct SearchArgs {
     const FatEdge *fat;
@@ -52,9 +52,18 @@ struct SearchArgs {
     unsigned long long *cnt;  // [0] expansions, [1] evaluations, [2] gathered bytes
     uint32_t arena_bytes;
     uint32_t vis_mask;           // visited table size - 1
-    uint32_t cap_s, cap_b;       // per-record match scratch: pad2(longest sparse row), pad2(longest BM25 row) floats
+    uint32_t ts_slots, ts_shift; // collision-free table of the query's sparse row (0 slots: not allocated)
+    uint32_t tb_slots, tb_shift; // same for the BM25 row
     // shared-memory byte offsets
-    uint32_t o_pool_id, o_pool_dis, o_pool_ent, o_pool_hop, o_vis, o_info, o_sq, o_bq, o_mv, o_kw, o_arena;
+    uint32_t o_pool_id, o_pool_dis, o_pool_ent, o_pool_hop, o_vis, o_info, o_sq, o_bq, o_ts, o_tb, o_kw, o_arena;
+};
+
+// A query row as the scoring code sees it: the terms as given (ascending ids; BM25 ids may carry the keyword flag
+// in bit 31) and, when the row is short, a collision-free hash table: slot = (id * mult) >> shift, every slot holds
+// at most one term, so a lookup is one shared-memory load and one compare.  mult == 0: no table, use the terms.
+struct QRow {
+    const uint2 *terms; uint32_t n;
+    const uint2 *tab; uint32_t shift, mult;
 };
 
 struct Ctx {  // per-thread view of the CTA's shared state
@@ -66,8 +75,8 @@ struct Ctx {  // per-thread view of the CTA's shared state
     uint32_t *vis;
     uint2 *info;
     uint2 *sq, *bq;     // the query's sparse / BM25 terms (id, weighted value), as given
-    float *mv;          // this warp's match scratch, kScoreBatch x (cap_s + cap_b) floats, all zero between uses
-    uint32_t nqs, nqb;
+    uint2 *ts, *tb;     // their collision-free tables
+    QRow qs, qb;
     uint32_t *kw_id;
     float *kw_dis;
     uint8_t *arena;
@@ -93,19 +102,19 @@ __device__ __forceinline__ uint32_t vis_insert(uint32_t *tab, uint32_t mask, uin
 }
 
 constexpr int kScoreBatch = 2;  // records a warp scores side by side (independent instruction streams)
+constexpr int kPerfectMax = 32; // query rows up to this many terms get a collision-free hash table
 
 // Fused distances of R records staged in shared memory, computed by a full warp.  Valid in lane 0.
 //   dense : HFMA2 in the reference's lane / chunk association (src/query.cu:538-554);
-//   sparse: every query term (one per lane) finds its position in the document's ascending id list by a
-//           branch-free binary search and drops its weighted value into a per-record scratch row; each lane then
-//           walks the document's pairs j = lane, lane + 32, ... in ascending order and multiply-adds
-//           scratch[j] * value[j] in fp32 -- unmatched positions hold 0 and leave the sum unchanged, so the per-lane
-//           sums are exactly those of cal_sparse_dist / cal_bm25_dist (include/utils.cuh:299-340);
+//   sparse: each lane walks the document's pairs j = lane, lane + 32, ... in ascending order, looks the id up in the
+//           query row and multiply-adds matches in fp32 -- the per-lane sums of cal_sparse_dist / cal_bm25_dist
+//           (include/utils.cuh:299-340).  The lookup is the collision-free table when the row has one (all loads of
+//           a 128-term chunk in flight together, misses contribute a zero product, which leaves the sum unchanged),
+//           else the reference's own binary search over the query row;
 //   then the reference's shfl_down trees and its double-precision `1.0 - dense - sparse`.
 template <int F, int R>
 __device__ __forceinline__ void score_records(const uint8_t *const (&rec)[R], const uint32_t (&ns)[R], const uint32_t (&nb)[R],
-                                              const uint32_t (&qreg)[16], const uint2 *qs, uint32_t nqs, const uint2 *qb,
-                                              uint32_t nqb, float *mv, uint32_t cap_s, uint32_t cap_b, int lane,
+                                              const uint32_t (&qreg)[16], const QRow &qs, const QRow &qb, int lane,
                                               float (&out)[R], uint32_t (&hit)[R]) {
     constexpr bool D = (F & PF_DENSE) != 0, S = (F & PF_SPARSE) != 0, B = (F & PF_BM25) != 0, UNF = (F & PF_UNFUSED) != 0;
     uint32_t acc[R];
@@ -131,69 +140,70 @@ __device__ __forceinline__ void score_records(const uint8_t *const (&rec)[R], co
 #pragma unroll
         for (int r = 0; r < R; ++r) p[r] += kDenseBytes;
     }
-    // one pass for the sparse section, one for the BM25 section
 #pragma unroll
     for (int sec = 0; sec < 2; ++sec) {
         if ((sec == 0 && !S) || (sec == 1 && !B)) continue;
-        const uint2 *q = sec == 0 ? qs : qb;
-        const uint32_t nq = sec == 0 ? nqs : nqb;
+        const QRow &q = sec == 0 ? qs : qb;
+        const uint32_t keymask = sec == 0 ? 0xFFFFFFFFu : 0x7FFFFFFFu;
         const uint2 *pr[R];
-        float *m[R];
         uint32_t cnt[R], nmax = 0;
+        float part[R];
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             pr[r] = reinterpret_cast<const uint2 *>(p[r]);
-            m[r] = mv + r * (cap_s + cap_b) + (sec == 0 ? 0u : cap_s);
             cnt[r] = sec == 0 ? ns[r] : nb[r];
             nmax = max(nmax, cnt[r]);
+            part[r] = 0.0f;
         }
-        for (uint32_t t0 = 0; t0 < nq; t0 += 32) {
-            const uint32_t t = t0 + lane;
-            const bool on = t < nq;
-            const uint2 qt = on ? q[t] : make_uint2(kEmpty, 0u);
-            const uint32_t key = sec == 0 ? qt.x : (on ? (qt.x & 0x7FFFFFFFu) : kEmpty);
-            const bool first = on && (t == 0 || (q[t - 1].x & (sec == 0 ? 0xFFFFFFFFu : 0x7FFFFFFFu)) != key);
-            uint32_t base[R], n[R];
+        if (q.mult != 0) {
+            for (uint32_t j0 = 0; j0 < nmax; j0 += 128) {
+                uint2 pv[R][4], e[R][4];
 #pragma unroll
-            for (int r = 0; r < R; ++r) { base[r] = 0; n[r] = cnt[r]; }
-            for (uint32_t span = nmax; span > 1; span -= span >> 1) {
+                for (int t = 0; t < 4; ++t)
 #pragma unroll
-                for (int r = 0; r < R; ++r)
-                    if (n[r] > 1) {
-                        const uint32_t half = n[r] >> 1;
-                        base[r] += (pr[r][base[r] + half].x < key) ? half : 0u;
-                        n[r] -= half;
+                    for (int r = 0; r < R; ++r) {
+                        const uint32_t j = j0 + 32 * t + lane;
+                        pv[r][t] = j < cnt[r] ? pr[r][j] : make_uint2(kEmpty, 0u);  // padding never adds to the sum
+                    }
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+#pragma unroll
+                    for (int r = 0; r < R; ++r) e[r][t] = q.tab[(pv[r][t].x * q.mult) >> q.shift];
+#pragma unroll
+                for (int t = 0; t < 4; ++t)
+#pragma unroll
+                    for (int r = 0; r < R; ++r) {
+                        const bool match = (e[r][t].x & keymask) == pv[r][t].x;
+                        part[r] = __fmaf_rn(match ? __uint_as_float(e[r][t].y) : 0.0f, __uint_as_float(pv[r][t].y), part[r]);
+                        if (sec == 1) hit[r] |= match ? (e[r][t].x >> 31) : 0u;
                     }
             }
+        } else if (q.n != 0) {
+            // ref: cal_sparse_dist / cal_bm25_dist -- lower bound of the document's id in the query row
+            for (uint32_t j = lane; j < nmax; j += 32) {
 #pragma unroll
-            for (int r = 0; r < R; ++r)
-                if (cnt[r]) {
-                    uint32_t b = base[r];
-                    b += (pr[r][b].x < key) ? 1u : 0u;
-                    if (first && b < cnt[r] && pr[r][b].x == key) {
-                        m[r][b] = __uint_as_float(qt.y);
-                        if (sec == 1) hit[r] |= qt.x >> 31;
+                for (int r = 0; r < R; ++r)
+                    if (j < cnt[r]) {
+                        const uint2 pv = pr[r][j];
+                        uint32_t base = 0, n = q.n;
+                        while (n > 1) {
+                            const uint32_t half = n >> 1;
+                            base += ((q.terms[base + half].x & keymask) < pv.x) ? half : 0u;
+                            n -= half;
+                        }
+                        base += ((q.terms[base].x & keymask) < pv.x) ? 1u : 0u;
+                        if (base < q.n && (q.terms[base].x & keymask) == pv.x) {
+                            part[r] = __fmaf_rn(__uint_as_float(q.terms[base].y), __uint_as_float(pv.y), part[r]);
+                            if (sec == 1) hit[r] |= q.terms[base].x >> 31;
+                        }
                     }
-                }
-        }
-        __syncwarp();
-        float part[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r) part[r] = 0.0f;
-        for (uint32_t j = lane; j < nmax; j += 32) {
-#pragma unroll
-            for (int r = 0; r < R; ++r)
-                if (j < cnt[r]) {
-                    part[r] = __fmaf_rn(m[r][j], __uint_as_float(pr[r][j].y), part[r]);
-                    m[r][j] = 0.0f;
-                }
+            }
         }
 #pragma unroll
         for (int r = 0; r < R; ++r) {
             tot[r] = (sec == 1 && S) ? __fadd_rn(tot[r], part[r]) : part[r];
             p[r] += 8u * pad2(cnt[r]);
         }
-        __syncwarp();
     }
 #pragma unroll
     for (int mm = 16; mm > 0; mm >>= 1) {
@@ -211,6 +221,25 @@ __device__ __forceinline__ void score_records(const uint8_t *const (&rec)[R], co
         if (S || B) v -= (double)tot[r];
         out[r] = (float)v;
     }
+}
+
+// Collision-free multiplier for a query row of up to 32 terms (one per lane of the calling warp): the first of a
+// fixed sequence of odd constants under which all slots differ.  0 when none of 64 candidates works (or the row is
+// longer, or holds a repeated id): the caller then scores through the terms.  Fills the (pre-cleared) table.
+__device__ __forceinline__ uint32_t build_perfect_table(const uint2 *terms, uint32_t n, uint2 *tab, uint32_t shift, int lane) {
+    if (n == 0 || n > (uint32_t)kPerfectMax || shift == 0) return 0;
+    const bool on = (uint32_t)lane < n;
+    const uint2 t = on ? terms[lane] : make_uint2(0u, 0u);
+    const uint32_t key = t.x & 0x7FFFFFFFu;
+    uint32_t found = 0, slot = 0;
+    for (uint32_t trial = 0; trial < 64 && !found; ++trial) {
+        const uint32_t mult = (0x9E3779B1u + trial * 0x3C6EF372u) | 1u;
+        slot = on ? ((key * mult) >> shift) : (0x80000000u | (uint32_t)lane);
+        const uint32_t grp = __match_any_sync(kFull, slot);
+        if (__all_sync(kFull, __popc(grp) == 1)) found = mult;
+    }
+    if (found && on) tab[slot] = t;
+    return found;
 }
 
 // The reference's bitonic network on 32 elements held one per lane (include/utils.cuh:147-165 with len = 32):
@@ -330,7 +359,7 @@ __device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const u
                     const uint2 inf = valid ? c.info[slot[r]] : make_uint2(0u, 0u);
                     rec[r] = c.arena + inf.x; rns[r] = inf.y & 0xFFFFu; rnb[r] = inf.y >> 16;
                 }
-                score_records<F, kScoreBatch>(rec, rns, rnb, qreg, c.sq, c.nqs, c.bq, c.nqb, c.mv, a.cap_s, a.cap_b, lane, d, hit);
+                score_records<F, kScoreBatch>(rec, rns, rnb, qreg, c.qs, c.qb, lane, d, hit);
 #pragma unroll
                 for (int r = 0; r < kScoreBatch; ++r) {
                     const uint32_t h = KW ? __ballot_sync(kFull, hit[r] != 0) : 0u;
@@ -388,7 +417,10 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
     c.info = reinterpret_cast<uint2 *>(smem + a.o_info);
     c.sq = reinterpret_cast<uint2 *>(smem + a.o_sq);
     c.bq = reinterpret_cast<uint2 *>(smem + a.o_bq);
-    c.nqs = c.nqb = 0;
+    c.ts = reinterpret_cast<uint2 *>(smem + a.o_ts);
+    c.tb = reinterpret_cast<uint2 *>(smem + a.o_tb);
+    c.qs = QRow{c.sq, 0u, c.ts, a.ts_shift, 0u};
+    c.qb = QRow{c.bq, 0u, c.tb, a.tb_shift, 0u};
     c.kw_id = reinterpret_cast<uint32_t *>(smem + a.o_kw);
     c.kw_dis = reinterpret_cast<float *>(smem + a.o_kw + 4 * kKeywordRing);
     c.arena = smem + a.o_arena;
@@ -402,8 +434,6 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
     uint32_t *stg_id = pool_id + topm;
     float *stg_dis = pool_dis + topm;
 
-    c.mv = reinterpret_cast<float *>(smem + a.o_mv) + (size_t)c.warp * kScoreBatch * (a.cap_s + a.cap_b);
-    for (uint32_t i = tid; i < kSearchWarps * kScoreBatch * (a.cap_s + a.cap_b); i += kSearchThreads) reinterpret_cast<float *>(smem + a.o_mv)[i] = 0.0f;
     if (tid == 0) { mbar_init(c.mbar, 1); mbar_fence_init(); }
     __syncthreads();
 
@@ -438,17 +468,27 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
         __syncthreads();
         if (S) {
             const uint32_t o = a.qs_off[qi];
-            c.nqs = a.qs_off[qi + 1] - o;
-            for (uint32_t j = tid; j < c.nqs; j += kSearchThreads)
+            c.qs.n = a.qs_off[qi + 1] - o;
+            for (uint32_t j = tid; j < c.qs.n; j += kSearchThreads)
                 c.sq[j] = make_uint2(a.qs_idx[o + j], __float_as_uint(__fmul_rn(a.qs_val[o + j], a.w_sparse)));
+            for (uint32_t j = tid; j < a.ts_slots; j += kSearchThreads) c.ts[j] = make_uint2(kEmpty, 0u);
         }
         if (B) {
             const uint32_t o = a.qb_off[qi];
-            c.nqb = a.qb_off[qi + 1] - o;
-            for (uint32_t j = tid; j < c.nqb; j += kSearchThreads)
+            c.qb.n = a.qb_off[qi + 1] - o;
+            for (uint32_t j = tid; j < c.qb.n; j += kSearchThreads)
                 c.bq[j] = make_uint2(a.qb_idx[o + j], __float_as_uint(__fmul_rn(a.qb_val[o + j], a.w_bm25)));
+            for (uint32_t j = tid; j < a.tb_slots; j += kSearchThreads) c.tb[j] = make_uint2(kEmpty, 0u);
         }
         __syncthreads();
+        if (warp == 0) {
+            const uint32_t ms = (S && a.ts_slots) ? build_perfect_table(c.sq, c.qs.n, c.ts, a.ts_shift, lane) : 0u;
+            const uint32_t mb = (B && a.tb_slots) ? build_perfect_table(c.bq, c.qb.n, c.tb, a.tb_shift, lane) : 0u;
+            if (lane == 0) { c.ctl[CTL_MULT_S] = ms; c.ctl[CTL_MULT_B] = mb; }
+        }
+        __syncthreads();
+        c.qs.mult = c.ctl[CTL_MULT_S];
+        c.qb.mult = c.ctl[CTL_MULT_B];
 
         // ---- seeding -------------------------------------------------------------------------------------
         if (!KG) {
@@ -773,10 +813,10 @@ __global__ void __launch_bounds__(32) distances_kernel(const SearchArgs a, size_
     extern __shared__ __align__(128) uint8_t smem[];
     uint2 *sq = reinterpret_cast<uint2 *>(smem + a.o_sq);
     uint2 *bq = reinterpret_cast<uint2 *>(smem + a.o_bq);
-    float *mv = reinterpret_cast<float *>(smem + a.o_mv);
+    uint2 *ts = reinterpret_cast<uint2 *>(smem + a.o_ts);
+    uint2 *tb = reinterpret_cast<uint2 *>(smem + a.o_tb);
     uint8_t *arena = smem + a.o_arena;
     const int lane = threadIdx.x;
-    for (uint32_t i = lane; i < a.cap_s + a.cap_b; i += 32) mv[i] = 0.0f;
     for (size_t p = blockIdx.x; p < n_pairs; p += gridDim.x) {
         const uint32_t qi = pair_q[p], x = pair_d[p];
         uint32_t qreg[16];
@@ -792,17 +832,24 @@ __global__ void __launch_bounds__(32) distances_kernel(const SearchArgs a, size_
             }
         }
         __syncwarp();
-        uint32_t nqs = 0, nqb = 0;
+        QRow qs{sq, 0u, ts, a.ts_shift, 0u}, qb{bq, 0u, tb, a.tb_shift, 0u};
         if (S) {
             const uint32_t o = a.qs_off[qi];
-            nqs = a.qs_off[qi + 1] - o;
-            for (uint32_t j = lane; j < nqs; j += 32) sq[j] = make_uint2(a.qs_idx[o + j], __float_as_uint(__fmul_rn(a.qs_val[o + j], a.w_sparse)));
+            qs.n = a.qs_off[qi + 1] - o;
+            for (uint32_t j = lane; j < qs.n; j += 32) sq[j] = make_uint2(a.qs_idx[o + j], __float_as_uint(__fmul_rn(a.qs_val[o + j], a.w_sparse)));
+            for (uint32_t j = lane; j < a.ts_slots; j += 32) ts[j] = make_uint2(kEmpty, 0u);
         }
         if (B) {
             const uint32_t o = a.qb_off[qi];
-            nqb = a.qb_off[qi + 1] - o;
-            for (uint32_t j = lane; j < nqb; j += 32) bq[j] = make_uint2(a.qb_idx[o + j], __float_as_uint(__fmul_rn(a.qb_val[o + j], a.w_bm25)));
+            qb.n = a.qb_off[qi + 1] - o;
+            for (uint32_t j = lane; j < qb.n; j += 32) bq[j] = make_uint2(a.qb_idx[o + j], __float_as_uint(__fmul_rn(a.qb_val[o + j], a.w_bm25)));
+            for (uint32_t j = lane; j < a.tb_slots; j += 32) tb[j] = make_uint2(kEmpty, 0u);
         }
+        __syncwarp();
+        // odd pairs go through the table, even pairs through the terms, so both lookups are exercised
+        if (S && a.ts_slots && (p & 1)) qs.mult = build_perfect_table(sq, qs.n, ts, a.ts_shift, lane);
+        if (B && a.tb_slots && (p & 1)) qb.mult = build_perfect_table(bq, qb.n, tb, a.tb_shift, lane);
+        __syncwarp();
         const uint64_t m = a.meta[x];
         const uint32_t ns = meta_ns(m), nb = meta_nb(m);
         const uint4 *src = reinterpret_cast<const uint4 *>(a.rec + meta_off16(m) * 16ull);
@@ -816,7 +863,7 @@ __global__ void __launch_bounds__(32) distances_kernel(const SearchArgs a, size_
         const uint32_t rns[1] = {ns}, rnb[1] = {nb};
         uint32_t hit[1];
         float d[1];
-        score_records<F, 1>(rec, rns, rnb, qreg, sq, nqs, bq, nqb, mv, a.cap_s, a.cap_b, lane, d, hit);
+        score_records<F, 1>(rec, rns, rnb, qreg, qs, qb, lane, d, hit);
         if (lane == 0) out[p] = d[0];
         __syncwarp();
     }
@@ -829,8 +876,7 @@ static uint32_t pow2_at_least(uint32_t v) { uint32_t p = 32; while (p < v) p <<=
 static uint32_t log2u(uint32_t p) { uint32_t l = 0; while ((1u << l) < p) ++l; return l; }
 
 static uint32_t layout(SearchArgs &a, const ap_index *ix, uint32_t warps, uint32_t cands, uint32_t flags, uint32_t max_qs, uint32_t max_qb) {
-    a.cap_s = (flags & PF_SPARSE) ? pad2(ix->max_ns) : 0u;
-    a.cap_b = (flags & PF_BM25) ? pad2(ix->max_nb) : 0u;
+    (void)ix; (void)warps;
     uint32_t o = 16 + 64;
     auto take = [&](uint32_t bytes, uint32_t align) { o = (o + align - 1) / align * align; uint32_t r = o; o += bytes; return r; };
     a.o_pool_id = take(4 * (cands + 32), 16);
@@ -843,7 +889,13 @@ static uint32_t layout(SearchArgs &a, const ap_index *ix, uint32_t warps, uint32
     a.o_info = take(8 * 32, 16);
     a.o_sq = take((flags & PF_SPARSE) ? 8 * std::max(1u, max_qs) : 0, 16);
     a.o_bq = take((flags & PF_BM25) ? 8 * std::max(1u, max_qb) : 0, 16);
-    a.o_mv = take(4 * warps * kScoreBatch * (a.cap_s + a.cap_b), 16);
+    // collision-free tables for short query rows: 16 slots per term keeps the search for a multiplier short
+    a.ts_slots = ((flags & PF_SPARSE) && max_qs <= (uint32_t)kPerfectMax) ? pow2_at_least(16 * std::max(1u, max_qs)) : 0u;
+    a.tb_slots = ((flags & PF_BM25) && max_qb <= (uint32_t)kPerfectMax) ? pow2_at_least(16 * std::max(1u, max_qb)) : 0u;
+    a.ts_shift = a.ts_slots ? 32 - log2u(a.ts_slots) : 0u;
+    a.tb_shift = a.tb_slots ? 32 - log2u(a.tb_slots) : 0u;
+    a.o_ts = take(8 * a.ts_slots, 16);
+    a.o_tb = take(8 * a.tb_slots, 16);
     a.o_kw = take((flags & PF_KEYWORD) ? 8 * kKeywordRing : 0, 16);
     a.o_arena = take(0, 128);
     return a.o_arena;  // fixed bytes before the arena

@@ -84,6 +84,23 @@ def test_small_arena_batches_give_same_result(small, index):
     assert np.array_equal(ids0, ids1) and np.array_equal(dis0.view(np.uint32), dis1.view(np.uint32))
 
 
+def test_long_query_rows(small, index):
+    """Query rows longer than 32 terms take the per-term lookup instead of the collision-free table; rows of mixed
+    length in one batch take either, and both agree with the oracle bit for bit."""
+    ql = synth.make_queries(48, small.corpus.idf, seed=77, nnz_sparse=70, nnz_bm25=40)
+    QD = np.concatenate([ql.dense.numpy(), small.QD[:16]])
+    cat = lambda a, b: orc.CsrNp(np.concatenate([a.off, b.off[1:17] + a.off[-1]]), np.concatenate([a.idx, b.idx[:int(b.off[16])]]),
+                                 np.concatenate([a.val, b.val[:int(b.off[16])]]))
+    QS, QB = cat(orc.CsrNp.from_torch(ql.sparse), small.QS), cat(orc.CsrNp.from_torch(ql.bm25), small.QB)
+    for w, flags in (((1.0, 1.0, 1.0), 7), ((1.0, 0.0, 0.0), 2)):
+        eff = orc.effective_weights(small.D, small.S, small.B, QD, QS, QB, *w)
+        qd, qs, qb = orc.scale_queries(QD, QS, QB, *eff)
+        want_ids, want_dis, _ = orc.search(small.Dh, small.S, small.B, orc.f2h(qd), qs, qb, small.graph, small.ep, 64, flags)
+        ids, dis, _ = index.search(QD, QS, QB, cands=64, weights=w)
+        assert np.array_equal(ids, want_ids)
+        assert np.array_equal(dis.view(np.uint32), want_dis.view(np.uint32))
+
+
 def test_recall_against_exact_bruteforce(small, index):
     eff, qdh, qs, qb, qd = helpers.scaled_queries(small, (1.0, 1.0, 1.0))
     gt, _, _ = orc.bruteforce(small.D, small.S, small.B, qd, qs, qb, 7, 10)
