@@ -243,6 +243,18 @@ class Index:
         _check(lib().ap_search_host(self._h, C.byref(q), C.byref(o), _ptr(ids), _ptr(dis), C.byref(st)))
         return ids, dis, st
 
+    def search_static(self, qdense, qsparse, qbm25, cands=128, weights=(1.0, 1.0, 1.0), kg_weight=0.0, flags=0, ent=None):
+        """`search` for callers that must not allocate device memory: the batch is staged in the library's fixed
+        device array (8 MiB per GPU) and the call makes no allocation; batches that do not fit raise ApoeError(4)."""
+        q, keep = self._host_queries(qdense, qsparse, qbm25, ent)
+        o = SearchOpts(cands=cands, flags=flags, sparse_weight=weights[0], bm25_weight=weights[1],
+                       dense_weight=weights[2], kg_weight=kg_weight)
+        ids = np.empty((q.nq, cands), dtype=np.uint32)
+        dis = np.empty((q.nq, cands), dtype=np.float32)
+        st = SearchStats()
+        _check(lib().ap_search_host_static(self._h, C.byref(q), C.byref(o), _ptr(ids), _ptr(dis), C.byref(st)))
+        return ids, dis, st
+
     def search_device(self, queries, out_ids, out_dis, cands=128, weights=(1.0, 1.0, 1.0), kg_weight=0.0, flags=0,
                       ent=None, max_nnz=(0, 0), stream=None, stats=True, arena_bytes=0, ctas_per_sm=0):
         """Device tensors in and out (queries: object with CUDA .dense and .sparse/.bm25 CSRs).  The weights are

@@ -138,6 +138,8 @@ struct SearchLaunch {
     uint32_t *out_ids;
     float *out_dis;
     cudaStream_t stream;
+    uint32_t *ctl = nullptr;            // control words of the kernel (next query, error word); null = the index's own
+    unsigned long long *cnt = nullptr;  // counters; null = the index's own
 };
 int search_launch(ap_index *ix, const SearchLaunch &L, uint32_t *launches);
 int distances_launch(ap_index *ix, const SearchLaunch &L, size_t n_pairs, const uint32_t *pair_q,

@@ -5,6 +5,7 @@
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
+#include <mutex>
 
 #include "apoe_common.cuh"
 
@@ -615,3 +616,124 @@ int ap_debug_counters(ap_index *ix, uint64_t *out8) {
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------
+// Search from host buffers without any allocation.
+//
+// ap_search_host stages a batch's queries and results in grow-only device buffers that it cudaMalloc's on demand.
+// Some callers must not allocate once they are serving: a process that has handed the whole GPU to another memory
+// pool has nothing left for cudaMalloc to give, and cudaMalloc / cudaFree may synchronise the device, which a
+// latency-bound query loop cannot afford.  For them the staging area below is part of the library image itself: a
+// file-scope device array that every GPU loading the library holds until the process exits.
+// ---------------------------------------------------------------------------------------------------------
+namespace apoe {
+
+constexpr size_t kStaticScratchBytes = AP_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+// In host code the array's name is only a handle for the runtime, never an address a kernel could use: the device
+// address is asked for once per device, with that device current, and cached.
+constexpr int kMaxDevices = 64;
+static unsigned char *g_static_ptr[kMaxDevices] = {nullptr};
+
+static int static_scratch_address(int device, unsigned char **out) {
+    if (device < 0 || device >= kMaxDevices) return fail(AP_ERR_ARG, "device %d out of range", device);
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    if (!g_static_ptr[device]) {
+        AP_CUDA(cudaSetDevice(device));
+        void *p = nullptr;
+        AP_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+        if (!p) return fail(AP_ERR_CUDA, "cudaGetSymbolAddress returned a null address for the static scratch");
+        g_static_ptr[device] = static_cast<unsigned char *>(p);
+    }
+    *out = g_static_ptr[device];
+    return AP_OK;
+}
+
+}  // namespace apoe
+
+extern "C" int ap_search_host_static(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids,
+                                     float *out_dis, ap_search_stats *stats) {
+    using namespace apoe;
+    const auto t0 = std::chrono::high_resolution_clock::now();
+    AP_TRY(check_search_args(ix, q, opts));
+    if (!out_ids || !out_dis) return fail(AP_ERR_ARG, "null output pointer");
+    AP_CUDA(cudaSetDevice(ix->device));
+    float ws = opts->sparse_weight, wb = opts->bm25_weight, wd = opts->dense_weight;
+    if (!(opts->flags & AP_SEARCH_RAW_WEIGHTS)) AP_TRY(effective_weights_host(ix, q, &ws, &wb, &wd));
+    uint32_t path = 0, mode = 0;
+    AP_TRY(dispatch_path(opts->flags, ws, wb, wd, opts->kg_weight, &path, &mode));
+    if ((mode & AP_SEARCH_KG) && ix->n_ent == 0) return fail(AP_ERR_STATE, "kg_weight >= 1e-5 but no knowledge graph is loaded");
+    uint32_t mqs = 0, mqb = 0;
+    AP_TRY(host_query_limits(ix, q, mode, &mqs, &mqb));
+
+    // carve the static array: control words and counters first, then the batch, every piece 256-byte aligned
+    const uint32_t nq = q->nq, cands = opts->cands;
+    const size_t nzs = q->sparse.off[nq], nzb = q->bm25.off[nq];
+    const size_t nze = (mode & AP_SEARCH_KG) ? q->ent_off[nq] : 0;
+    size_t need = 0;
+    auto carve = [&](size_t bytes) { const size_t at = need; need = (need + bytes + 255) / 256 * 256; return at; };
+    const size_t o_ctl = carve(64), o_cnt = carve(64);
+    const size_t o_qd = carve((size_t)nq * kDim * 4), o_so = carve((size_t)(nq + 1) * 4), o_si = carve(nzs * 4), o_sv = carve(nzs * 4);
+    const size_t o_bo = carve((size_t)(nq + 1) * 4), o_bi = carve(nzb * 4), o_bv = carve(nzb * 4);
+    const size_t o_eo = carve((mode & AP_SEARCH_KG) ? (size_t)(nq + 1) * 4 : 0), o_ei = carve(nze * 4);
+    const size_t o_ids = carve((size_t)nq * cands * 4), o_dis = carve((size_t)nq * cands * 4);
+    if (need > kStaticScratchBytes)
+        return fail(AP_ERR_LIMIT, "this batch needs %zu bytes of device staging, the static area holds %zu (%u queries, cands %u): "
+                                  "send fewer queries per call or use ap_search_host", need, (size_t)kStaticScratchBytes, nq, cands);
+    unsigned char *base = nullptr;
+    AP_TRY(static_scratch_address(ix->device, &base));
+
+    cudaStream_t st = 0;
+    // the area keeps whatever the previous call left: next-query counter, error word and counters start at zero
+    AP_CUDA(cudaMemsetAsync(base + o_ctl, 0, 64, st));
+    AP_CUDA(cudaMemsetAsync(base + o_cnt, 0, 64, st));
+    size_t h2d = 0;
+    auto put = [&](size_t at, const void *src, size_t bytes) -> int {
+        if (bytes) AP_CUDA(cudaMemcpyAsync(base + at, src, bytes, cudaMemcpyHostToDevice, st));
+        h2d += bytes;
+        return AP_OK;
+    };
+    AP_TRY(put(o_qd, q->dense, (size_t)nq * kDim * 4));
+    AP_TRY(put(o_so, q->sparse.off, (size_t)(nq + 1) * 4)); AP_TRY(put(o_si, q->sparse.idx, nzs * 4)); AP_TRY(put(o_sv, q->sparse.val, nzs * 4));
+    AP_TRY(put(o_bo, q->bm25.off, (size_t)(nq + 1) * 4)); AP_TRY(put(o_bi, q->bm25.idx, nzb * 4)); AP_TRY(put(o_bv, q->bm25.val, nzb * 4));
+    if (mode & AP_SEARCH_KG) { AP_TRY(put(o_eo, q->ent_off, (size_t)(nq + 1) * 4)); AP_TRY(put(o_ei, q->ent_idx, nze * 4)); }
+
+    SearchLaunch L{};
+    L.qdense = reinterpret_cast<const float *>(base + o_qd);
+    L.qs_off = reinterpret_cast<const uint32_t *>(base + o_so); L.qs_idx = reinterpret_cast<const uint32_t *>(base + o_si);
+    L.qs_val = reinterpret_cast<const float *>(base + o_sv);
+    L.qb_off = reinterpret_cast<const uint32_t *>(base + o_bo); L.qb_idx = reinterpret_cast<const uint32_t *>(base + o_bi);
+    L.qb_val = reinterpret_cast<const float *>(base + o_bv);
+    if (mode & AP_SEARCH_KG) { L.qe_off = reinterpret_cast<const uint32_t *>(base + o_eo); L.qe_idx = reinterpret_cast<const uint32_t *>(base + o_ei); }
+    L.out_ids = reinterpret_cast<uint32_t *>(base + o_ids); L.out_dis = reinterpret_cast<float *>(base + o_dis);
+    L.ctl = reinterpret_cast<uint32_t *>(base + o_ctl); L.cnt = reinterpret_cast<unsigned long long *>(base + o_cnt);
+    L.nq = nq; L.max_qs = mqs; L.max_qb = mqb;
+    L.w_sparse = ws; L.w_bm25 = wb; L.w_dense = wd; L.kg_weight = opts->kg_weight;
+    L.cands = cands; L.flags = (opts->flags & ~(AP_SEARCH_KEYWORD | AP_SEARCH_KG)) | mode; L.path = path;
+    L.arena_bytes = opts->arena_bytes; L.ctas_per_sm = opts->ctas_per_sm; L.stream = st;
+    uint32_t launches = 0;
+    AP_CUDA(cudaEventRecord(ix->ev0, st));
+    AP_TRY(search_launch(ix, L, &launches));
+    AP_CUDA(cudaEventRecord(ix->ev1, st));
+    AP_CUDA(cudaMemcpyAsync(out_ids, L.out_ids, (size_t)nq * cands * 4, cudaMemcpyDeviceToHost, st));
+    AP_CUDA(cudaMemcpyAsync(out_dis, L.out_dis, (size_t)nq * cands * 4, cudaMemcpyDeviceToHost, st));
+    uint32_t ctl[2] = {0, 0};
+    unsigned long long cnt[3] = {0, 0, 0};
+    AP_CUDA(cudaMemcpyAsync(ctl, L.ctl, 8, cudaMemcpyDeviceToHost, st));
+    AP_CUDA(cudaMemcpyAsync(cnt, L.cnt, 24, cudaMemcpyDeviceToHost, st));
+    AP_CUDA(cudaStreamSynchronize(st));
+    if (ctl[1] != 0) return fail(AP_ERR_DEVICE, "search kernel raised error word %u (a bounded wait ran out or a record exceeds the arena)", ctl[1]);
+    if (stats) {
+        float ms = 0.f;
+        AP_CUDA(cudaEventElapsedTime(&ms, ix->ev0, ix->ev1));
+        stats->kernel_ms = ms; stats->expansions = cnt[0]; stats->evaluations = cnt[1]; stats->gathered_bytes = cnt[2];
+        stats->eff_sparse = ws; stats->eff_bm25 = wb; stats->eff_dense = wd; stats->path = path; stats->launches = launches;
+        const size_t d2h = (size_t)nq * cands * 8;
+        stats->h2d_bytes_lo = (uint32_t)h2d; stats->h2d_bytes_hi = (uint32_t)((uint64_t)h2d >> 32);
+        stats->d2h_bytes_lo = (uint32_t)d2h; stats->d2h_bytes_hi = (uint32_t)((uint64_t)d2h >> 32);
+        stats->total_ms = std::chrono::duration<double, std::milli>(std::chrono::high_resolution_clock::now() - t0).count();
+    }
+    return AP_OK;
+}

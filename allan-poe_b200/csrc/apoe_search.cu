@@ -937,7 +937,7 @@ static void fill_args(ap_index *ix, const SearchLaunch &L, SearchArgs &a) {
     a.qe_off = L.qe_off; a.qe_idx = L.qe_idx;
     a.nq = L.nq; a.w_sparse = L.w_sparse; a.w_bm25 = L.w_bm25; a.w_dense = L.w_dense; a.kg_weight = L.kg_weight;
     a.cands = L.cands; a.out_ids = L.out_ids; a.out_dis = L.out_dis;
-    a.ctl = ix->d_ctl; a.cnt = ix->d_cnt;
+    a.ctl = L.ctl ? L.ctl : ix->d_ctl; a.cnt = L.cnt ? L.cnt : ix->d_cnt;
 }
 
 static int kernel_flags(const SearchLaunch &L) {
@@ -965,7 +965,7 @@ int search_launch(ap_index *ix, const SearchLaunch &L, uint32_t *launches) {
     if (!(f & PF_DENSE)) f &= ~PF_UNFUSED;
     const uint32_t fixed = layout(a, ix, kSearchWarps, L.cands, (uint32_t)f, L.max_qs, L.max_qb);
     const uint32_t need = std::max(16u, need_bytes_for(ix, f));
-    AP_CUDA(cudaMemsetAsync(ix->d_ctl, 0, 4, L.stream));  // next-query counter; the error word is sticky
+    AP_CUDA(cudaMemsetAsync(a.ctl, 0, 4, L.stream));  // next-query counter; the error word is sticky
     int rc = AP_ERR_ARG;
     switch (f) {
 #define X(FL) case (FL): rc = launch_one<(FL)>(ix, a, fixed, L.ctas_per_sm, L.arena_bytes, need, L.stream); break;

@@ -34,6 +34,7 @@ extern "C" {
 #define AP_KNN 64            /* k-NN list width before pruning, ref: src/index.cu:6 */
 #define AP_ENTRY_POINTS 32   /* ref: src/index.cu:923, src/query.cu:440-444 */
 #define AP_MAX_CANDS 512     /* ref: src/query.cu:9 */
+#define AP_STATIC_SCRATCH_BYTES (8u << 20) /* staging area of ap_search_host_static, held by every GPU that loads the library */
 
 typedef struct ap_index ap_index;
 
@@ -191,6 +192,18 @@ int ap_search_host(ap_index *ix, const ap_queries *q, const ap_search_opts *opts
  * Asynchronous with respect to the host unless stats != NULL. */
 int ap_search_device(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids, float *out_dis,
                      void *stream, ap_search_stats *stats);
+
+/* No counterpart in the reference.  ap_search_host for callers that cannot allocate device memory while they serve:
+ * a process whose GPU memory is entirely owned by another pool (cudaMalloc would fail), or a query loop that cannot
+ * tolerate the device-wide synchronisation cudaMalloc / cudaFree may cause.  Same arguments, same results, but the
+ * device staging of the batch (queries, control words, results) lives in a fixed array inside the library image
+ * (AP_STATIC_SCRATCH_BYTES per GPU, held until the process exits) and the call performs no cudaMalloc, cudaFree or
+ * other allocating call.  A batch whose staging does not fit returns AP_ERR_LIMIT and says how much it needs.
+ * The first call on a device looks up the array's device address (once per device); make that first call before
+ * any stream capture starts.  All calls on a device share the array, whatever index they use: it keeps the previous
+ * call's contents (the call clears what must start at zero), and two calls that overlap on the GPU race. */
+int ap_search_host_static(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids,
+                          float *out_dis, ap_search_stats *stats);
 
 /* Fused distances of explicit (query, doc) pairs with the search kernel's arithmetic (test hook).
  * Host buffers; weights are applied as given (no normalisation). */
