@@ -259,7 +259,7 @@ struct JoinArgs {
     uint32_t prop_per;                     // partners proposed to each participant (<= kPropPerMax)
     uint32_t o_tab, o_dm, o_arena;
 };
-constexpr int kJoinThreads = 256;
+constexpr int kJoinThreads = 512;
 
 __device__ __forceinline__ void jtab_insert(uint2 *tab, uint32_t mask, uint32_t shift, uint32_t key, uint32_t valbits) {
     uint32_t h = (key * 2654435761u) >> shift;
@@ -524,6 +524,19 @@ __global__ void __launch_bounds__(128, 8) knn_merge_kernel(Knn k) {
     if (lane == 0 && changed) atomicAdd(k.stats + 1, (unsigned long long)changed);
 }
 
+// Reverse pass (ref: merge_reverse_plus, src/index.cu:386-478): every list entry (v -> u, d) is offered to u as
+// (u -> v, d); the following merge keeps u's best 64.  Offers beyond the proposal capacity keep the closer ones.
+__global__ void knn_reverse_kernel(Knn k) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= k.n * (uint32_t)kK) return;
+    const uint32_t v = i / kK, u = k.ids[i] & 0x7FFFFFFFu;
+    const float d = k.dis[i];
+    if (u >= k.n || u == v || !(d < kInfDis)) return;
+    if (!(d < k.dis[(size_t)u * kK + kK - 1])) return;           // cannot enter u's list
+    const uint32_t t = atomicAdd(&k.propn[u], 1u);
+    if (t < kPropCap) k.prop[(size_t)u * kPropCap + t] = make_uint2(__float_as_uint(d), v);
+}
+
 __global__ void knn_finish_kernel(Knn k, uint32_t *out_ids) {  // strip flags; unfilled slots point at a valid id
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= k.n * (uint32_t)kK) return;
@@ -673,29 +686,61 @@ __global__ void __launch_bounds__(kPruneThreads, 2) prune_kernel(const PruneArgs
             const uint32_t ns = meta_ns(sm), nb = meta_nb(sm), pns = pad2(ns);
             float sp = 0.0f, bm = 0.0f;
             uint32_t kw = 0;
-            for (uint32_t j = lane; j < ns; j += 32) {
-                const uint2 p = __ldg(pr + j);
-                uint32_t h = (p.x * 2654435761u) >> a.tab_shift;
-                for (uint32_t s = 0; s <= a.tab_mask; ++s) {
-                    const uint2 e = tab[h];
-                    if (e.x == kEmpty) break;
-                    if (e.x == p.x) { sp = __fmaf_rn(__uint_as_float(e.y), __uint_as_float(p.y), sp); break; }
-                    h = (h + 1) & a.tab_mask;
+            // Four terms per lane in flight: all first slots are read together, colliding ones take the next slot
+            // together, longer chains are walked one by one; the multiply-adds then run in ascending term order
+            // with the matched value or zero (a zero product leaves the sum as it is), so each lane's partial is
+            // the one the reference's per-term loop produces.
+#pragma unroll
+            for (int sec = 0; sec < 2; ++sec) {
+                const uint2 *row = sec == 0 ? pr : pr + pns;
+                const uint32_t cnt = sec == 0 ? ns : nb;
+                float part = 0.0f;
+                for (uint32_t j0 = 0; j0 < cnt; j0 += 128) {
+                    uint2 pv[4], e[4];
+                    uint32_t key[4], hs[4], chain = 0;
+                    float qv[4];
+                    bool fnd[4];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        const uint32_t j = j0 + 32 * t + lane;
+                        pv[t] = j < cnt ? __ldg(row + j) : make_uint2(kEmpty, 0u);
+                        key[t] = (sec == 1 && j < cnt) ? (pv[t].x | 0x80000000u) : pv[t].x;
+                        hs[t] = (key[t] * 2654435761u) >> a.tab_shift;
+                    }
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) e[t] = tab[hs[t]];
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        fnd[t] = e[t].x == key[t];
+                        qv[t] = fnd[t] ? __uint_as_float(e[t].y) : 0.0f;
+                        chain |= (!fnd[t] && e[t].x != kEmpty) ? (1u << t) : 0u;
+                    }
+                    if (__any_sync(kFull, chain != 0)) {
+#pragma unroll
+                        for (int t = 0; t < 4; ++t) e[t] = tab[(hs[t] + 1) & a.tab_mask];
+#pragma unroll
+                        for (int t = 0; t < 4; ++t)
+                            if ((chain >> t) & 1u) {
+                                if (e[t].x == key[t]) { fnd[t] = true; qv[t] = __uint_as_float(e[t].y); }
+                                else if (e[t].x != kEmpty) {
+                                    uint32_t h = (hs[t] + 2) & a.tab_mask;
+                                    for (uint32_t s2 = 0; s2 < a.tab_mask; ++s2) {
+                                        const uint2 e2 = tab[h];
+                                        if (e2.x == kEmpty) break;
+                                        if (e2.x == key[t]) { fnd[t] = true; qv[t] = __uint_as_float(e2.y); break; }
+                                        h = (h + 1) & a.tab_mask;
+                                    }
+                                }
+                            }
+                    }
+#pragma unroll
+                    for (int t = 0; t < 4; ++t) {
+                        part = __fmaf_rn(qv[t], __uint_as_float(pv[t].y), part);
+                        // a BM25 term of s that the candidate lacks but the node owns (ref :144-149)
+                        if (sec == 1 && j0 + 32 * t + lane < cnt && !fnd[t] && set_contains(own, a.own_mask, a.own_shift, pv[t].x)) kw = 1;
+                    }
                 }
-            }
-            for (uint32_t j = lane; j < nb; j += 32) {
-                const uint2 p = __ldg(pr + pns + j);
-                const uint32_t key = p.x | 0x80000000u;
-                uint32_t h = (key * 2654435761u) >> a.tab_shift;
-                bool found = false;
-                for (uint32_t s = 0; s <= a.tab_mask; ++s) {
-                    const uint2 e = tab[h];
-                    if (e.x == kEmpty) break;
-                    if (e.x == key) { bm = __fmaf_rn(__uint_as_float(e.y), __uint_as_float(p.y), bm); found = true; break; }
-                    h = (h + 1) & a.tab_mask;
-                }
-                // a term of s that the candidate lacks but the node owns (ref :144-149)
-                if (!found && set_contains(own, a.own_mask, a.own_shift, p.x)) kw = 1;
+                if (sec == 0) sp = part; else bm = part;
             }
             float tot = __fadd_rn(sp, bm);
 #pragma unroll
@@ -1003,6 +1048,12 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
         const unsigned long long upd = st[1] - prev_updates;
         prev_updates = st[1];
         if (it >= 3 && upd < (unsigned long long)n * kK / 1000) { ++it; break; }  // < 0.1 % of the entries changed
+    }
+    if (!(o.reserved[1] & 1u)) {   // reverse pass unless switched off
+        AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
+        knn_reverse_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k);
+        knn_merge_kernel<<<(n + 3) / 4, 128>>>(k);
+        launches += 2;
     }
     for (auto &e : ev) cudaEventDestroy(e);
     AP_CUDA(cudaDeviceSynchronize());

@@ -262,7 +262,7 @@ def run_own(args):
                 "algorithmic_bytes_per_launch": int(algo), "expansions_per_query": round(st.expansions / nq, 1),
                 "evaluations_per_query": round(st.evaluations / nq, 1)}
         cpu, recall = None, None
-        if not args.skip_cpu and not sharded:
+        if not args.skip_cpu and not sharded and world == 1:
             D = corpus.dense.cpu().numpy()
             sys.path.insert(0, os.path.join(ROOT, "oracle"))
             import apoe_oracle as orc
