@@ -168,10 +168,11 @@ class Index:
     def save_graph(self, path: str) -> None:
         _check(lib().ap_index_save_graph(self._h, path.encode()))
 
-    def build(self, iterations: int = 0, seed: int = 0, flags: int = 0, dense_scale: float = 0.0, prop_per: int = 0, tune: int = 0) -> BuildStats:
+    def build(self, iterations: int = 0, seed: int = 0, flags: int = 0, dense_scale: float = 0.0, prop_per: int = 0, tune: int = 0, seed_take: int = 0) -> BuildStats:
         o = BuildOpts(iterations=iterations, seed=seed, flags=flags, dense_scale=dense_scale)
         o.reserved[0] = prop_per
         o.reserved[1] = tune
+        o.reserved[2] = seed_take
         st = BuildStats()
         _check(lib().ap_index_build(self._h, C.byref(o), C.byref(st)))
         return st

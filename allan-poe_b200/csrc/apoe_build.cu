@@ -10,10 +10,12 @@
 // and BM25 inner products by hashing one row and probing with the other), proposes the best partners to every
 // participant and merges proposals into the sorted lists with a warp bitonic sort.
 #include <cub/device/device_radix_sort.cuh>
+#include <cub/device/device_scan.cuh>
 
 #include <algorithm>
 #include <chrono>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 
 #include "apoe_common.cuh"
@@ -89,6 +91,15 @@ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
     return x;
 }
 
+// Pair ownership (experimental): mode 0 offers an evaluated pair to both ends, mode 1 to exactly one end chosen by
+// a hash of the two ids, mode 2 to one end for half of the pairs and to both for the rest.
+__device__ __forceinline__ bool pair_owned(uint32_t mode, uint32_t me, uint32_t other) {
+    if (mode == 0) return true;
+    const uint32_t lo = min(me, other), hi = max(me, other), h = mix32(lo * 0x9e3779b1u + hi);
+    if (mode == 2 && (h & 2u)) return true;
+    return (h & 1u) ? me < other : me > other;
+}
+
 // Random initial lists: 64 distinct ids != v with distance 1e6 and the "new" flag (ref: initialize_graph,
 // src/index.cu:99-106, seeded there from clock(); here from `seed` so a build is repeatable).
 __global__ void knn_init_kernel(Knn k, uint32_t seed) {
@@ -104,6 +115,164 @@ __global__ void knn_init_kernel(Knn k, uint32_t seed) {
     }
     k.ids[i] = id | kNewFlag;
     k.dis[i] = kInfDis;
+}
+
+__device__ __forceinline__ void jtab_insert(uint2 *tab, uint32_t mask, uint32_t shift, uint32_t key, uint32_t valbits);
+
+// ---------------------------------------------------------------------------------------------------------
+// Term-seeded start.  The hybrid distance of two documents is dominated by the BM25 weights of the rare terms
+// they share, so before the first round every document meets the documents next to it in the posting lists of
+// its rarest BM25 terms: the (term, document) pairs of the corpus are radix-sorted into postings, each document
+// takes up to `take` followers from its rarest postings until it has 64 candidates, their distances are
+// evaluated directly and offered to both sides, and a merge turns the offers into the first sorted lists.
+// (The reference starts from random lists only, src/index.cu:99-106; random entries stay behind the seeds.)
+// ---------------------------------------------------------------------------------------------------------
+__global__ void inv_count_kernel(uint32_t n, const uint64_t *__restrict__ meta, uint32_t *__restrict__ cnt) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i <= n) cnt[i] = i < n ? meta_nb(meta[i]) : 0u;
+}
+__global__ void inv_keys_kernel(uint32_t n, const uint64_t *__restrict__ meta, const uint8_t *__restrict__ rec,
+                                const uint32_t *__restrict__ off, unsigned long long *__restrict__ keys) {
+    const uint32_t d = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (d >= n) return;
+    const uint64_t m = meta[d];
+    const uint2 *pr = reinterpret_cast<const uint2 *>(rec + meta_off16(m) * 16ull + kDenseBytes) + pad2(meta_ns(m));
+    unsigned long long *out = keys + off[d];
+    for (uint32_t j = lane; j < meta_nb(m); j += 32) out[j] = ((unsigned long long)pr[j].x << 32) | d;
+}
+__device__ __forceinline__ uint32_t lower_bound_u64(const unsigned long long *__restrict__ a, uint32_t lo, uint32_t hi, unsigned long long key) {
+    while (lo < hi) {
+        const uint32_t mid = lo + ((hi - lo) >> 1);
+        if (__ldg(a + mid) < key) lo = mid + 1; else hi = mid;
+    }
+    return lo;
+}
+constexpr int kSeedTermsPerLane = 4;   // the first 128 BM25 terms of a document are considered
+__global__ void seed_cand_kernel(uint32_t n, const uint64_t *__restrict__ meta, const uint8_t *__restrict__ rec,
+                                 const unsigned long long *__restrict__ keys, uint32_t total, uint32_t take,
+                                 uint32_t *__restrict__ cand) {
+    const uint32_t v = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (v >= n) return;
+    const uint64_t m = meta[v];
+    const uint32_t nb = meta_nb(m);
+    const uint2 *pr = reinterpret_cast<const uint2 *>(rec + meta_off16(m) * 16ull + kDenseBytes) + pad2(meta_ns(m));
+    uint32_t lo[kSeedTermsPerLane], df[kSeedTermsPerLane], term[kSeedTermsPerLane];
+#pragma unroll
+    for (int t = 0; t < kSeedTermsPerLane; ++t) {
+        const uint32_t j = lane + 32 * t;
+        lo[t] = 0; df[t] = kEmpty; term[t] = 0;
+        if (j < nb) {
+            term[t] = pr[j].x;
+            lo[t] = lower_bound_u64(keys, 0, total, (unsigned long long)term[t] << 32);
+            const uint32_t hi = lower_bound_u64(keys, lo[t], total, ((unsigned long long)term[t] + 1ull) << 32);
+            df[t] = hi - lo[t] >= 2 ? hi - lo[t] : kEmpty;   // a posting of one document (this one) seeds nothing
+        }
+    }
+    uint32_t cnt = 0;
+    while (cnt < (uint32_t)kK) {
+        unsigned long long best = ~0ull;   // (df, slot, lane), smallest first
+#pragma unroll
+        for (int t = 0; t < kSeedTermsPerLane; ++t) {
+            const unsigned long long c = ((unsigned long long)df[t] << 8) | ((unsigned long long)t << 5) | lane;
+            best = c < best ? c : best;
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const unsigned long long other = __shfl_xor_sync(kFull, best, o);
+            best = other < best ? other : best;
+        }
+        const uint32_t DF = (uint32_t)(best >> 8);
+        if (DF == kEmpty) break;
+        const uint32_t owner = (uint32_t)best & 31u, slot = ((uint32_t)best >> 5) & 3u;
+        uint32_t my_lo = lo[0], my_term = term[0];
+#pragma unroll
+        for (int t = 1; t < kSeedTermsPerLane; ++t) if (slot == (uint32_t)t) { my_lo = lo[t]; my_term = term[t]; }
+        const uint32_t L = __shfl_sync(kFull, my_lo, owner), T = __shfl_sync(kFull, my_term, owner);
+        if (lane == owner) {
+#pragma unroll
+            for (int t = 0; t < kSeedTermsPerLane; ++t) if (slot == (uint32_t)t) df[t] = kEmpty;
+        }
+        const uint32_t p = lower_bound_u64(keys, L, L + DF, ((unsigned long long)T << 32) | v) - L;
+        const uint32_t tk = min(min(DF - 1u, take), (uint32_t)kK - cnt);
+        if (lane < tk) cand[(size_t)v * kK + cnt + lane] = (uint32_t)__ldg(keys + L + (p + 1u + lane) % DF);
+        cnt += tk;
+    }
+    for (uint32_t j = cnt + lane; j < (uint32_t)kK; j += 32) cand[(size_t)v * kK + j] = kEmpty;
+}
+
+// Distances of every document to its seed candidates, one warp per document: the document's sparse and BM25
+// terms go into a per-warp hash table, its dense row into registers, each candidate's record is read once.
+constexpr int kSeedWarps = 4;
+__global__ void __launch_bounds__(kSeedWarps * 32) seed_dist_kernel(Knn k, const uint64_t *__restrict__ meta, const uint8_t *__restrict__ rec,
+                                                                   const uint32_t *__restrict__ cand, uint32_t tab_mask, uint32_t tab_shift, uint32_t own_mode) {
+    extern __shared__ __align__(16) uint8_t smem[];
+    const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint32_t v = blockIdx.x * kSeedWarps + warp;
+    if (v >= k.n) return;
+    uint2 *tab = reinterpret_cast<uint2 *>(smem) + (size_t)warp * (tab_mask + 1);
+    for (uint32_t i = lane; i <= tab_mask; i += 32) tab[i] = make_uint2(kEmpty, 0u);
+    __syncwarp();
+    const uint64_t m = meta[v];
+    const uint8_t *r = rec + meta_off16(m) * 16ull;
+    {
+        const uint2 *pr = reinterpret_cast<const uint2 *>(r + kDenseBytes);
+        const uint32_t ns = meta_ns(m), nb = meta_nb(m), pns = pad2(ns);
+        for (uint32_t j = lane; j < ns + nb; j += 32) {
+            const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
+            jtab_insert(tab, tab_mask, tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y);
+        }
+    }
+    uint4 a[4];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) a[q] = __ldg(reinterpret_cast<const uint4 *>(r) + lane + 32 * q);
+    __syncwarp();
+    unsigned long long evals = 0;
+    for (int j = 0; j < kK; ++j) {
+        const uint32_t c = cand[(size_t)v * kK + j];
+        if (c >= k.n || c == v) continue;
+        const uint64_t cm = meta[c];
+        const uint8_t *cr = rec + meta_off16(cm) * 16ull;
+        float acc = 0.0f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+            const uint4 b = __ldg(reinterpret_cast<const uint4 *>(cr) + lane + 32 * q);
+            const uint32_t aw[4] = {a[q].x, a[q].y, a[q].z, a[q].w}, bw[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+            for (int w = 0; w < 4; ++w) {
+                const float2 fa = __half22float2(*reinterpret_cast<const __half2 *>(&aw[w]));
+                const float2 fb = __half22float2(*reinterpret_cast<const __half2 *>(&bw[w]));
+                acc = fmaf(fa.x, fb.x, acc); acc = fmaf(fa.y, fb.y, acc);
+            }
+        }
+        const uint2 *pr = reinterpret_cast<const uint2 *>(cr + kDenseBytes);
+        const uint32_t ns = meta_ns(cm), nb = meta_nb(cm), pns = pad2(ns);
+        for (uint32_t q = lane; q < ns + nb; q += 32) {
+            const uint2 p = q < ns ? __ldg(pr + q) : __ldg(pr + pns + (q - ns));
+            const uint32_t key = q < ns ? p.x : (p.x | 0x80000000u);
+            uint32_t h = (key * 2654435761u) >> tab_shift;
+            for (uint32_t s = 0; s <= tab_mask; ++s) {
+                const uint2 e = tab[h];
+                if (e.x == kEmpty) break;
+                if (e.x == key) { acc = fmaf(__uint_as_float(e.y), __uint_as_float(p.y), acc); break; }
+                h = (h + 1) & tab_mask;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(kFull, acc, o);
+        if (lane == 0) {
+            const float d = 1.0f - acc;
+            if (pair_owned(own_mode, v, c)) {
+                const uint32_t t = atomicAdd(&k.propn[v], 1u);
+                if (t < kPropCap) k.prop[(size_t)v * kPropCap + t] = make_uint2(__float_as_uint(d), c);
+            }
+            if (pair_owned(own_mode, c, v)) {
+                const uint32_t t2 = atomicAdd(&k.propn[c], 1u);
+                if (t2 < kPropCap) k.prop[(size_t)c * kPropCap + t2] = make_uint2(__float_as_uint(d), v);
+            }
+        }
+        ++evals;
+    }
+    if (lane == 0 && evals) atomicAdd(k.stats + 0, evals);
 }
 
 // Sampling: the closest 16 unsampled ("new") entries and a random 16 of the sampled ("old") entries of every list,
@@ -242,6 +411,29 @@ __global__ void __launch_bounds__(256, 2) join_dense_simt_kernel(uint32_t node0,
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Two-choice (cuckoo) term tables in shared memory.  A row's (term id, value) pairs are stored so that every key
+// sits in one of its two hashed slots; a lookup is two loads and two compares with no branch, which matters
+// because a warp probes 100+ keys per step and a rarely taken chain walk would be taken by some lane every time.
+// An entry is one 64-bit word: id in the low half, value bits in the high half; empty = (0xFFFFFFFF, 0).
+// ---------------------------------------------------------------------------------------------------------
+constexpr unsigned long long kCkEmpty = 0x00000000FFFFFFFFull;
+__device__ __forceinline__ uint32_t ck_h1(uint32_t key, uint32_t shift) { return (key * 2654435761u) >> shift; }
+__device__ __forceinline__ uint32_t ck_h2(uint32_t key, uint32_t shift) { return ((key ^ 0x5bd1e995u) * 0x85ebca6bu + 0x1b873593u) >> shift; }
+// Lock-free insertion by eviction; false when the kick budget runs out (the caller then gives the row up).
+__device__ __forceinline__ bool ck_insert(unsigned long long *tab, uint32_t shift, uint32_t key, uint32_t valbits) {
+    unsigned long long item = ((unsigned long long)valbits << 32) | key;
+    uint32_t h = ck_h1(key, shift);
+    for (int kick = 0; kick < 48; ++kick) {
+        const unsigned long long old = atomicExch(tab + h, item);
+        if (old == kCkEmpty) return true;
+        item = old;
+        const uint32_t k = (uint32_t)old, a1 = ck_h1(k, shift), a2 = ck_h2(k, shift);
+        h = h == a1 ? a2 : a1;
+    }
+    return false;
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // Join, sparse + BM25 part, distance assembly, partner selection and proposals.  One CTA per node.
 // ---------------------------------------------------------------------------------------------------------
 struct JoinArgs {
@@ -257,6 +449,7 @@ struct JoinArgs {
     uint32_t arena_bytes;    // shared-memory budget for the sparse sections of all participants
     uint32_t tab_mask, tab_shift, groups;  // hash table of one new row's terms; rows hashed per round
     uint32_t prop_per;                     // partners proposed to each participant (<= kPropPerMax)
+    uint32_t own_mode;                     // see pair_owned
     uint32_t o_tab, o_dm, o_arena;
 };
 constexpr int kJoinThreads = 512;
@@ -276,7 +469,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     __shared__ uint64_t mbar;
     __shared__ uint32_t s_off[kPart + 1], s_id[kPart], s_ns[kPart], s_nb[kPart];
     __shared__ float s_kth[kPart];
-    __shared__ uint32_t s_rows, s_new;
+    __shared__ uint32_t s_rows, s_new, s_bad;
     uint2 *tab = reinterpret_cast<uint2 *>(smem + a.o_tab);
     float *dm = reinterpret_cast<float *>(smem + a.o_dm);  // [32][64] distances: new row i x participant j
     uint8_t *arena = smem + a.o_arena;
@@ -286,7 +479,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     const uint32_t v = a.node0 + local;
     uint32_t n_new = a.pcnt[(size_t)v * 2], rows = a.pcnt[(size_t)v * 2 + 1];
     if (rows <= 1) return;
-    if (tid == 0) { mbar_init(&mbar, 1); mbar_fence_init(); }
+    if (tid == 0) { mbar_init(&mbar, 1); mbar_fence_init(); s_bad = 0; }
     if (tid < kPart) {
         const uint32_t id = tid < (int)rows ? a.plist[(size_t)v * kPart + tid] : kEmpty;
         s_id[tid] = id;
@@ -334,61 +527,46 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
             const uint32_t i = i0 + g;
             const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[i]);
             const uint32_t ns = s_ns[i], nb = s_nb[i], pns = pad2(ns);
-            uint2 *t = tab + (size_t)g * (a.tab_mask + 1);
+            unsigned long long *t = reinterpret_cast<unsigned long long *>(tab + (size_t)g * (a.tab_mask + 1));
             for (uint32_t j = tid; j < ns + nb; j += kJoinThreads) {
                 const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
-                jtab_insert(t, a.tab_mask, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y);
+                if (!ck_insert(t, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y)) atomicOr(&s_bad, 1u << g);
             }
         }
         __syncthreads();
+        const uint32_t bad = s_bad;   // rows whose table could not be built sit this join out
         // One warp per participant j: its terms are read into registers once (6 per lane per 192-term chunk, slot
         // indices precomputed -- every table uses the same hash) and probed against each hashed row i < j of the
-        // group with all first probes in flight together; the rare collision chains are walked afterwards.
+        // group, two loads per term and table.
         for (uint32_t j = warp; j < rows; j += kJoinThreads / 32) {
             if (j <= i0) continue;
             const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[j]);
             const uint32_t ns = s_ns[j], nb = s_nb[j], pns = pad2(ns), nt = ns + nb;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
             for (uint32_t base = 0; base < nt; base += 192) {
-                uint32_t key[6], hs[6]; float val[6];
+                uint32_t key[6], h1[6], h2[6]; float val[6];
 #pragma unroll
                 for (int t = 0; t < 6; ++t) {
                     const uint32_t q = base + t * 32 + lane;
                     uint2 p = make_uint2(kEmpty, 0u);   // padding: matches only an empty slot, whose value is 0
                     if (q < nt) { p = q < ns ? pr[q] : pr[pns + (q - ns)]; if (q >= ns) p.x |= 0x80000000u; }
                     key[t] = p.x; val[t] = __uint_as_float(p.y);
-                    hs[t] = (p.x * 2654435761u) >> a.tab_shift;
+                    h1[t] = ck_h1(p.x, a.tab_shift); h2[t] = ck_h2(p.x, a.tab_shift);
                 }
 #pragma unroll
                 for (int g = 0; g < 4; ++g) {
                     if ((uint32_t)g < g_cnt) {
                         const uint2 *t2 = tab + (size_t)g * (a.tab_mask + 1);
-                        uint2 e[6];
 #pragma unroll
-                        for (int t = 0; t < 6; ++t) e[t] = t2[hs[t]];
-                        uint32_t chain = 0;   // terms whose first slot holds another key
+                        for (int half = 0; half < 2; ++half) {
+                            uint2 e1[3], e2[3];
 #pragma unroll
-                        for (int t = 0; t < 6; ++t) {
-                            acc[g] = fmaf(e[t].x == key[t] ? __uint_as_float(e[t].y) : 0.0f, val[t], acc[g]);
-                            chain |= (e[t].x != key[t] && e[t].x != kEmpty) ? (1u << t) : 0u;
-                        }
-                        if (__any_sync(kFull, chain != 0)) {
-                            // second slot for every term at once (no divergence), longer chains one by one
+                            for (int t = 0; t < 3; ++t) { e1[t] = t2[h1[3 * half + t]]; e2[t] = t2[h2[3 * half + t]]; }
 #pragma unroll
-                            for (int t = 0; t < 6; ++t) e[t] = t2[(hs[t] + 1) & a.tab_mask];
-#pragma unroll
-                            for (int t = 0; t < 6; ++t) {
-                                const bool live = (chain >> t) & 1u;
-                                acc[g] = fmaf((live && e[t].x == key[t]) ? __uint_as_float(e[t].y) : 0.0f, val[t], acc[g]);
-                                if (live && e[t].x != key[t] && e[t].x != kEmpty) {
-                                    uint32_t h = (hs[t] + 2) & a.tab_mask;
-                                    for (uint32_t s2 = 0; s2 < a.tab_mask; ++s2) {
-                                        const uint2 e2 = t2[h];
-                                        if (e2.x == kEmpty) break;
-                                        if (e2.x == key[t]) { acc[g] = fmaf(__uint_as_float(e2.y), val[t], acc[g]); break; }
-                                        h = (h + 1) & a.tab_mask;
-                                    }
-                                }
+                            for (int t = 0; t < 3; ++t) {
+                                const uint32_t kk = key[3 * half + t];
+                                const uint32_t vb = e1[t].x == kk ? e1[t].y : (e2[t].x == kk ? e2[t].y : 0u);
+                                acc[g] = fmaf(__uint_as_float(vb), val[3 * half + t], acc[g]);
                             }
                         }
                     }
@@ -407,11 +585,12 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
                 r += __shfl_xor_sync(kFull, r, 2);
                 r += __shfl_xor_sync(kFull, r, 1);
                 const uint32_t g = (lane >> 3) & 3u, i = i0 + g;
-                if ((lane & 7) == 0 && g < g_cnt && i < j) { dm[i * kPart + j] = 1.0f - D[(size_t)j * kNewMax + i] - r; ++evals; }
+                if ((lane & 7) == 0 && g < g_cnt && i < j) { dm[i * kPart + j] = ((bad >> g) & 1u) ? kInfDis : 1.0f - D[(size_t)j * kNewMax + i] - r; ++evals; }
             }
         }
         __syncthreads();
         for (uint32_t q = tid; q < (a.tab_mask + 1) * g_cnt; q += kJoinThreads) tab[q] = make_uint2(kEmpty, 0u);
+        if (tid == 0) s_bad = 0;
         __syncthreads();
     }
 
@@ -424,7 +603,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
         for (int q = 0; q < kPropPerMax; ++q) { bd[q] = s_kth[p]; bi[q] = kEmpty; }
         const uint32_t lim = p < n_new ? rows : n_new;
         for (uint32_t j = 0; j < lim; ++j) {
-            if (j == p) continue;
+            if (j == p || !pair_owned(a.own_mode, s_id[p], s_id[j])) continue;
             const uint32_t lo = min(p, j), hi = max(p, j);
             const float d = dm[lo * kPart + hi];
             if (d < bd[kPropPer - 1]) {
@@ -562,6 +741,7 @@ struct PruneArgs {
     uint32_t own_mask, own_shift;   // the node's own BM25 term set
     uint32_t o_tab, o_own, o_lists;
     int unfused;
+    const uint32_t *node_list;      // when set, block i prunes node node_list[i]
 };
 
 // the reference's shared-memory bitonic network on (key, value) pairs, run by the whole CTA
@@ -602,7 +782,7 @@ __global__ void __launch_bounds__(kPruneThreads, 2) prune_kernel(const PruneArgs
     uint32_t *own = reinterpret_cast<uint32_t *>(smem + a.o_own);
     uint32_t *lists = reinterpret_cast<uint32_t *>(smem + a.o_lists);   // 64 x 64 neighbour ids
     float *ldis = reinterpret_cast<float *>(lists + kK * kK);          // 64 x 64 neighbour distances
-    const uint32_t bid = blockIdx.x;
+    const uint32_t bid = a.node_list ? a.node_list[blockIdx.x] : blockIdx.x;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     if (bid >= a.n) return;
     const uint32_t *g = a.knn + (size_t)bid * kK;
@@ -792,6 +972,321 @@ __global__ void __launch_bounds__(kPruneThreads, 2) prune_kernel(const PruneArgs
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Pruning, all-pairs form.  The step-wise kernel above walks the 63 selection steps one after the other and
+// evaluates the inner products of a step only when the step is reached, so most of its time is load latency on
+// a chain of dependent steps.  Every inner product a step can ask for is known in advance, though: step b
+// compares candidate b (hashed / held in registers) with an earlier candidate a < b (streamed), in that
+// orientation.  This kernel therefore evaluates all 2016 ordered pairs of a node's 64 neighbours first, with the
+// rows staged in shared memory and the reference's lane / chunk association and rounding kept per pair, and
+// then replays the selection steps on the finished 64 x 64 tables with one warp.  Nodes whose neighbours'
+// sparse sections do not fit the staging area are listed for the step-wise kernel.
+// ---------------------------------------------------------------------------------------------------------
+constexpr int kP2Threads = 512;
+constexpr int kP2Warps = kP2Threads / 32;
+constexpr int kP2Groups = 4;   // candidate rows hashed per pass
+
+struct Prune2Args {
+    PruneArgs p;
+    uint32_t groups;                       // <= kP2Groups
+    uint32_t o_ip, o_kw, o_region, region_bytes;
+    uint32_t *ovf_list, *ovf_cnt, *err;
+};
+
+// One section (sparse or BM25) of streamed row `row` against the hashed candidate rows of a group: every lane walks
+// its terms j = lane, lane + 32, ... in ascending order, NS terms per pass, and adds value x matched value (zero
+// when the candidate lacks the term, which leaves the running sum as it is) -- the reference's per-lane order.
+template <int NS, bool BM>
+__device__ __forceinline__ void p2_section(const uint2 *__restrict__ row, uint32_t cnt, const uint2 *__restrict__ tab, uint32_t tabn,
+                                           uint32_t shift, uint32_t g_lo, uint32_t g_cnt, int lane, float (&part)[kP2Groups],
+                                           uint32_t &kwm) {
+    for (uint32_t j0 = 0; j0 < cnt; j0 += 32 * NS) {
+        uint32_t key[NS], h1[NS], h2[NS], ownbit = 0;
+        float val[NS];
+#pragma unroll
+        for (int t = 0; t < NS; ++t) {
+            const uint32_t j = j0 + 32 * t + lane;
+            uint2 pv = make_uint2(kEmpty, 0u);   // padding meets an empty slot or nothing: a zero product either way
+            if (j < cnt) {
+                pv = row[j];
+                if (BM) { ownbit |= (pv.x >> 31) << t; pv.x |= 0x80000000u; }
+            }
+            key[t] = pv.x; val[t] = __uint_as_float(pv.y);
+            h1[t] = ck_h1(pv.x, shift); h2[t] = ck_h2(pv.x, shift);
+        }
+#pragma unroll
+        for (int gi = 0; gi < kP2Groups; ++gi) {
+            if ((uint32_t)gi < g_cnt && (uint32_t)gi >= g_lo) {
+                const uint2 *t2 = tab + (size_t)gi * tabn;
+                uint2 e1[NS], e2[NS];
+#pragma unroll
+                for (int t = 0; t < NS; ++t) { e1[t] = t2[h1[t]]; e2[t] = t2[h2[t]]; }
+                uint32_t fnd = 0;
+                float p = part[gi];
+#pragma unroll
+                for (int t = 0; t < NS; ++t) {
+                    const bool hit1 = e1[t].x == key[t], hit2 = e2[t].x == key[t];
+                    const uint32_t vb = hit1 ? e1[t].y : (hit2 ? e2[t].y : 0u);
+                    p = __fmaf_rn(__uint_as_float(vb), val[t], p);
+                    fnd |= (hit1 || hit2) ? (1u << t) : 0u;
+                }
+                part[gi] = p;
+                if (BM && (ownbit & ~fnd)) kwm |= 1u << gi;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2Args q) {
+    const PruneArgs &a = q.p;
+    extern __shared__ __align__(128) uint8_t smem[];
+    __shared__ uint64_t mbar;
+    __shared__ uint32_t nei0[kK], nei1[kK], nei2[kK + 1], det[kK], s_off[kK + 1], sel_pos[kK];
+    __shared__ uint64_t meta0[kK];
+    __shared__ float pow0[kK];
+    __shared__ uint32_t s_task, s_fit;
+    float *IP = reinterpret_cast<float *>(smem + q.o_ip);      // [b][a], a < b
+    uint8_t *KW = smem + q.o_kw;                               // [b][a] keyword flag of the pair
+    uint2 *tab = reinterpret_cast<uint2 *>(smem + a.o_tab);
+    uint32_t *own = reinterpret_cast<uint32_t *>(smem + a.o_own);
+    uint8_t *region = smem + q.o_region;
+    uint32_t *lists = reinterpret_cast<uint32_t *>(region);
+    float *ldis = reinterpret_cast<float *>(lists + kK * kK);
+    const uint32_t bid = blockIdx.x;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (bid >= a.n) return;
+    const uint32_t *g = a.knn + (size_t)bid * kK;
+
+    if (tid == 0) { mbar_init(&mbar, 1); mbar_fence_init(); s_task = 0; nei2[kK] = 0; }
+    if (tid < kK) { nei0[tid] = g[tid]; det[tid] = 0; nei2[tid] = 0; }
+    for (uint32_t i = tid; i <= a.own_mask; i += kP2Threads) own[i] = kEmpty;
+    for (uint32_t i = tid; i < kK * kK; i += kP2Threads) KW[i] = 0;
+    __syncthreads();
+    {   // the node's own BM25 terms (ref :559-565)
+        const uint64_t m = a.meta[bid];
+        const uint2 *pr = reinterpret_cast<const uint2 *>(a.rec + meta_off16(m) * 16ull + kDenseBytes) + pad2(meta_ns(m));
+        for (uint32_t j = tid; j < meta_nb(m); j += kP2Threads) {
+            const uint32_t key = pr[j].x;
+            uint32_t h = (key * 2654435761u) >> a.own_shift;
+            for (uint32_t s = 0; s <= a.own_mask; ++s) {
+                const uint32_t old = atomicCAS(&own[h], kEmpty, key);
+                if (old == kEmpty || old == key) break;
+                h = (h + 1) & a.own_mask;
+            }
+        }
+    }
+    // detour counts (ref :572-597) and the detour order
+    for (uint32_t idx = tid; idx < kK * kK; idx += kP2Threads) {
+        const uint32_t p = idx >> 6, j = idx & 63;
+        lists[idx] = a.knn[(size_t)nei0[p] * kK + j];
+        ldis[idx] = a.knn_dis[(size_t)nei0[p] * kK + j];
+    }
+    __syncthreads();
+    for (uint32_t pair = tid; pair < kK * kK; pair += kP2Threads) {
+        const uint32_t p = pair >> 6, t = pair & 63;
+        if (t <= p) continue;
+        const uint32_t key = nei0[t];
+        int r = -1;
+        for (int j = 0; j < kK; ++j) if (lists[p * kK + j] == key) { r = j; break; }
+        if (r >= 0 && ldis[p * kK + r] < a.knn_dis[(size_t)bid * kK + t]) atomicAdd(&det[t], 1u);
+    }
+    __syncthreads();
+    block_bitonic_kv(det, nei0, kK, tid, kP2Threads);
+    if (tid < kK) { meta0[tid] = a.meta[nei0[tid]]; pow0[tid] = a.power[nei0[tid]]; }
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t o = 0;
+        for (int r = 0; r < kK; ++r) { s_off[r] = o; o += 8u * (pad2(meta_ns(meta0[r])) + pad2(meta_nb(meta0[r]))); }
+        s_off[kK] = o;
+        s_fit = o <= q.region_bytes;
+        if (!s_fit) q.ovf_list[atomicAdd(q.ovf_cnt, 1u)] = bid;
+    }
+    __syncthreads();
+    if (!s_fit) return;
+
+    // ---- dense inner products: rows a of one half staged, candidate rows b in registers ----------------------
+    uint32_t parity = 0;
+    for (int ch = 0; ch < 2; ++ch) {
+        if (tid == 0) { s_task = 0; mbar_arrive_expect_tx(&mbar, 32u * kDenseBytes); }
+        fence_proxy_async();   // the region was last touched by ordinary loads / stores
+        __syncthreads();
+        if (tid < 32) bulk_g2s(region + (size_t)tid * kDenseBytes, a.rec + meta_off16(meta0[32 * ch + tid]) * 16ull, kDenseBytes, &mbar);
+        mbar_wait_bounded(&mbar, parity, q.err, 5u);
+        parity ^= 1u;
+        const uint2 *srow = reinterpret_cast<const uint2 *>(region);
+        const uint32_t ntasks = ch == 0 ? 63u : 31u;
+        for (;;) {
+            uint32_t t = 0;
+            if (lane == 0) t = atomicAdd(&s_task, 1u);
+            t = __shfl_sync(kFull, t, 0);
+            if (t >= ntasks) break;
+            const uint32_t b = 63u - t;
+            const uint32_t n_a = min(32u, b - 32u * ch);    // rows a = 32 ch .. 32 ch + n_a - 1 are earlier than b
+            uint32_t creg[16];
+            {
+                const uint2 *d = reinterpret_cast<const uint2 *>(a.rec + meta_off16(meta0[b]) * 16ull);
+#pragma unroll
+                for (int k = 0; k < 8; ++k) { const uint2 x = __ldg(d + lane + 32 * k); creg[2 * k] = x.x; creg[2 * k + 1] = x.y; }
+            }
+            uint32_t acc[32];
+#pragma unroll
+            for (int al = 0; al < 32; ++al) {
+                uint32_t s = 0;
+                if ((uint32_t)al < n_a) {
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) {
+                        const uint2 x = srow[al * 256 + lane + 32 * k];
+                        s = hfma2_rn(creg[2 * k], x.x, s); s = hfma2_rn(creg[2 * k + 1], x.y, s);
+                    }
+                }
+                acc[al] = s;
+            }
+            // 32 tree sums at once; the pairing (l, l ^ 16), (l, l ^ 8), ... is the reference's shuffle-down tree as seen
+            // from lane 0, and half addition commutes, so lane l ends with exactly the sum lane 0 would hold for row l
+#pragma unroll
+            for (int o = 16, len = 32; o >= 1; o >>= 1, len >>= 1) {
+#pragma unroll
+                for (int w = 0; w < len / 2; ++w) {
+                    const bool up = (lane & o) != 0;
+                    const uint32_t keep = up ? acc[w + len / 2] : acc[w];
+                    const uint32_t send = up ? acc[w] : acc[w + len / 2];
+                    acc[w] = hadd2_rn(keep, __shfl_xor_sync(kFull, send, o));
+                }
+            }
+            if ((uint32_t)lane < n_a) IP[b * kK + 32 * ch + lane] = half_sum_to_float(acc[0]);
+        }
+        __syncthreads();
+    }
+
+    // ---- sparse and BM25 sections of all 64 rows into the region ------------------------------------------
+    if (tid == 0) mbar_arrive_expect_tx(&mbar, s_off[kK]);
+    fence_proxy_async();
+    __syncthreads();
+    if (tid < kK) {
+        const uint32_t sz = s_off[tid + 1] - s_off[tid];
+        if (sz) bulk_g2s(region + s_off[tid], a.rec + meta_off16(meta0[tid]) * 16ull + kDenseBytes, sz, &mbar);
+    }
+    for (uint32_t i = tid; i < (a.tab_mask + 1) * q.groups; i += kP2Threads) tab[i] = make_uint2(kEmpty, 0u);
+    if (s_off[kK]) mbar_wait_bounded(&mbar, parity, q.err, 6u);
+    __syncthreads();
+    // bit 31 of a staged BM25 id: the node itself owns the term (ref :144-149 asks this per pair)
+    for (int r = warp; r < kK; r += kP2Warps) {
+        uint2 *pr = reinterpret_cast<uint2 *>(region + s_off[r]) + pad2(meta_ns(meta0[r]));
+        for (uint32_t j = lane; j < meta_nb(meta0[r]); j += 32)
+            if (set_contains(own, a.own_mask, a.own_shift, pr[j].x)) pr[j].x |= 0x80000000u;
+    }
+    __syncthreads();
+
+    for (uint32_t b0 = 0; b0 < (uint32_t)kK; b0 += q.groups) {
+        const uint32_t g_cnt = min(q.groups, (uint32_t)kK - b0);
+        for (uint32_t gi = 0; gi < g_cnt; ++gi) {
+            const uint32_t b = b0 + gi;
+            if (b == 0) continue;
+            const uint2 *pr = reinterpret_cast<const uint2 *>(region + s_off[b]);
+            const uint32_t ns = meta_ns(meta0[b]), nb = meta_nb(meta0[b]), pns = pad2(ns);
+            unsigned long long *t = reinterpret_cast<unsigned long long *>(tab + (size_t)gi * (a.tab_mask + 1));
+            for (uint32_t j = tid; j < ns + nb; j += kP2Threads) {
+                const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
+                if (!ck_insert(t, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y)) s_fit = 0;
+            }
+        }
+        __syncthreads();
+        if (!s_fit) {   // a table could not be built: the step-wise kernel takes the node
+            if (tid == 0) q.ovf_list[atomicAdd(q.ovf_cnt, 1u)] = bid;
+            return;
+        }
+        const uint32_t a_end = min(b0 + g_cnt - 1u, (uint32_t)kK - 1u);   // rows a < the group's last candidate
+        for (uint32_t ar = warp; ar < a_end; ar += kP2Warps) {
+            const uint2 *pr = reinterpret_cast<const uint2 *>(region + s_off[ar]);
+            const uint32_t ns = meta_ns(meta0[ar]), nb = meta_nb(meta0[ar]), pns = pad2(ns);
+            float sp[kP2Groups] = {0.f, 0.f, 0.f, 0.f}, bm[kP2Groups] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t kwm = 0;   // bit g: a BM25 term of row a that the node owns and candidate g lacks
+            const uint32_t g_lo = ar >= b0 ? ar - b0 + 1u : 0u;   // candidates b0 + g must come after row a
+            p2_section<4, false>(pr, ns, tab, a.tab_mask + 1, a.tab_shift, g_lo, g_cnt, lane, sp, kwm);
+            p2_section<2, true>(pr + pns, nb, tab, a.tab_mask + 1, a.tab_shift, g_lo, g_cnt, lane, bm, kwm);
+            float tot[kP2Groups];
+#pragma unroll
+            for (int gi = 0; gi < kP2Groups; ++gi) tot[gi] = __fadd_rn(sp[gi], bm[gi]);
+            // four tree sums in 2 + 1 + 3 shuffles, same pairing order (16, 8, 4, 2, 1) as the reference's tree
+            const bool up4 = (lane & 16) != 0;
+            const float k0 = up4 ? tot[2] : tot[0], k1 = up4 ? tot[3] : tot[1];
+            const float s0 = up4 ? tot[0] : tot[2], s1 = up4 ? tot[1] : tot[3];
+            const float a0 = __fadd_rn(k0, __shfl_xor_sync(kFull, s0, 16)), a1 = __fadd_rn(k1, __shfl_xor_sync(kFull, s1, 16));
+            const bool up3 = (lane & 8) != 0;
+            float r = __fadd_rn(up3 ? a1 : a0, __shfl_xor_sync(kFull, up3 ? a0 : a1, 8));
+            r = __fadd_rn(r, __shfl_xor_sync(kFull, r, 4));
+            r = __fadd_rn(r, __shfl_xor_sync(kFull, r, 2));
+            r = __fadd_rn(r, __shfl_xor_sync(kFull, r, 1));
+            uint32_t kw_any = 0;
+#pragma unroll
+            for (int gi = 0; gi < kP2Groups; ++gi) kw_any |= __any_sync(kFull, (kwm >> gi) & 1u) ? (1u << gi) : 0u;
+            const uint32_t gi = (lane >> 3) & 3u, b = b0 + gi;
+            if ((lane & 7) == 0 && gi < g_cnt && b > ar) {
+                IP[b * kK + ar] = __fadd_rn(IP[b * kK + ar], r);
+                KW[b * kK + ar] = (kw_any >> gi) & 1u;
+            }
+        }
+        __syncthreads();
+        for (uint32_t i = tid; i < (a.tab_mask + 1) * g_cnt; i += kP2Threads) tab[i] = make_uint2(kEmpty, 0u);
+        __syncthreads();
+    }
+
+    // ---- the selection steps (ref :613-676) replayed on the tables by one warp -----------------------------
+    if (warp == 0) {
+        uint32_t ipn = 1;
+        if (lane == 0) { nei1[0] = nei0[0]; sel_pos[0] = 0; }
+        __syncwarp();
+        for (uint32_t b = 1; b < (uint32_t)kK && ipn < (uint32_t)kK; ++b) {
+            const float cpow = pow0[b];
+            bool rej = false, open = false, tomb[2] = {false, false};
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const uint32_t i = lane + 32 * h;
+                if (i < ipn && nei1[i] != kEmpty) {
+                    const uint32_t pos = sel_pos[i];
+                    const float ip = IP[b * kK + pos];
+                    if (cpow < ip) rej = true;
+                    if (pow0[pos] < ip) tomb[h] = true;
+                }
+            }
+            if (lane < 16) {
+                // slot i runs on warp i % 16 of the reference and that warp's flag stays set for the rest of the step
+                uint32_t vf = 0;
+                for (uint32_t i = lane; i < ipn; i += 16)
+                    if (nei1[i] != kEmpty) {
+                        if (KW[b * kK + sel_pos[i]]) vf = 1;
+                        if (vf != 1) open = true;
+                    }
+            }
+            __syncwarp();
+#pragma unroll
+            for (int h = 0; h < 2; ++h) if (tomb[h]) nei1[lane + 32 * h] = kEmpty;
+            const bool rej_any = __any_sync(kFull, rej), open_any = __any_sync(kFull, open);
+            uint32_t n2 = ipn;
+            if (!rej_any) { if (lane == 0) { nei1[n2] = nei0[b]; sel_pos[n2] = b; } ++n2; }
+            if (!open_any && lane == 0) nei2[n2] = 1;   // written after the increment, as in the reference
+            ipn = n2;
+            __syncwarp();
+        }
+        if (lane == 0) {
+            uint32_t count = 0, i_neis;
+            for (i_neis = 0; i_neis < ipn && count < AP_DEGREE; ++i_neis)
+                if (nei1[i_neis] != kEmpty) nei0[count++] = nei1[i_neis];
+            uint32_t *ke = a.kw_edge + (size_t)bid * 33;
+            uint32_t kc = 0;
+            for (uint32_t i = i_neis; i < ipn; ++i)
+                if (nei2[i] == 1 && nei1[i] != kEmpty && kc < 32) { ke[kc + 1] = nei1[i]; ++kc; }
+            ke[0] = kc;
+            for (uint32_t i = kc + 1; i < 33; ++i) ke[i] = 0;
+        }
+    }
+    __syncthreads();
+    if (tid < AP_DEGREE) {
+        a.new_list[(size_t)bid * AP_DEGREE + tid] = nei0[tid];
+        a.detour[(size_t)bid * AP_DEGREE + tid] = det[tid];
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // Reverse edges and final rows: ref src/index.cu:699-711 (scatter) and :717-807 (allan_poe_final_graph).
 // The reference scatters with atomics from racing blocks; here every edge gets the key
 // (target, source, slot), the keys are radix-sorted, and each target replays its edges in ascending
@@ -929,15 +1424,52 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
     if (!kw) AP_TRY(db.alloc(&kw, (size_t)n * 33));
     PruneArgs a{};
     a.n = n; a.knn = d_knn; a.knn_dis = d_knn_dis; a.power = d_power; a.meta = ix->meta; a.rec = ix->rec_build;
-    a.new_list = nl; a.detour = detour; a.kw_edge = kw; a.unfused = 0;
+    a.new_list = nl; a.detour = detour; a.kw_edge = kw; a.unfused = 0; a.node_list = nullptr;
     const uint32_t tabn = pow2_at_least(2 * (ix->max_ns + ix->max_nb), 64), ownn = pow2_at_least(2 * ix->max_nb, 64);
     a.tab_mask = tabn - 1; a.tab_shift = 32 - log2u(tabn); a.own_mask = ownn - 1; a.own_shift = 32 - log2u(ownn);
     a.o_tab = 0; a.o_own = 8 * tabn; a.o_lists = a.o_own + 4 * ownn;
     const size_t smem = a.o_lists + (size_t)kK * kK * 8;
     if (smem > ix->smem_per_block) return fail(AP_ERR_LIMIT, "pruning needs %zu bytes of shared memory per block", smem);
     AP_CUDA(cudaFuncSetAttribute(prune_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    prune_kernel<<<n, kPruneThreads, smem>>>(a);
-    AP_CUDA(cudaGetLastError());
+
+    // all-pairs kernel first; the step-wise kernel takes the nodes it lists (or all of them when the tables alone
+    // leave no room for a staging area, or when APOE_PRUNE_KERNEL=stepwise asks for it)
+    Prune2Args q{};
+    q.p = a;
+    q.o_ip = 0; q.o_kw = kK * kK * 4; q.p.o_own = q.o_kw + kK * kK;
+    q.p.o_tab = (q.p.o_own + 4 * ownn + 15) / 16 * 16;
+    const size_t fixed = 4096;   // static shared memory of the kernel, rounded up
+    const size_t avail = ix->smem_per_block > fixed ? ix->smem_per_block - fixed : 0;
+    uint32_t groups = kP2Groups;
+    while (groups > 1 && q.p.o_tab + (size_t)groups * tabn * 8 + 96 * 1024 > avail) --groups;
+    q.groups = groups;
+    q.o_region = (uint32_t)((q.p.o_tab + (size_t)groups * tabn * 8 + 127) / 128 * 128);
+    const char *force = getenv("APOE_PRUNE_KERNEL");
+    const bool pairs_ok = avail >= (size_t)q.o_region + 64 * 1024 && !(force && !strcmp(force, "stepwise"));
+    uint32_t n_step = n;
+    uint32_t *ovf_list = nullptr, *ovf_cnt = nullptr;
+    if (pairs_ok) {
+        q.region_bytes = (uint32_t)((avail - q.o_region) / 128 * 128);
+        AP_TRY(db.alloc(&ovf_list, n)); AP_TRY(db.alloc(&ovf_cnt, 1));
+        AP_CUDA(cudaMemsetAsync(ovf_cnt, 0, 4));
+        q.ovf_list = ovf_list; q.ovf_cnt = ovf_cnt; q.err = ix->d_ctl + 1;
+        const size_t smem2 = (size_t)q.o_region + q.region_bytes;
+        AP_CUDA(cudaFuncSetAttribute(prune_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+        prune_pairs_kernel<<<n, kP2Threads, smem2>>>(q);
+        AP_CUDA(cudaGetLastError());
+        AP_CUDA(cudaMemcpy(&n_step, ovf_cnt, 4, cudaMemcpyDeviceToHost));
+        a.node_list = ovf_list;
+        if (launches) ++*launches;
+    }
+    if (n_step) {
+        prune_kernel<<<n_step, kPruneThreads, smem>>>(a);
+        AP_CUDA(cudaGetLastError());
+    }
+    {
+        uint32_t ew = 0;
+        AP_CUDA(cudaMemcpy(&ew, ix->d_ctl + 1, 4, cudaMemcpyDeviceToHost));
+        if (ew) { cudaMemset(ix->d_ctl + 1, 0, 4); return fail(AP_ERR_DEVICE, "a pruning kernel raised error word %u (a bounded wait ran out)", ew); }
+    }
 
     const size_t total = (size_t)n * AP_DEGREE;
     unsigned long long *keys, *keys_s; uint32_t *vals, *vals_s, *indeg, *start;
@@ -966,6 +1498,42 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
 int join_dense_tc_launch(ap_index *ix, uint32_t node0, uint32_t nodes, const uint32_t *plist, const uint32_t *pcnt, float *D,
                          cudaStream_t stream);  // apoe_join_tc.cu
 
+// Term-seeded first lists (see seed_cand_kernel).  Skipped when the corpus has no BM25 terms or more than 2^31 - 1.
+static int seed_run(ap_index *ix, const Knn &k, uint32_t take, uint32_t own_mode, uint32_t *launches) {
+    const uint32_t n = ix->n;
+    DevBuf db;
+    uint32_t *cnt, *off, *cand;
+    AP_TRY(db.alloc(&cnt, (size_t)n + 1)); AP_TRY(db.alloc(&off, (size_t)n + 1));
+    inv_count_kernel<<<n / 256 + 1, 256>>>(n, ix->meta, cnt);
+    size_t tmp_bytes = 0;
+    AP_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, cnt, off, (int)(n + 1)));
+    uint8_t *tmp; AP_TRY(db.alloc(&tmp, tmp_bytes));
+    AP_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, cnt, off, (int)(n + 1)));
+    // the 32-bit running sum wraps on huge corpora; the per-document counts are <= 16383, so the check below on
+    // the host-side total of max_nb * n is exact enough to rule that out
+    if ((unsigned long long)ix->max_nb * n >= (1ull << 31)) return AP_OK;
+    uint32_t total = 0;
+    AP_CUDA(cudaMemcpy(&total, off + n, 4, cudaMemcpyDeviceToHost));
+    if (total == 0) return AP_OK;
+    unsigned long long *keys, *keys_s;
+    AP_TRY(db.alloc(&keys, total));
+    inv_keys_kernel<<<(n + 7) / 8, 256>>>(n, ix->meta, ix->rec_build, off, keys);
+    AP_TRY(sort_u64_pairs(db, keys, nullptr, total, 64, &keys_s, nullptr));
+    AP_TRY(db.alloc(&cand, (size_t)n * kK));
+    seed_cand_kernel<<<(n + 7) / 8, 256>>>(n, ix->meta, ix->rec_build, keys_s, total, take, cand);
+    const uint32_t tabn = pow2_at_least(2 * (ix->max_ns + ix->max_nb), 64);
+    const size_t smem = (size_t)kSeedWarps * tabn * 8;
+    if (smem > ix->smem_per_block) return AP_OK;   // rows too long for per-warp tables: random start only
+    AP_CUDA(cudaFuncSetAttribute(seed_dist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
+    seed_dist_kernel<<<(n + kSeedWarps - 1) / kSeedWarps, kSeedWarps * 32, smem>>>(k, ix->meta, ix->rec_build, cand, tabn - 1, 32 - log2u(tabn), own_mode);
+    knn_merge_kernel<<<(n + 3) / 4, 128>>>(k);
+    AP_CUDA(cudaGetLastError());
+    AP_CUDA(cudaDeviceSynchronize());
+    *launches += 7;
+    return AP_OK;
+}
+
 int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats) {
     ap_build_opts o{};
     if (opts_in) o = *opts_in;
@@ -990,6 +1558,8 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     uint32_t launches = 0;
     AP_TRY(norms_run(ix, power)); ++launches;
     knn_init_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k, o.seed ? o.seed : 20261125u); ++launches;
+    const uint32_t own_mode = (o.reserved[1] & 8u) ? 1u : ((o.reserved[1] & 16u) ? 2u : 0u);
+    if (!(o.reserved[1] & 2u)) AP_TRY(seed_run(ix, k, o.reserved[2] ? std::min<uint32_t>(o.reserved[2], 32u) : 8u, own_mode, &launches));   // term-seeded start unless switched off
 
     // scratch for the dense tiles, in batches of nodes
     const uint32_t batch = std::min<uint32_t>(n, 1u << 18);
@@ -1001,6 +1571,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     ja.plist = k.plist; ja.pcnt = k.pcnt; ja.meta = ix->meta; ja.rec = ix->rec_build; ja.D = D; ja.knn_dis = k.dis;
     ja.prop = k.prop; ja.propn = k.propn; ja.stats = k.stats; ja.err = err;
     ja.prop_per = std::min<uint32_t>(kPropPerMax, o.reserved[0] ? o.reserved[0] : 4);
+    ja.own_mode = own_mode;
     const uint32_t tabn = pow2_at_least(2 * (ix->max_ns + ix->max_nb), 64);
     ja.tab_mask = tabn - 1; ja.tab_shift = 32 - log2u(tabn);
     // two CTAs per SM: tables for up to 4 hashed rows, the 32 x 64 distance tile, the rest is arena
@@ -1021,7 +1592,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     float phase_ms[4] = {0, 0, 0, 0};  // sample + lists, dense tiles, sparse + proposals, merge
     uint32_t it = 0;
     unsigned long long prev_updates = 0;
-    for (; it < iters; ++it) {
+    for (; it < iters && !(o.reserved[1] & 4u); ++it) {
         AP_CUDA(cudaMemsetAsync(k.scnt, 0, (size_t)n * 16));
         AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
         AP_CUDA(cudaEventRecord(ev[0]));
@@ -1049,7 +1620,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
         prev_updates = st[1];
         if (it >= 3 && upd < (unsigned long long)n * kK / 1000) { ++it; break; }  // < 0.1 % of the entries changed
     }
-    if (!(o.reserved[1] & 1u)) {   // reverse pass unless switched off
+    if (!(o.reserved[1] & 1u) && own_mode == 0) {   // reverse pass unless switched off
         AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
         knn_reverse_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k);
         knn_merge_kernel<<<(n + 3) / 4, 128>>>(k);

@@ -195,6 +195,9 @@ __device__ __forceinline__ void bulk_g2s(void *dst_smem, const void *src_gmem, u
                  : "memory");
 }
 
+// Orders earlier ordinary (generic-proxy) accesses of shared memory before later bulk async copies into it.
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 // half2 arithmetic on packed bit patterns with the rounding spelled out, so the compiler can neither fuse nor split.
 __device__ __forceinline__ uint32_t hfma2_rn(uint32_t a, uint32_t b, uint32_t c) {
     uint32_t d;

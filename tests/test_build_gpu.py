@@ -23,7 +23,14 @@ def test_norms_match_oracle_bitwise(tiny, bix):
     assert np.array_equal(got.view(np.uint32), tiny.power.view(np.uint32))
 
 
-def test_prune_and_rows_match_oracle_bitwise(tiny, bix):
+@pytest.fixture(params=["pairs", "stepwise"])
+def prune_kernel(request, monkeypatch):
+    """Both pruning kernels: the all-pairs one (default) and the step-wise one it falls back to."""
+    monkeypatch.setenv("APOE_PRUNE_KERNEL", request.param)
+    return request.param
+
+
+def test_prune_and_rows_match_oracle_bitwise(tiny, bix, prune_kernel):
     """Same pre-pruning k-NN lists in -> same forward lists, keyword-edge lists and 40-wide rows out."""
     new_list, kw, rows = bix.prune(tiny.knn, tiny.knn_dis, tiny.power)
     assert np.array_equal(new_list, tiny.new_list)
@@ -33,7 +40,7 @@ def test_prune_and_rows_match_oracle_bitwise(tiny, bix):
     assert np.array_equal(g, tiny.graph) and np.array_equal(ep, tiny.ep)
 
 
-def test_prune_on_perturbed_lists(tiny, bix):
+def test_prune_on_perturbed_lists(tiny, bix, prune_kernel):
     """Lists with repeated ids and ties (what NN-Descent can leave behind) still match the oracle."""
     rng = np.random.default_rng(1)
     knn = tiny.knn.copy()
@@ -44,6 +51,33 @@ def test_prune_on_perturbed_lists(tiny, bix):
     want = orc.prune(tiny.D7h, tiny.S, tiny.B, knn, dis, tiny.power)
     got = bix.prune(knn, dis, tiny.power)
     assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1]) and np.array_equal(got[2], want[2])
+
+
+def test_prune_kernels_agree_with_long_rows():
+    """A few documents with thousands of terms: nodes next to them overflow the all-pairs staging area and take the
+    step-wise kernel; the result still equals the oracle's."""
+    ds = helpers.make_dataset(1500, 4, seed=33, with_graph=False)
+    rng = np.random.default_rng(2)
+    S, B = ds.S, ds.B
+    # rebuild the BM25 rows so that 6 documents carry 900 terms each
+    off, idx, val = [0], [], []
+    heavy = set(rng.choice(ds.n, 6, replace=False).tolist())
+    for i in range(ds.n):
+        a, b = int(B.off[i]), int(B.off[i + 1])
+        if i in heavy:
+            ids = np.sort(rng.choice(synth.BM25_VOCAB, 900, replace=False)).astype(np.uint32)
+            idx.append(ids); val.append(rng.random(900, dtype=np.float32) + 0.5)
+        else:
+            idx.append(B.idx[a:b]); val.append(B.val[a:b])
+        off.append(off[-1] + len(idx[-1]))
+    B2 = orc.CsrNp(np.asarray(off, dtype=np.uint32), np.concatenate(idx).astype(np.uint32), np.concatenate(val).astype(np.float32))
+    ix = apoe.Index.from_host(ds.D, S, B2, for_build=True)
+    power = orc.cal_power(ds.D7h, S, B2)
+    knn, dis = helpers.exact_knn(ds.D, S, B2)
+    want = orc.prune(ds.D7h, S, B2, knn, dis, power)
+    got = ix.prune(knn, dis, power)
+    assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1]) and np.array_equal(got[2], want[2])
+    ix.close()
 
 
 def _join_lists(n, nodes, rng):
