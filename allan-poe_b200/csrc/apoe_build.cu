@@ -97,6 +97,8 @@ __device__ __forceinline__ bool pair_owned(uint32_t mode, uint32_t me, uint32_t 
     if (mode == 0) return true;
     const uint32_t lo = min(me, other), hi = max(me, other), h = mix32(lo * 0x9e3779b1u + hi);
     if (mode == 2 && (h & 2u)) return true;
+    if (mode == 3 && (h & 2u)) return false;          // half of all pairs dropped
+    if (mode == 4 && (h & 6u)) return false;          // three quarters dropped
     return (h & 1u) ? me < other : me > other;
 }
 
@@ -118,6 +120,8 @@ __global__ void knn_init_kernel(Knn k, uint32_t seed) {
 }
 
 __device__ __forceinline__ void jtab_insert(uint2 *tab, uint32_t mask, uint32_t shift, uint32_t key, uint32_t valbits);
+__device__ __forceinline__ uint32_t f2ord(float f);
+__device__ __forceinline__ float ord2f(uint32_t o);
 
 // ---------------------------------------------------------------------------------------------------------
 // Term-seeded start.  The hybrid distance of two documents is dominated by the BM25 weights of the rare terms
@@ -411,26 +415,50 @@ __global__ void __launch_bounds__(256, 2) join_dense_simt_kernel(uint32_t node0,
 }
 
 // ---------------------------------------------------------------------------------------------------------
-// Two-choice (cuckoo) term tables in shared memory.  A row's (term id, value) pairs are stored so that every key
-// sits in one of its two hashed slots; a lookup is two loads and two compares with no branch, which matters
-// because a warp probes 100+ keys per step and a rarely taken chain walk would be taken by some lane every time.
-// An entry is one 64-bit word: id in the low half, value bits in the high half; empty = (0xFFFFFFFF, 0).
+// Two-choice (cuckoo) term tables in shared memory, G tables side by side.  Every key of a hashed row sits in one of
+// its two hashed slots, so a lookup is two loads and two compares with no branch -- this matters because a warp
+// probes 100+ keys per step and a rarely taken chain walk would be taken by some lane every time.  The G tables of
+// a group share the hash functions and are interleaved: slot h is one line of G keys (K[h * G + g]) and one line of
+// G value words (V[h * G + g]); a probe fetches the key line of all G tables in one vector load and touches V only
+// on a match, which halves the shared-memory wavefronts against G separate (key, value) tables.  Empty: key
+// 0xFFFFFFFF, value 0.
 // ---------------------------------------------------------------------------------------------------------
-constexpr unsigned long long kCkEmpty = 0x00000000FFFFFFFFull;
 __device__ __forceinline__ uint32_t ck_h1(uint32_t key, uint32_t shift) { return (key * 2654435761u) >> shift; }
 __device__ __forceinline__ uint32_t ck_h2(uint32_t key, uint32_t shift) { return ((key ^ 0x5bd1e995u) * 0x85ebca6bu + 0x1b873593u) >> shift; }
-// Lock-free insertion by eviction; false when the kick budget runs out (the caller then gives the row up).
-__device__ __forceinline__ bool ck_insert(unsigned long long *tab, uint32_t shift, uint32_t key, uint32_t valbits) {
-    unsigned long long item = ((unsigned long long)valbits << 32) | key;
+// Lock-free key insertion by eviction into table g; false when the kick budget runs out (the caller gives the row up).
+template <int G>
+__device__ __forceinline__ bool ck_insert_key(uint32_t *K, uint32_t g, uint32_t shift, uint32_t key) {
     uint32_t h = ck_h1(key, shift);
     for (int kick = 0; kick < 48; ++kick) {
-        const unsigned long long old = atomicExch(tab + h, item);
-        if (old == kCkEmpty) return true;
-        item = old;
-        const uint32_t k = (uint32_t)old, a1 = ck_h1(k, shift), a2 = ck_h2(k, shift);
+        const uint32_t old = atomicExch(K + h * G + g, key);
+        if (old == kEmpty) return true;
+        key = old;
+        const uint32_t a1 = ck_h1(key, shift), a2 = ck_h2(key, shift);
         h = h == a1 ? a2 : a1;
     }
     return false;
+}
+// After all keys of table g are placed: the value goes where its key ended up.
+template <int G>
+__device__ __forceinline__ uint32_t ck_store_value(const uint32_t *K, uint32_t *V, uint32_t g, uint32_t shift, uint32_t key, uint32_t valbits) {
+    const uint32_t h1 = ck_h1(key, shift), h2 = ck_h2(key, shift);
+    const uint32_t h = K[h1 * G + g] == key ? h1 : (K[h2 * G + g] == key ? h2 : kEmpty);
+    if (h != kEmpty) V[h * G + g] = valbits;
+    return h;   // the slot, 0xFFFFFFFF when the key was given up
+}
+template <int G> struct KeyLine;
+template <> struct KeyLine<4> { static __device__ __forceinline__ void load(const uint32_t *K, uint32_t h, uint32_t (&k)[4]) { const uint4 v = *reinterpret_cast<const uint4 *>(K + h * 4); k[0] = v.x; k[1] = v.y; k[2] = v.z; k[3] = v.w; } };
+template <> struct KeyLine<2> { static __device__ __forceinline__ void load(const uint32_t *K, uint32_t h, uint32_t (&k)[2]) { const uint2 v = *reinterpret_cast<const uint2 *>(K + h * 2); k[0] = v.x; k[1] = v.y; } };
+template <> struct KeyLine<1> { static __device__ __forceinline__ void load(const uint32_t *K, uint32_t h, uint32_t (&k)[1]) { k[0] = K[h]; } };
+// value x matched value of table g for one probed key (0 when the table lacks the key); *found tells which
+template <int G>
+__device__ __forceinline__ uint32_t ck_match(const uint32_t *V, const uint32_t (&k1)[G], const uint32_t (&k2)[G], int g, uint32_t h1, uint32_t h2,
+                                             uint32_t key, bool *found) {
+    const bool hit1 = k1[g] == key, hit2 = k2[g] == key;
+    uint32_t vb = 0;
+    if (hit1 || hit2) vb = V[(hit1 ? h1 : h2) * G + g];
+    *found = hit1 || hit2;
+    return vb;
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -453,6 +481,7 @@ struct JoinArgs {
     uint32_t o_tab, o_dm, o_arena;
 };
 constexpr int kJoinThreads = 512;
+constexpr int kJoinSlots = 2;     // terms per lane and pass of the probing loop (a pass covers 32 x this many terms)
 
 __device__ __forceinline__ void jtab_insert(uint2 *tab, uint32_t mask, uint32_t shift, uint32_t key, uint32_t valbits) {
     uint32_t h = (key * 2654435761u) >> shift;
@@ -464,13 +493,16 @@ __device__ __forceinline__ void jtab_insert(uint2 *tab, uint32_t mask, uint32_t 
     }
 }
 
+template <int G>
 __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const JoinArgs a) {
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t mbar;
     __shared__ uint32_t s_off[kPart + 1], s_id[kPart], s_ns[kPart], s_nb[kPart];
     __shared__ float s_kth[kPart];
-    __shared__ uint32_t s_rows, s_new, s_bad;
-    uint2 *tab = reinterpret_cast<uint2 *>(smem + a.o_tab);
+    __shared__ uint32_t s_rows, s_new, s_bad, s_wide;
+    const uint32_t tabn = a.tab_mask + 1;
+    uint32_t *K = reinterpret_cast<uint32_t *>(smem + a.o_tab);   // [slot][G] keys, then [slot][G] value words
+    uint32_t *V = K + (size_t)tabn * G;
     float *dm = reinterpret_cast<float *>(smem + a.o_dm);  // [32][64] distances: new row i x participant j
     uint8_t *arena = smem + a.o_arena;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -479,7 +511,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     const uint32_t v = a.node0 + local;
     uint32_t n_new = a.pcnt[(size_t)v * 2], rows = a.pcnt[(size_t)v * 2 + 1];
     if (rows <= 1) return;
-    if (tid == 0) { mbar_init(&mbar, 1); mbar_fence_init(); s_bad = 0; }
+    if (tid == 0) { mbar_init(&mbar, 1); mbar_fence_init(); s_bad = 0; s_wide = 0; }
     if (tid < kPart) {
         const uint32_t id = tid < (int)rows ? a.plist[(size_t)v * kPart + tid] : kEmpty;
         s_id[tid] = id;
@@ -506,7 +538,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
         const uint32_t sz = s_off[tid + 1] - s_off[tid];
         if (sz) bulk_g2s(arena + s_off[tid], a.rec + meta_off16(a.meta[s_id[tid]]) * 16ull + kDenseBytes, sz, &mbar);
     }
-    for (uint32_t i = tid; i < (a.tab_mask + 1) * a.groups; i += kJoinThreads) tab[i] = make_uint2(kEmpty, 0u);
+    for (uint32_t i = tid; i < tabn * G; i += kJoinThreads) { K[i] = kEmpty; V[i] = 0u; }
     mbar_wait_bounded(&mbar, 0, a.err, 3u);
     __syncthreads();
 
@@ -520,33 +552,49 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     __syncthreads();
     const float *D = s_D;
     unsigned long long evals = 0;
-    for (uint32_t i0 = 0; i0 < n_new; i0 += a.groups) {
-        const uint32_t g_cnt = min(a.groups, n_new - i0);
-        // hash the terms of rows i0 .. i0+g_cnt-1 (BM25 ids get bit 31 so both vocabularies share one table)
+    for (uint32_t i0 = 0; i0 < n_new; i0 += G) {
+        const uint32_t g_cnt = min((uint32_t)G, n_new - i0);
+        // hash the terms of rows i0 .. i0+g_cnt-1 (BM25 ids get bit 31 so both vocabularies share one table):
+        // keys first, then every value to the slot its key settled in
         for (uint32_t g = 0; g < g_cnt; ++g) {
             const uint32_t i = i0 + g;
             const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[i]);
             const uint32_t ns = s_ns[i], nb = s_nb[i], pns = pad2(ns);
-            unsigned long long *t = reinterpret_cast<unsigned long long *>(tab + (size_t)g * (a.tab_mask + 1));
             for (uint32_t j = tid; j < ns + nb; j += kJoinThreads) {
-                const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
-                if (!ck_insert(t, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y)) atomicOr(&s_bad, 1u << g);
+                const uint32_t id = j < ns ? pr[j].x : (pr[pns + (j - ns)].x | 0x80000000u);
+                if (!ck_insert_key<G>(K, g, a.tab_shift, id)) atomicOr(&s_bad, 1u << g);
+            }
+        }
+        __syncthreads();
+        uint32_t my_slot[G];   // where this thread's term of each hashed row ended up (rows of <= kJoinThreads terms)
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            my_slot[g] = kEmpty;
+            if ((uint32_t)g < g_cnt) {
+                const uint32_t i = i0 + g;
+                const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[i]);
+                const uint32_t ns = s_ns[i], nb = s_nb[i], pns = pad2(ns);
+                if (ns + nb > (uint32_t)kJoinThreads && tid == 0) s_wide = 1;
+                for (uint32_t j = tid; j < ns + nb; j += kJoinThreads) {
+                    const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
+                    my_slot[g] = ck_store_value<G>(K, V, g, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y);
+                }
             }
         }
         __syncthreads();
         const uint32_t bad = s_bad;   // rows whose table could not be built sit this join out
-        // One warp per participant j: its terms are read into registers once (6 per lane per 192-term chunk, slot
-        // indices precomputed -- every table uses the same hash) and probed against each hashed row i < j of the
-        // group, two loads per term and table.
+        const uint32_t wide = s_wide;
+        // One warp per participant j: its terms pass through registers 64 at a time (the two slot indices of each
+        // computed once -- every table uses the same hashes) and are probed against the key lines of the group.
         for (uint32_t j = warp; j < rows; j += kJoinThreads / 32) {
             if (j <= i0) continue;
             const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[j]);
             const uint32_t ns = s_ns[j], nb = s_nb[j], pns = pad2(ns), nt = ns + nb;
             float acc[4] = {0.f, 0.f, 0.f, 0.f};
-            for (uint32_t base = 0; base < nt; base += 192) {
-                uint32_t key[6], h1[6], h2[6]; float val[6];
+            for (uint32_t base = 0; base < nt; base += 32 * kJoinSlots) {
+                uint32_t key[kJoinSlots], h1[kJoinSlots], h2[kJoinSlots]; float val[kJoinSlots];
 #pragma unroll
-                for (int t = 0; t < 6; ++t) {
+                for (int t = 0; t < kJoinSlots; ++t) {
                     const uint32_t q = base + t * 32 + lane;
                     uint2 p = make_uint2(kEmpty, 0u);   // padding: matches only an empty slot, whose value is 0
                     if (q < nt) { p = q < ns ? pr[q] : pr[pns + (q - ns)]; if (q >= ns) p.x |= 0x80000000u; }
@@ -554,21 +602,14 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
                     h1[t] = ck_h1(p.x, a.tab_shift); h2[t] = ck_h2(p.x, a.tab_shift);
                 }
 #pragma unroll
-                for (int g = 0; g < 4; ++g) {
-                    if ((uint32_t)g < g_cnt) {
-                        const uint2 *t2 = tab + (size_t)g * (a.tab_mask + 1);
+                for (int t = 0; t < kJoinSlots; ++t) {
+                    uint32_t k1[G], k2[G];
+                    KeyLine<G>::load(K, h1[t], k1); KeyLine<G>::load(K, h2[t], k2);
 #pragma unroll
-                        for (int half = 0; half < 2; ++half) {
-                            uint2 e1[3], e2[3];
-#pragma unroll
-                            for (int t = 0; t < 3; ++t) { e1[t] = t2[h1[3 * half + t]]; e2[t] = t2[h2[3 * half + t]]; }
-#pragma unroll
-                            for (int t = 0; t < 3; ++t) {
-                                const uint32_t kk = key[3 * half + t];
-                                const uint32_t vb = e1[t].x == kk ? e1[t].y : (e2[t].x == kk ? e2[t].y : 0u);
-                                acc[g] = fmaf(__uint_as_float(vb), val[3 * half + t], acc[g]);
-                            }
-                        }
+                    for (int g = 0; g < G; ++g) {
+                        bool found;
+                        const uint32_t vb = ck_match<G>(V, k1, k2, g, h1[t], h2[t], key[t], &found);
+                        acc[g] = fmaf(__uint_as_float(vb), val[t], acc[g]);
                     }
                 }
             }
@@ -589,39 +630,50 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
             }
         }
         __syncthreads();
-        for (uint32_t q = tid; q < (a.tab_mask + 1) * g_cnt; q += kJoinThreads) tab[q] = make_uint2(kEmpty, 0u);
-        if (tid == 0) s_bad = 0;
+        // empty the tables again: every thread wipes the slots of its own terms, unless a row was too long for that
+        if (wide || bad) { for (uint32_t q = tid; q < tabn * G; q += kJoinThreads) { K[q] = kEmpty; V[q] = 0u; } }
+        else {
+#pragma unroll
+            for (int g = 0; g < G; ++g) if (my_slot[g] != kEmpty) { K[my_slot[g] * G + g] = kEmpty; V[my_slot[g] * G + g] = 0u; }
+        }
+        if (tid == 0) { s_bad = 0; s_wide = 0; }
         __syncthreads();
     }
 
-    // partner selection: every participant proposes to itself its kPropPer closest partners of this join
-    if (tid < (int)rows) {
-        const uint32_t p = tid;
-        float bd[kPropPerMax]; uint32_t bi[kPropPerMax];
-        const int kPropPer = (int)a.prop_per;
+    // partner selection: every participant proposes to itself its prop_per closest partners of this join that beat
+    // its current 64th distance.  One warp per participant: each lane holds the distances to partners lane and
+    // lane + 32, the best ones are peeled off by warp-wide minima.
+    for (uint32_t p = warp; p < rows; p += kJoinThreads / 32) {
+        const uint32_t lim = p < n_new ? rows : n_new, me = s_id[p];
+        const float kth = s_kth[p];
+        unsigned long long c[2];
 #pragma unroll
-        for (int q = 0; q < kPropPerMax; ++q) { bd[q] = s_kth[p]; bi[q] = kEmpty; }
-        const uint32_t lim = p < n_new ? rows : n_new;
-        for (uint32_t j = 0; j < lim; ++j) {
-            if (j == p || !pair_owned(a.own_mode, s_id[p], s_id[j])) continue;
-            const uint32_t lo = min(p, j), hi = max(p, j);
-            const float d = dm[lo * kPart + hi];
-            if (d < bd[kPropPer - 1]) {
-                // insertion into the ascending top list (fully unrolled so the arrays stay in registers)
-                float cd = d; uint32_t ci = s_id[j];
-#pragma unroll
-                for (int q = 0; q < kPropPerMax; ++q)
-                    if (q < kPropPer && cd < bd[q]) { const float td = bd[q]; const uint32_t ti = bi[q]; bd[q] = cd; bi[q] = ci; cd = td; ci = ti; }
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t j = lane + 32 * h;
+            c[h] = ~0ull;
+            if (j < lim && j != p && pair_owned(a.own_mode, me, s_id[j])) {
+                const float d = dm[min(p, j) * kPart + max(p, j)];
+                if (d < kth) c[h] = ((unsigned long long)f2ord(d) << 32) | j;
             }
         }
-        const uint32_t me = s_id[p];
+        unsigned long long mine = ~0ull;   // lane q ends up with the q-th best
+        for (uint32_t q = 0; q < a.prop_per; ++q) {
+            unsigned long long best = c[0] < c[1] ? c[0] : c[1];
 #pragma unroll
-        for (int q = 0; q < kPropPerMax; ++q)
-            if (q < kPropPer && bi[q] != kEmpty) {
-                const uint32_t t = atomicAdd(&a.propn[me], 1u);
-                if (t < kPropCap) a.prop[(size_t)me * kPropCap + t] = make_uint2(__float_as_uint(bd[q]), bi[q]);
-                else atomicAdd(a.stats + 2, 1ull);
+            for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(kFull, best, o);
+                best = other < best ? other : best;
             }
+            if (best == ~0ull) break;
+            if (c[0] == best) c[0] = ~0ull;
+            if (c[1] == best) c[1] = ~0ull;
+            if (lane == q) mine = best;
+        }
+        if (mine != ~0ull) {
+            const uint32_t t = atomicAdd(&a.propn[me], 1u);
+            if (t < kPropCap) a.prop[(size_t)me * kPropCap + t] = make_uint2(__float_as_uint(ord2f((uint32_t)(mine >> 32))), s_id[(uint32_t)mine & 63u]);
+            else atomicAdd(a.stats + 2, 1ull);
+        }
     }
     if (evals) atomicAdd(a.stats + 0, evals);
 }
@@ -981,7 +1033,7 @@ __global__ void __launch_bounds__(kPruneThreads, 2) prune_kernel(const PruneArgs
 // then replays the selection steps on the finished 64 x 64 tables with one warp.  Nodes whose neighbours'
 // sparse sections do not fit the staging area are listed for the step-wise kernel.
 // ---------------------------------------------------------------------------------------------------------
-constexpr int kP2Threads = 512;
+constexpr int kP2Threads = 1024;
 constexpr int kP2Warps = kP2Threads / 32;
 constexpr int kP2Groups = 4;   // candidate rows hashed per pass
 
@@ -995,10 +1047,9 @@ struct Prune2Args {
 // One section (sparse or BM25) of streamed row `row` against the hashed candidate rows of a group: every lane walks
 // its terms j = lane, lane + 32, ... in ascending order, NS terms per pass, and adds value x matched value (zero
 // when the candidate lacks the term, which leaves the running sum as it is) -- the reference's per-lane order.
-template <int NS, bool BM>
-__device__ __forceinline__ void p2_section(const uint2 *__restrict__ row, uint32_t cnt, const uint2 *__restrict__ tab, uint32_t tabn,
-                                           uint32_t shift, uint32_t g_lo, uint32_t g_cnt, int lane, float (&part)[kP2Groups],
-                                           uint32_t &kwm) {
+template <int NS, bool BM, int G>
+__device__ __forceinline__ void p2_section(const uint2 *__restrict__ row, uint32_t cnt, const uint32_t *__restrict__ K, const uint32_t *__restrict__ V,
+                                           uint32_t shift, int lane, float (&part)[kP2Groups], uint32_t &kwm) {
     for (uint32_t j0 = 0; j0 < cnt; j0 += 32 * NS) {
         uint32_t key[NS], h1[NS], h2[NS], ownbit = 0;
         float val[NS];
@@ -1014,28 +1065,21 @@ __device__ __forceinline__ void p2_section(const uint2 *__restrict__ row, uint32
             h1[t] = ck_h1(pv.x, shift); h2[t] = ck_h2(pv.x, shift);
         }
 #pragma unroll
-        for (int gi = 0; gi < kP2Groups; ++gi) {
-            if ((uint32_t)gi < g_cnt && (uint32_t)gi >= g_lo) {
-                const uint2 *t2 = tab + (size_t)gi * tabn;
-                uint2 e1[NS], e2[NS];
+        for (int t = 0; t < NS; ++t) {
+            uint32_t k1[G], k2[G];
+            KeyLine<G>::load(K, h1[t], k1); KeyLine<G>::load(K, h2[t], k2);
 #pragma unroll
-                for (int t = 0; t < NS; ++t) { e1[t] = t2[h1[t]]; e2[t] = t2[h2[t]]; }
-                uint32_t fnd = 0;
-                float p = part[gi];
-#pragma unroll
-                for (int t = 0; t < NS; ++t) {
-                    const bool hit1 = e1[t].x == key[t], hit2 = e2[t].x == key[t];
-                    const uint32_t vb = hit1 ? e1[t].y : (hit2 ? e2[t].y : 0u);
-                    p = __fmaf_rn(__uint_as_float(vb), val[t], p);
-                    fnd |= (hit1 || hit2) ? (1u << t) : 0u;
-                }
-                part[gi] = p;
-                if (BM && (ownbit & ~fnd)) kwm |= 1u << gi;
+            for (int gi = 0; gi < G; ++gi) {
+                bool found;
+                const uint32_t vb = ck_match<G>(V, k1, k2, gi, h1[t], h2[t], key[t], &found);
+                part[gi] = __fmaf_rn(__uint_as_float(vb), val[t], part[gi]);
+                if (BM && ((ownbit >> t) & 1u) && !found) kwm |= 1u << gi;
             }
         }
     }
 }
 
+template <int G>
 __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2Args q) {
     const PruneArgs &a = q.p;
     extern __shared__ __align__(128) uint8_t smem[];
@@ -1046,7 +1090,9 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
     __shared__ uint32_t s_task, s_fit;
     float *IP = reinterpret_cast<float *>(smem + q.o_ip);      // [b][a], a < b
     uint8_t *KW = smem + q.o_kw;                               // [b][a] keyword flag of the pair
-    uint2 *tab = reinterpret_cast<uint2 *>(smem + a.o_tab);
+    const uint32_t tabn = a.tab_mask + 1;
+    uint32_t *K = reinterpret_cast<uint32_t *>(smem + a.o_tab);   // [slot][G] keys, then [slot][G] value words
+    uint32_t *V = K + (size_t)tabn * G;
     uint32_t *own = reinterpret_cast<uint32_t *>(smem + a.o_own);
     uint8_t *region = smem + q.o_region;
     uint32_t *lists = reinterpret_cast<uint32_t *>(region);
@@ -1165,7 +1211,7 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
         const uint32_t sz = s_off[tid + 1] - s_off[tid];
         if (sz) bulk_g2s(region + s_off[tid], a.rec + meta_off16(meta0[tid]) * 16ull + kDenseBytes, sz, &mbar);
     }
-    for (uint32_t i = tid; i < (a.tab_mask + 1) * q.groups; i += kP2Threads) tab[i] = make_uint2(kEmpty, 0u);
+    for (uint32_t i = tid; i < tabn * G; i += kP2Threads) { K[i] = kEmpty; V[i] = 0u; }
     if (s_off[kK]) mbar_wait_bounded(&mbar, parity, q.err, 6u);
     __syncthreads();
     // bit 31 of a staged BM25 id: the node itself owns the term (ref :144-149 asks this per pair)
@@ -1176,17 +1222,16 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
     }
     __syncthreads();
 
-    for (uint32_t b0 = 0; b0 < (uint32_t)kK; b0 += q.groups) {
-        const uint32_t g_cnt = min(q.groups, (uint32_t)kK - b0);
+    for (uint32_t b0 = 0; b0 < (uint32_t)kK; b0 += G) {
+        const uint32_t g_cnt = min((uint32_t)G, (uint32_t)kK - b0);
         for (uint32_t gi = 0; gi < g_cnt; ++gi) {
             const uint32_t b = b0 + gi;
             if (b == 0) continue;
             const uint2 *pr = reinterpret_cast<const uint2 *>(region + s_off[b]);
             const uint32_t ns = meta_ns(meta0[b]), nb = meta_nb(meta0[b]), pns = pad2(ns);
-            unsigned long long *t = reinterpret_cast<unsigned long long *>(tab + (size_t)gi * (a.tab_mask + 1));
             for (uint32_t j = tid; j < ns + nb; j += kP2Threads) {
-                const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
-                if (!ck_insert(t, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y)) s_fit = 0;
+                const uint32_t id = j < ns ? pr[j].x : (pr[pns + (j - ns)].x | 0x80000000u);
+                if (!ck_insert_key<G>(K, gi, a.tab_shift, id)) s_fit = 0;
             }
         }
         __syncthreads();
@@ -1194,15 +1239,25 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
             if (tid == 0) q.ovf_list[atomicAdd(q.ovf_cnt, 1u)] = bid;
             return;
         }
+        for (uint32_t gi = 0; gi < g_cnt; ++gi) {
+            const uint32_t b = b0 + gi;
+            if (b == 0) continue;
+            const uint2 *pr = reinterpret_cast<const uint2 *>(region + s_off[b]);
+            const uint32_t ns = meta_ns(meta0[b]), nb = meta_nb(meta0[b]), pns = pad2(ns);
+            for (uint32_t j = tid; j < ns + nb; j += kP2Threads) {
+                const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
+                ck_store_value<G>(K, V, gi, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y);
+            }
+        }
+        __syncthreads();
         const uint32_t a_end = min(b0 + g_cnt - 1u, (uint32_t)kK - 1u);   // rows a < the group's last candidate
         for (uint32_t ar = warp; ar < a_end; ar += kP2Warps) {
             const uint2 *pr = reinterpret_cast<const uint2 *>(region + s_off[ar]);
             const uint32_t ns = meta_ns(meta0[ar]), nb = meta_nb(meta0[ar]), pns = pad2(ns);
             float sp[kP2Groups] = {0.f, 0.f, 0.f, 0.f}, bm[kP2Groups] = {0.f, 0.f, 0.f, 0.f};
             uint32_t kwm = 0;   // bit g: a BM25 term of row a that the node owns and candidate g lacks
-            const uint32_t g_lo = ar >= b0 ? ar - b0 + 1u : 0u;   // candidates b0 + g must come after row a
-            p2_section<4, false>(pr, ns, tab, a.tab_mask + 1, a.tab_shift, g_lo, g_cnt, lane, sp, kwm);
-            p2_section<2, true>(pr + pns, nb, tab, a.tab_mask + 1, a.tab_shift, g_lo, g_cnt, lane, bm, kwm);
+            p2_section<4, false, G>(pr, ns, K, V, a.tab_shift, lane, sp, kwm);
+            p2_section<2, true, G>(pr + pns, nb, K, V, a.tab_shift, lane, bm, kwm);
             float tot[kP2Groups];
 #pragma unroll
             for (int gi = 0; gi < kP2Groups; ++gi) tot[gi] = __fadd_rn(sp[gi], bm[gi]);
@@ -1226,7 +1281,7 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
             }
         }
         __syncthreads();
-        for (uint32_t i = tid; i < (a.tab_mask + 1) * g_cnt; i += kP2Threads) tab[i] = make_uint2(kEmpty, 0u);
+        for (uint32_t i = tid; i < tabn * G; i += kP2Threads) { K[i] = kEmpty; V[i] = 0u; }
         __syncthreads();
     }
 
@@ -1441,7 +1496,7 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
     const size_t fixed = 4096;   // static shared memory of the kernel, rounded up
     const size_t avail = ix->smem_per_block > fixed ? ix->smem_per_block - fixed : 0;
     uint32_t groups = kP2Groups;
-    while (groups > 1 && q.p.o_tab + (size_t)groups * tabn * 8 + 96 * 1024 > avail) --groups;
+    while (groups > 1 && q.p.o_tab + (size_t)groups * tabn * 8 + 96 * 1024 > avail) groups >>= 1;   // key lines are 1, 2 or 4 wide
     q.groups = groups;
     q.o_region = (uint32_t)((q.p.o_tab + (size_t)groups * tabn * 8 + 127) / 128 * 128);
     const char *force = getenv("APOE_PRUNE_KERNEL");
@@ -1454,8 +1509,9 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
         AP_CUDA(cudaMemsetAsync(ovf_cnt, 0, 4));
         q.ovf_list = ovf_list; q.ovf_cnt = ovf_cnt; q.err = ix->d_ctl + 1;
         const size_t smem2 = (size_t)q.o_region + q.region_bytes;
-        AP_CUDA(cudaFuncSetAttribute(prune_pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
-        prune_pairs_kernel<<<n, kP2Threads, smem2>>>(q);
+        auto pairs_kernel = groups == 4 ? prune_pairs_kernel<4> : (groups == 2 ? prune_pairs_kernel<2> : prune_pairs_kernel<1>);
+        AP_CUDA(cudaFuncSetAttribute(pairs_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem2));
+        pairs_kernel<<<n, kP2Threads, smem2>>>(q);
         AP_CUDA(cudaGetLastError());
         AP_CUDA(cudaMemcpy(&n_step, ovf_cnt, 4, cudaMemcpyDeviceToHost));
         a.node_list = ovf_list;
@@ -1558,7 +1614,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     uint32_t launches = 0;
     AP_TRY(norms_run(ix, power)); ++launches;
     knn_init_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k, o.seed ? o.seed : 20261125u); ++launches;
-    const uint32_t own_mode = (o.reserved[1] & 8u) ? 1u : ((o.reserved[1] & 16u) ? 2u : 0u);
+    const uint32_t own_mode = (o.reserved[1] >> 3) & 7u;
     if (!(o.reserved[1] & 2u)) AP_TRY(seed_run(ix, k, o.reserved[2] ? std::min<uint32_t>(o.reserved[2], 32u) : 8u, own_mode, &launches));   // term-seeded start unless switched off
 
     // scratch for the dense tiles, in batches of nodes
@@ -1576,13 +1632,15 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     ja.tab_mask = tabn - 1; ja.tab_shift = 32 - log2u(tabn);
     // two CTAs per SM: tables for up to 4 hashed rows, the 32 x 64 distance tile, the rest is arena
     const size_t per_cta = ix->smem_per_sm / 2 - 1024 - 10240 /* static: dense tile + bookkeeping */;
-    ja.groups = (uint32_t)std::max<size_t>(1, std::min<size_t>(4, (per_cta / 4) / (8 * (size_t)tabn)));
+    // key lines of a group are 1, 2 or 4 wide; four tables may take up to 40 % of the CTA's shared memory
+    ja.groups = 8 * (size_t)tabn * 4 <= per_cta * 2 / 5 ? 4u : (8 * (size_t)tabn * 2 <= per_cta / 3 ? 2u : 1u);
     ja.o_tab = 0; ja.o_dm = 8 * tabn * ja.groups; ja.o_arena = (ja.o_dm + 4 * kNewMax * kPart + 127) / 128 * 128;
     if (per_cta <= ja.o_arena + 8u * (pad2(ix->max_ns) + pad2(ix->max_nb)) * 2)
         return fail(AP_ERR_LIMIT, "rows of %u + %u terms leave no room for a local join in shared memory", ix->max_ns, ix->max_nb);
     ja.arena_bytes = (uint32_t)std::min<size_t>((per_cta - ja.o_arena) / 128 * 128, 512u * 1024u);
     const size_t join_smem = ja.o_arena + ja.arena_bytes;
-    AP_CUDA(cudaFuncSetAttribute(join_sparse_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)join_smem));
+    auto join_kernel = ja.groups == 4 ? join_sparse_kernel<4> : (ja.groups == 2 ? join_sparse_kernel<2> : join_sparse_kernel<1>);
+    AP_CUDA(cudaFuncSetAttribute(join_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)join_smem));
     const size_t simt_smem = (size_t)kNewMax * kDenseBytes;
     AP_CUDA(cudaFuncSetAttribute(join_dense_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)simt_smem));
 
@@ -1606,7 +1664,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
             else AP_TRY(join_dense_tc_launch(ix, node0, nodes, k.plist, k.pcnt, D, 0));
             if (node0 == 0) AP_CUDA(cudaEventRecord(ev[2]));
             ja.node0 = node0; ja.nodes = nodes;
-            join_sparse_kernel<<<nodes, kJoinThreads, join_smem>>>(ja);
+            join_kernel<<<nodes, kJoinThreads, join_smem>>>(ja);
             launches += 2;
         }
         AP_CUDA(cudaEventRecord(ev[3]));
