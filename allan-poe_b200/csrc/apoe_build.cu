@@ -1084,10 +1084,10 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
     const PruneArgs &a = q.p;
     extern __shared__ __align__(128) uint8_t smem[];
     __shared__ uint64_t mbar;
-    __shared__ uint32_t nei0[kK], nei1[kK], nei2[kK + 1], det[kK], s_off[kK + 1], sel_pos[kK];
+    __shared__ uint32_t nei0[kK], nei1[kK], nei2[kK + 1], det[kK], s_off[kK + 1];
     __shared__ uint64_t meta0[kK];
     __shared__ float pow0[kK];
-    __shared__ uint32_t s_task, s_fit;
+    __shared__ uint32_t s_task, s_fit, s_dup;
     float *IP = reinterpret_cast<float *>(smem + q.o_ip);      // [b][a], a < b
     uint8_t *KW = smem + q.o_kw;                               // [b][a] keyword flag of the pair
     const uint32_t tabn = a.tab_mask + 1;
@@ -1126,14 +1126,46 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
         lists[idx] = a.knn[(size_t)nei0[p] * kK + j];
         ldis[idx] = a.knn_dis[(size_t)nei0[p] * kK + j];
     }
+    // position table: R[p][t] = first place of neighbour t's id in neighbour p's list (the reference scans the list
+    // for it); filled by looking every list entry up in a small hash of the node's own 64 neighbour ids
+    uint32_t *R = reinterpret_cast<uint32_t *>(ldis + kK * kK);          // 64 x 64
+    uint32_t *hk = R + kK * kK, *hv = hk + 256;                          // 256-slot hash: id -> a place t in nei0
+    for (uint32_t i = tid; i < kK * kK; i += kP2Threads) R[i] = kEmpty;
+    if (tid < 256) hk[tid] = kEmpty;
+    if (tid == 0) s_dup = 0;
+    __syncthreads();
+    if (tid < kK) {
+        const uint32_t id = nei0[tid];
+        uint32_t h = (id * 2654435761u) >> 24;
+        for (int s = 0; s < 256; ++s) {
+            const uint32_t old = atomicCAS(&hk[h], kEmpty, id);
+            if (old == kEmpty) { hv[h] = tid; break; }
+            if (old == id) { s_dup = 1; break; }      // the same id twice among the neighbours: slow path below
+            h = (h + 1) & 255u;
+        }
+    }
+    __syncthreads();
+    const bool dup = s_dup != 0;
+    for (uint32_t idx = tid; idx < kK * kK; idx += kP2Threads) {
+        const uint32_t pl = idx >> 6, j = idx & 63, id = lists[idx];
+        uint32_t h = (id * 2654435761u) >> 24, t = kEmpty;
+        for (int s = 0; s < 256; ++s) {
+            const uint32_t e = hk[h];
+            if (e == kEmpty) break;
+            if (e == id) { t = hv[h]; break; }
+            h = (h + 1) & 255u;
+        }
+        if (t != kEmpty) {
+            if (!dup) atomicMin(&R[pl * kK + t], j);
+            else for (uint32_t t2 = 0; t2 < (uint32_t)kK; ++t2) if (nei0[t2] == id) atomicMin(&R[pl * kK + t2], j);
+        }
+    }
     __syncthreads();
     for (uint32_t pair = tid; pair < kK * kK; pair += kP2Threads) {
-        const uint32_t p = pair >> 6, t = pair & 63;
-        if (t <= p) continue;
-        const uint32_t key = nei0[t];
-        int r = -1;
-        for (int j = 0; j < kK; ++j) if (lists[p * kK + j] == key) { r = j; break; }
-        if (r >= 0 && ldis[p * kK + r] < a.knn_dis[(size_t)bid * kK + t]) atomicAdd(&det[t], 1u);
+        const uint32_t pl = pair >> 6, t = pair & 63;
+        if (t <= pl) continue;
+        const uint32_t r = R[pair];
+        if (r != kEmpty && ldis[pl * kK + r] < a.knn_dis[(size_t)bid * kK + t]) atomicAdd(&det[t], 1u);
     }
     __syncthreads();
     block_bitonic_kv(det, nei0, kK, tid, kP2Threads);
@@ -1224,12 +1256,14 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
 
     for (uint32_t b0 = 0; b0 < (uint32_t)kK; b0 += G) {
         const uint32_t g_cnt = min((uint32_t)G, (uint32_t)kK - b0);
-        for (uint32_t gi = 0; gi < g_cnt; ++gi) {
+        // the G candidate rows are hashed side by side: a quarter of the CTA per row
+        constexpr uint32_t kSlice = kP2Threads / 4;
+        for (uint32_t gi = tid / kSlice; gi < g_cnt; gi += 4) {
             const uint32_t b = b0 + gi;
             if (b == 0) continue;
             const uint2 *pr = reinterpret_cast<const uint2 *>(region + s_off[b]);
             const uint32_t ns = meta_ns(meta0[b]), nb = meta_nb(meta0[b]), pns = pad2(ns);
-            for (uint32_t j = tid; j < ns + nb; j += kP2Threads) {
+            for (uint32_t j = tid % kSlice; j < ns + nb; j += kSlice) {
                 const uint32_t id = j < ns ? pr[j].x : (pr[pns + (j - ns)].x | 0x80000000u);
                 if (!ck_insert_key<G>(K, gi, a.tab_shift, id)) s_fit = 0;
             }
@@ -1239,12 +1273,12 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
             if (tid == 0) q.ovf_list[atomicAdd(q.ovf_cnt, 1u)] = bid;
             return;
         }
-        for (uint32_t gi = 0; gi < g_cnt; ++gi) {
+        for (uint32_t gi = tid / kSlice; gi < g_cnt; gi += 4) {
             const uint32_t b = b0 + gi;
             if (b == 0) continue;
             const uint2 *pr = reinterpret_cast<const uint2 *>(region + s_off[b]);
             const uint32_t ns = meta_ns(meta0[b]), nb = meta_nb(meta0[b]), pns = pad2(ns);
-            for (uint32_t j = tid; j < ns + nb; j += kP2Threads) {
+            for (uint32_t j = tid % kSlice; j < ns + nb; j += kSlice) {
                 const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
                 ck_store_value<G>(K, V, gi, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y);
             }
@@ -1281,47 +1315,71 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
             }
         }
         __syncthreads();
-        for (uint32_t i = tid; i < tabn * G; i += kP2Threads) { K[i] = kEmpty; V[i] = 0u; }
+        // empty the tables again: every term wipes the slots that hold its key
+        for (uint32_t gi = tid / kSlice; gi < g_cnt; gi += 4) {
+            const uint32_t b = b0 + gi;
+            if (b == 0) continue;
+            const uint2 *pr = reinterpret_cast<const uint2 *>(region + s_off[b]);
+            const uint32_t ns = meta_ns(meta0[b]), nb = meta_nb(meta0[b]), pns = pad2(ns);
+            for (uint32_t j = tid % kSlice; j < ns + nb; j += kSlice) {
+                const uint32_t id = j < ns ? pr[j].x : (pr[pns + (j - ns)].x | 0x80000000u);
+                const uint32_t h1 = ck_h1(id, a.tab_shift), h2 = ck_h2(id, a.tab_shift);
+                if (K[h1 * G + gi] == id) { K[h1 * G + gi] = kEmpty; V[h1 * G + gi] = 0u; }
+                if (K[h2 * G + gi] == id) { K[h2 * G + gi] = kEmpty; V[h2 * G + gi] = 0u; }
+            }
+        }
         __syncthreads();
     }
 
     // ---- the selection steps (ref :613-676) replayed on the tables by one warp -----------------------------
     if (warp == 0) {
+        // lane l keeps selected slots l and l + 32: the candidate's place in detour order, its norm, whether it is
+        // still alive (not tombstoned)
+        uint32_t pos[2] = {0u, 0u};
+        float spow[2] = {pow0[0], 0.f};
+        bool alive[2] = {lane == 0, false};
         uint32_t ipn = 1;
-        if (lane == 0) { nei1[0] = nei0[0]; sel_pos[0] = 0; }
-        __syncwarp();
+        unsigned long long kwmask = 0;   // bit n - 1: nei2[n] set
         for (uint32_t b = 1; b < (uint32_t)kK && ipn < (uint32_t)kK; ++b) {
             const float cpow = pow0[b];
-            bool rej = false, open = false, tomb[2] = {false, false};
+            bool rej = false, tomb[2], kw[2];
 #pragma unroll
             for (int h = 0; h < 2; ++h) {
-                const uint32_t i = lane + 32 * h;
-                if (i < ipn && nei1[i] != kEmpty) {
-                    const uint32_t pos = sel_pos[i];
-                    const float ip = IP[b * kK + pos];
-                    if (cpow < ip) rej = true;
-                    if (pow0[pos] < ip) tomb[h] = true;
-                }
+                const bool valid = lane + 32u * h < ipn && alive[h];
+                const float ip = valid ? IP[b * kK + pos[h]] : 0.0f;
+                rej = rej || (valid && cpow < ip);
+                tomb[h] = valid && spow[h] < ip;
+                kw[h] = valid && KW[b * kK + pos[h]] != 0;
             }
-            if (lane < 16) {
-                // slot i runs on warp i % 16 of the reference and that warp's flag stays set for the rest of the step
-                uint32_t vf = 0;
-                for (uint32_t i = lane; i < ipn; i += 16)
-                    if (nei1[i] != kEmpty) {
-                        if (KW[b * kK + sel_pos[i]]) vf = 1;
-                        if (vf != 1) open = true;
-                    }
-            }
-            __syncwarp();
-#pragma unroll
-            for (int h = 0; h < 2; ++h) if (tomb[h]) nei1[lane + 32 * h] = kEmpty;
+            const uint32_t am0 = __ballot_sync(kFull, lane < ipn && alive[0]), am1 = __ballot_sync(kFull, lane + 32u < ipn && alive[1]);
+            const uint32_t km0 = __ballot_sync(kFull, kw[0]), km1 = __ballot_sync(kFull, kw[1]);
+            // The reference runs slot i on warp i % 16 and that warp's flag, once a slot set it, stays set for the rest of
+            // the step: within a class (i mod 16, ascending i) the step stays "open" exactly when the first live slot of
+            // the class has no keyword flag.
+            const uint32_t r = lane & 15u;
+            const uint32_t e = ((am0 >> r) & 1u) | (((am0 >> (r + 16)) & 1u) << 1) | (((am1 >> r) & 1u) << 2) | (((am1 >> (r + 16)) & 1u) << 3);
+            const uint32_t kk = ((km0 >> r) & 1u) | (((km0 >> (r + 16)) & 1u) << 1) | (((km1 >> r) & 1u) << 2) | (((km1 >> (r + 16)) & 1u) << 3);
+            const bool open = e != 0 && ((kk >> (__ffs(e) - 1)) & 1u) == 0;
             const bool rej_any = __any_sync(kFull, rej), open_any = __any_sync(kFull, open);
+            alive[0] = alive[0] && !tomb[0]; alive[1] = alive[1] && !tomb[1];
             uint32_t n2 = ipn;
-            if (!rej_any) { if (lane == 0) { nei1[n2] = nei0[b]; sel_pos[n2] = b; } ++n2; }
-            if (!open_any && lane == 0) nei2[n2] = 1;   // written after the increment, as in the reference
+            if (!rej_any) {
+                if (lane == (n2 & 31u)) {
+                    if (n2 < 32u) { pos[0] = b; spow[0] = cpow; alive[0] = true; }
+                    else { pos[1] = b; spow[1] = cpow; alive[1] = true; }
+                }
+                ++n2;
+            }
+            if (!open_any) kwmask |= 1ull << (n2 - 1u);   // nei2[n2], indexed after the increment as in the reference
             ipn = n2;
-            __syncwarp();
         }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            const uint32_t i = lane + 32u * h;
+            if (i < ipn) nei1[i] = alive[h] ? nei0[pos[h]] : kEmpty;
+            if (i < (uint32_t)kK) nei2[i + 1] = (uint32_t)((kwmask >> i) & 1ull);
+        }
+        __syncwarp();
         if (lane == 0) {
             uint32_t count = 0, i_neis;
             for (i_neis = 0; i_neis < ipn && count < AP_DEGREE; ++i_neis)
