@@ -16,7 +16,7 @@ _LIB = None
 
 AP_OK = 0
 CREATE_FOR_BUILD = 1
-BUILD_SIMT_JOIN, BUILD_KEEP_KNN = 1, 2
+BUILD_SIMT_JOIN, BUILD_KEEP_KNN, BUILD_RANDOM_START, BUILD_SHARED_PAIRS, BUILD_REVERSE_PASS = 1, 2, 4, 8, 16
 SEARCH_KEYWORD, SEARCH_KG, SEARCH_RAW_WEIGHTS, SEARCH_UNFUSED_DENSE = 1, 2, 4, 8
 DIM, ROW, DEGREE, KNN, ENTRY_POINTS = 1024, 40, 32, 64, 32
 
@@ -33,13 +33,13 @@ class _Csr(C.Structure):
 
 class BuildOpts(C.Structure):
     _fields_ = [("iterations", C.c_uint32), ("seed", C.c_uint32), ("flags", C.c_uint32), ("dense_scale", C.c_float),
-                ("reserved", C.c_uint32 * 4)]
+                ("proposals", C.c_uint32), ("seed_take", C.c_uint32), ("reserved", C.c_uint32 * 2)]
 
 
 class BuildStats(C.Structure):
     _fields_ = [("seconds_total", C.c_double), ("seconds_knn", C.c_double), ("seconds_prune", C.c_double),
                 ("distance_evals", C.c_uint64), ("list_updates", C.c_uint64), ("iterations_run", C.c_uint32),
-                ("launches", C.c_uint32), ("reserved", C.c_uint32 * 4)]
+                ("launches", C.c_uint32), ("proposal_overflows", C.c_uint32), ("phase_10us", C.c_uint32 * 3)]
 
 
 class SearchOpts(C.Structure):
@@ -168,11 +168,10 @@ class Index:
     def save_graph(self, path: str) -> None:
         _check(lib().ap_index_save_graph(self._h, path.encode()))
 
-    def build(self, iterations: int = 0, seed: int = 0, flags: int = 0, dense_scale: float = 0.0, prop_per: int = 0, tune: int = 0, seed_take: int = 0) -> BuildStats:
-        o = BuildOpts(iterations=iterations, seed=seed, flags=flags, dense_scale=dense_scale)
-        o.reserved[0] = prop_per
-        o.reserved[1] = tune
-        o.reserved[2] = seed_take
+    def build(self, iterations: int = 0, seed: int = 0, flags: int = 0, dense_scale: float = 0.0, proposals: int = 0,
+              seed_take: int = 0) -> BuildStats:
+        o = BuildOpts(iterations=iterations, seed=seed, flags=flags, dense_scale=dense_scale, proposals=proposals,
+                      seed_take=seed_take)
         st = BuildStats()
         _check(lib().ap_index_build(self._h, C.byref(o), C.byref(st)))
         return st

@@ -91,14 +91,12 @@ __device__ __forceinline__ uint32_t mix32(uint32_t x) {
     return x;
 }
 
-// Pair ownership (experimental): mode 0 offers an evaluated pair to both ends, mode 1 to exactly one end chosen by
-// a hash of the two ids, mode 2 to one end for half of the pairs and to both for the rest.
-__device__ __forceinline__ bool pair_owned(uint32_t mode, uint32_t me, uint32_t other) {
-    if (mode == 0) return true;
+// Pair ownership: an evaluated pair is offered to exactly one of its ends, chosen by a hash of the two ids, unless
+// `shared` asks for both.  A document's list then holds its nearest among the pairs it owns, the other pairs reach it
+// as reverse edges of the final rows.
+__device__ __forceinline__ bool pair_owned(uint32_t shared, uint32_t me, uint32_t other) {
+    if (shared) return true;
     const uint32_t lo = min(me, other), hi = max(me, other), h = mix32(lo * 0x9e3779b1u + hi);
-    if (mode == 2 && (h & 2u)) return true;
-    if (mode == 3 && (h & 2u)) return false;          // half of all pairs dropped
-    if (mode == 4 && (h & 6u)) return false;          // three quarters dropped
     return (h & 1u) ? me < other : me > other;
 }
 
@@ -208,7 +206,7 @@ __global__ void seed_cand_kernel(uint32_t n, const uint64_t *__restrict__ meta, 
 // terms go into a per-warp hash table, its dense row into registers, each candidate's record is read once.
 constexpr int kSeedWarps = 4;
 __global__ void __launch_bounds__(kSeedWarps * 32) seed_dist_kernel(Knn k, const uint64_t *__restrict__ meta, const uint8_t *__restrict__ rec,
-                                                                   const uint32_t *__restrict__ cand, uint32_t tab_mask, uint32_t tab_shift, uint32_t own_mode) {
+                                                                   const uint32_t *__restrict__ cand, uint32_t tab_mask, uint32_t tab_shift, uint32_t shared_pairs) {
     extern __shared__ __align__(16) uint8_t smem[];
     const uint32_t lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint32_t v = blockIdx.x * kSeedWarps + warp;
@@ -265,11 +263,11 @@ __global__ void __launch_bounds__(kSeedWarps * 32) seed_dist_kernel(Knn k, const
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(kFull, acc, o);
         if (lane == 0) {
             const float d = 1.0f - acc;
-            if (pair_owned(own_mode, v, c)) {
+            if (pair_owned(shared_pairs, v, c)) {
                 const uint32_t t = atomicAdd(&k.propn[v], 1u);
                 if (t < kPropCap) k.prop[(size_t)v * kPropCap + t] = make_uint2(__float_as_uint(d), c);
             }
-            if (pair_owned(own_mode, c, v)) {
+            if (pair_owned(shared_pairs, c, v)) {
                 const uint32_t t2 = atomicAdd(&k.propn[c], 1u);
                 if (t2 < kPropCap) k.prop[(size_t)c * kPropCap + t2] = make_uint2(__float_as_uint(d), v);
             }
@@ -477,7 +475,7 @@ struct JoinArgs {
     uint32_t arena_bytes;    // shared-memory budget for the sparse sections of all participants
     uint32_t tab_mask, tab_shift, groups;  // hash table of one new row's terms; rows hashed per round
     uint32_t prop_per;                     // partners proposed to each participant (<= kPropPerMax)
-    uint32_t own_mode;                     // see pair_owned
+    uint32_t shared_pairs;                 // see pair_owned
     uint32_t o_tab, o_dm, o_arena;
 };
 constexpr int kJoinThreads = 512;
@@ -499,7 +497,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     __shared__ uint64_t mbar;
     __shared__ uint32_t s_off[kPart + 1], s_id[kPart], s_ns[kPart], s_nb[kPart];
     __shared__ float s_kth[kPart];
-    __shared__ uint32_t s_rows, s_new, s_bad, s_wide;
+    __shared__ uint32_t s_rows, s_new, s_bad;
     const uint32_t tabn = a.tab_mask + 1;
     uint32_t *K = reinterpret_cast<uint32_t *>(smem + a.o_tab);   // [slot][G] keys, then [slot][G] value words
     uint32_t *V = K + (size_t)tabn * G;
@@ -511,7 +509,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     const uint32_t v = a.node0 + local;
     uint32_t n_new = a.pcnt[(size_t)v * 2], rows = a.pcnt[(size_t)v * 2 + 1];
     if (rows <= 1) return;
-    if (tid == 0) { mbar_init(&mbar, 1); mbar_fence_init(); s_bad = 0; s_wide = 0; }
+    if (tid == 0) { mbar_init(&mbar, 1); mbar_fence_init(); s_bad = 0; }
     if (tid < kPart) {
         const uint32_t id = tid < (int)rows ? a.plist[(size_t)v * kPart + tid] : kEmpty;
         s_id[tid] = id;
@@ -554,36 +552,30 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     unsigned long long evals = 0;
     for (uint32_t i0 = 0; i0 < n_new; i0 += G) {
         const uint32_t g_cnt = min((uint32_t)G, n_new - i0);
-        // hash the terms of rows i0 .. i0+g_cnt-1 (BM25 ids get bit 31 so both vocabularies share one table):
-        // keys first, then every value to the slot its key settled in
-        for (uint32_t g = 0; g < g_cnt; ++g) {
+        // hash the terms of rows i0 .. i0+g_cnt-1 (BM25 ids get bit 31 so both vocabularies share one table), a
+        // quarter of the CTA per row: keys first, then every value to the slot its key settled in
+        constexpr uint32_t kSlice = kJoinThreads / 4;
+        for (uint32_t g = tid / kSlice; g < g_cnt; g += 4) {
             const uint32_t i = i0 + g;
             const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[i]);
             const uint32_t ns = s_ns[i], nb = s_nb[i], pns = pad2(ns);
-            for (uint32_t j = tid; j < ns + nb; j += kJoinThreads) {
+            for (uint32_t j = tid % kSlice; j < ns + nb; j += kSlice) {
                 const uint32_t id = j < ns ? pr[j].x : (pr[pns + (j - ns)].x | 0x80000000u);
                 if (!ck_insert_key<G>(K, g, a.tab_shift, id)) atomicOr(&s_bad, 1u << g);
             }
         }
         __syncthreads();
-        uint32_t my_slot[G];   // where this thread's term of each hashed row ended up (rows of <= kJoinThreads terms)
-#pragma unroll
-        for (int g = 0; g < G; ++g) {
-            my_slot[g] = kEmpty;
-            if ((uint32_t)g < g_cnt) {
-                const uint32_t i = i0 + g;
-                const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[i]);
-                const uint32_t ns = s_ns[i], nb = s_nb[i], pns = pad2(ns);
-                if (ns + nb > (uint32_t)kJoinThreads && tid == 0) s_wide = 1;
-                for (uint32_t j = tid; j < ns + nb; j += kJoinThreads) {
-                    const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
-                    my_slot[g] = ck_store_value<G>(K, V, g, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y);
-                }
+        for (uint32_t g = tid / kSlice; g < g_cnt; g += 4) {
+            const uint32_t i = i0 + g;
+            const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[i]);
+            const uint32_t ns = s_ns[i], nb = s_nb[i], pns = pad2(ns);
+            for (uint32_t j = tid % kSlice; j < ns + nb; j += kSlice) {
+                const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
+                ck_store_value<G>(K, V, g, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y);
             }
         }
         __syncthreads();
         const uint32_t bad = s_bad;   // rows whose table could not be built sit this join out
-        const uint32_t wide = s_wide;
         // One warp per participant j: its terms pass through registers 64 at a time (the two slot indices of each
         // computed once -- every table uses the same hashes) and are probed against the key lines of the group.
         for (uint32_t j = warp; j < rows; j += kJoinThreads / 32) {
@@ -630,13 +622,22 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
             }
         }
         __syncthreads();
-        // empty the tables again: every thread wipes the slots of its own terms, unless a row was too long for that
-        if (wide || bad) { for (uint32_t q = tid; q < tabn * G; q += kJoinThreads) { K[q] = kEmpty; V[q] = 0u; } }
+        // empty the tables again: every term wipes the slots that hold its key
+        if (bad) { for (uint32_t q = tid; q < tabn * G; q += kJoinThreads) { K[q] = kEmpty; V[q] = 0u; } }
         else {
-#pragma unroll
-            for (int g = 0; g < G; ++g) if (my_slot[g] != kEmpty) { K[my_slot[g] * G + g] = kEmpty; V[my_slot[g] * G + g] = 0u; }
+            for (uint32_t g = tid / kSlice; g < g_cnt; g += 4) {
+                const uint32_t i = i0 + g;
+                const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[i]);
+                const uint32_t ns = s_ns[i], nb = s_nb[i], pns = pad2(ns);
+                for (uint32_t j = tid % kSlice; j < ns + nb; j += kSlice) {
+                    const uint32_t id = j < ns ? pr[j].x : (pr[pns + (j - ns)].x | 0x80000000u);
+                    const uint32_t h1 = ck_h1(id, a.tab_shift), h2 = ck_h2(id, a.tab_shift);
+                    if (K[h1 * G + g] == id) { K[h1 * G + g] = kEmpty; V[h1 * G + g] = 0u; }
+                    if (K[h2 * G + g] == id) { K[h2 * G + g] = kEmpty; V[h2 * G + g] = 0u; }
+                }
+            }
         }
-        if (tid == 0) { s_bad = 0; s_wide = 0; }
+        if (tid == 0) s_bad = 0;
         __syncthreads();
     }
 
@@ -651,7 +652,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
         for (int h = 0; h < 2; ++h) {
             const uint32_t j = lane + 32 * h;
             c[h] = ~0ull;
-            if (j < lim && j != p && pair_owned(a.own_mode, me, s_id[j])) {
+            if (j < lim && j != p && pair_owned(a.shared_pairs, me, s_id[j])) {
                 const float d = dm[min(p, j) * kPart + max(p, j)];
                 if (d < kth) c[h] = ((unsigned long long)f2ord(d) << 32) | j;
             }
@@ -1613,7 +1614,7 @@ int join_dense_tc_launch(ap_index *ix, uint32_t node0, uint32_t nodes, const uin
                          cudaStream_t stream);  // apoe_join_tc.cu
 
 // Term-seeded first lists (see seed_cand_kernel).  Skipped when the corpus has no BM25 terms or more than 2^31 - 1.
-static int seed_run(ap_index *ix, const Knn &k, uint32_t take, uint32_t own_mode, uint32_t *launches) {
+static int seed_run(ap_index *ix, const Knn &k, uint32_t take, uint32_t shared_pairs, uint32_t *launches) {
     const uint32_t n = ix->n;
     DevBuf db;
     uint32_t *cnt, *off, *cand;
@@ -1640,7 +1641,7 @@ static int seed_run(ap_index *ix, const Knn &k, uint32_t take, uint32_t own_mode
     if (smem > ix->smem_per_block) return AP_OK;   // rows too long for per-warp tables: random start only
     AP_CUDA(cudaFuncSetAttribute(seed_dist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
-    seed_dist_kernel<<<(n + kSeedWarps - 1) / kSeedWarps, kSeedWarps * 32, smem>>>(k, ix->meta, ix->rec_build, cand, tabn - 1, 32 - log2u(tabn), own_mode);
+    seed_dist_kernel<<<(n + kSeedWarps - 1) / kSeedWarps, kSeedWarps * 32, smem>>>(k, ix->meta, ix->rec_build, cand, tabn - 1, 32 - log2u(tabn), shared_pairs);
     knn_merge_kernel<<<(n + 3) / 4, 128>>>(k);
     AP_CUDA(cudaGetLastError());
     AP_CUDA(cudaDeviceSynchronize());
@@ -1651,7 +1652,7 @@ static int seed_run(ap_index *ix, const Knn &k, uint32_t take, uint32_t own_mode
 int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats) {
     ap_build_opts o{};
     if (opts_in) o = *opts_in;
-    const uint32_t iters = o.iterations ? o.iterations : 12;
+    const uint32_t iters = o.iterations ? o.iterations : 8;
     const float scale = o.dense_scale != 0.f ? o.dense_scale : 7.0f;
     const uint32_t n = ix->n;
     if (n < 2) return fail(AP_ERR_ARG, "a graph needs at least 2 documents");
@@ -1672,8 +1673,8 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     uint32_t launches = 0;
     AP_TRY(norms_run(ix, power)); ++launches;
     knn_init_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k, o.seed ? o.seed : 20261125u); ++launches;
-    const uint32_t own_mode = (o.reserved[1] >> 3) & 7u;
-    if (!(o.reserved[1] & 2u)) AP_TRY(seed_run(ix, k, o.reserved[2] ? std::min<uint32_t>(o.reserved[2], 32u) : 8u, own_mode, &launches));   // term-seeded start unless switched off
+    const uint32_t shared_pairs = (o.flags & AP_BUILD_SHARED_PAIRS) ? 1u : 0u;
+    if (!(o.flags & AP_BUILD_RANDOM_START)) AP_TRY(seed_run(ix, k, o.seed_take ? std::min<uint32_t>(o.seed_take, 32u) : 4u, shared_pairs, &launches));
 
     // scratch for the dense tiles, in batches of nodes
     const uint32_t batch = std::min<uint32_t>(n, 1u << 18);
@@ -1684,8 +1685,8 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     JoinArgs ja{};
     ja.plist = k.plist; ja.pcnt = k.pcnt; ja.meta = ix->meta; ja.rec = ix->rec_build; ja.D = D; ja.knn_dis = k.dis;
     ja.prop = k.prop; ja.propn = k.propn; ja.stats = k.stats; ja.err = err;
-    ja.prop_per = std::min<uint32_t>(kPropPerMax, o.reserved[0] ? o.reserved[0] : 4);
-    ja.own_mode = own_mode;
+    ja.prop_per = std::min<uint32_t>(kPropPerMax, o.proposals ? o.proposals : 4);
+    ja.shared_pairs = shared_pairs;
     const uint32_t tabn = pow2_at_least(2 * (ix->max_ns + ix->max_nb), 64);
     ja.tab_mask = tabn - 1; ja.tab_shift = 32 - log2u(tabn);
     // two CTAs per SM: tables for up to 4 hashed rows, the 32 x 64 distance tile, the rest is arena
@@ -1708,7 +1709,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     float phase_ms[4] = {0, 0, 0, 0};  // sample + lists, dense tiles, sparse + proposals, merge
     uint32_t it = 0;
     unsigned long long prev_updates = 0;
-    for (; it < iters && !(o.reserved[1] & 4u); ++it) {
+    for (; it < iters; ++it) {
         AP_CUDA(cudaMemsetAsync(k.scnt, 0, (size_t)n * 16));
         AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
         AP_CUDA(cudaEventRecord(ev[0]));
@@ -1736,7 +1737,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
         prev_updates = st[1];
         if (it >= 3 && upd < (unsigned long long)n * kK / 1000) { ++it; break; }  // < 0.1 % of the entries changed
     }
-    if (!(o.reserved[1] & 1u) && own_mode == 0) {   // reverse pass unless switched off
+    if (shared_pairs && (o.flags & AP_BUILD_REVERSE_PASS)) {
         AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
         knn_reverse_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k);
         knn_merge_kernel<<<(n + 3) / 4, 128>>>(k);
@@ -1764,9 +1765,9 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
         stats->seconds_prune = std::chrono::duration<double>(t2 - t1).count();
         stats->seconds_total = std::chrono::duration<double>(t2 - t0).count();
         stats->distance_evals = st[0]; stats->list_updates = st[1]; stats->iterations_run = it; stats->launches = launches;
-        stats->reserved[0] = (uint32_t)st[2];
+        stats->proposal_overflows = (uint32_t)st[2];
         // phase times in 10 us units: sample + lists, dense tiles (first batch), sparse + proposals, merge
-        for (int ph = 0; ph < 3; ++ph) stats->reserved[1 + ph] = (uint32_t)(phase_ms[ph == 0 ? 1 : (ph == 1 ? 2 : 3)] * 100.f);
+        for (int ph = 0; ph < 3; ++ph) stats->phase_10us[ph] = (uint32_t)(phase_ms[ph + 1] * 100.f);
     }
     if (!(o.flags & AP_BUILD_KEEP_KNN)) {
         cudaFree(ix->knn_ids); cudaFree(ix->knn_dis); ix->knn_ids = nullptr; ix->knn_dis = nullptr;

@@ -49,26 +49,37 @@ typedef struct {
 #define AP_CREATE_FOR_BUILD 1u /* also keep the build-time copy (dense x dense_scale) until the graph is built */
 
 /* ---- build ---------------------------------------------------------- */
-#define AP_BUILD_SIMT_JOIN 1u   /* local join on CUDA cores instead of tcgen05 (debug / cross-check) */
-#define AP_BUILD_KEEP_KNN 2u    /* keep the pre-pruning k-NN lists readable through ap_index_get_knn */
+#define AP_BUILD_SIMT_JOIN 1u     /* local join on CUDA cores instead of tcgen05 (debug / cross-check) */
+#define AP_BUILD_KEEP_KNN 2u      /* keep the pre-pruning k-NN lists readable through ap_index_get_knn */
+#define AP_BUILD_RANDOM_START 4u  /* random initial lists only, as the reference (src/index.cu:99-106); default: the lists
+                                     are first seeded from the posting lists of each document's rarest BM25 terms */
+#define AP_BUILD_SHARED_PAIRS 8u  /* offer every evaluated pair to both of its ends (classic NN-Descent).  Default: each
+                                     pair belongs to one end (hash of the two ids), so the forward half of a final row
+                                     and its reverse-edge half (src/index.cu:699-711) carry different neighbours */
+#define AP_BUILD_REVERSE_PASS 16u /* with AP_BUILD_SHARED_PAIRS: closing reverse merge as merge_reverse_plus
+                                     (src/index.cu:386-478) */
 
 typedef struct {
-    uint32_t iterations;   /* NN-Descent rounds; 0 = library default */
+    uint32_t iterations;   /* NN-Descent rounds; 0 = library default (8) */
     uint32_t seed;         /* random initial graph; the reference seeds from clock() (src/index.cu:102) */
     uint32_t flags;        /* AP_BUILD_* */
     float dense_scale;     /* build-time dense weight; 0 = 7.0 as in src/index.cu:836-840 */
-    uint32_t reserved[4];
+    uint32_t proposals;    /* closest partners each participant of a local join keeps; 0 = 4, at most 8 */
+    uint32_t seed_take;    /* followers taken from each posting list by the seeded start; 0 = 4, at most 32 */
+    uint32_t reserved[2];
 } ap_build_opts;
 
 typedef struct {
     double seconds_total;      /* same span as the reference's "Indexing time" (src/index.cu:889-910) */
-    double seconds_knn;        /* NN-Descent part */
+    double seconds_knn;        /* seeded start + NN-Descent part */
     double seconds_prune;      /* detour count + RNG-IP prune + row assembly */
-    uint64_t distance_evals;   /* hybrid distances evaluated by the local joins */
+    uint64_t distance_evals;   /* hybrid distances evaluated by the seeded start and the local joins */
     uint64_t list_updates;     /* k-NN list entries replaced */
     uint32_t iterations_run;
     uint32_t launches;         /* kernels launched */
-    uint32_t reserved[4];
+    uint32_t proposal_overflows; /* proposals dropped because a document's inbox (192 per round) was full */
+    uint32_t phase_10us[3];    /* summed over rounds, in 10 us: dense tiles of the first node batch, the remaining
+                                  join work (sparse / BM25 parts, proposals), list merge */
 } ap_build_stats;
 
 /* ---- search --------------------------------------------------------- */

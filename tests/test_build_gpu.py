@@ -114,16 +114,29 @@ def test_dense_join_tensor_core_matches_simt(tiny, bix):
         assert np.allclose(got[v, :rows, :nn], ref[v, :rows, :nn], rtol=1e-5, atol=2e-4), v
 
 
-@pytest.mark.parametrize("simt", [True, False])
-def test_build_quality(simt):
-    """NN-Descent + pruning on 6 000 documents: k-NN recall against exact lists, search recall against brute force."""
+@pytest.mark.parametrize("simt,shared", [(True, False), (False, False), (False, True)])
+def test_build_quality(simt, shared):
+    """Seeded start + NN-Descent + pruning on 6 000 documents: k-NN recall against exact lists, search recall against
+    brute force.  With owned pairs (the default) a true neighbour sits in the list of the end that owns the pair, so
+    recall counts a document's own list together with the lists that hold it."""
     ds = helpers.make_dataset(6000, 100, seed=21, with_graph=False)
     ix = apoe.Index.from_host(ds.D, ds.S, ds.B, for_build=True)
-    st = ix.build(flags=apoe.BUILD_KEEP_KNN | (apoe.BUILD_SIMT_JOIN if simt else 0), seed=3)
+    flags = apoe.BUILD_KEEP_KNN | (apoe.BUILD_SIMT_JOIN if simt else 0) | (apoe.BUILD_SHARED_PAIRS if shared else 0)
+    st = ix.build(flags=flags, seed=3)
     ids, dis, power = ix.get_knn()
     assert np.all(np.diff(dis, axis=1) >= 0)
     knn, _ = helpers.exact_knn(ds.D, ds.S, ds.B)
-    rec = np.mean([len(set(ids[i, :32].tolist()) & set(knn[i, :32].tolist())) / 32 for i in range(0, ds.n, 7)])
+    near = [set(r.tolist()) for r in ids]
+    if not shared:
+        for u in range(ds.n):
+            for v in ids[u]:
+                assert u not in near[int(v)] or int(v) == u, "a pair sits in the lists of both of its ends"
+        holders = [set() for _ in range(ds.n)]
+        for u in range(ds.n):
+            for v in ids[u]:
+                holders[int(v)].add(u)
+        near = [near[i] | holders[i] for i in range(ds.n)]
+    rec = np.mean([len(near[i] & set(knn[i, :32].tolist())) / 32 for i in range(0, ds.n, 7)])
     assert rec >= 0.80, rec
     want_power = orc.cal_power(ds.D7h, ds.S, ds.B)
     assert np.array_equal(power.view(np.uint32), want_power.view(np.uint32))
