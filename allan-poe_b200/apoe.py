@@ -42,6 +42,12 @@ class BuildStats(C.Structure):
                 ("launches", C.c_uint32), ("proposal_overflows", C.c_uint32), ("phase_10us", C.c_uint32 * 3)]
 
 
+class IngestStats(C.Structure):
+    _fields_ = [("seconds_total", C.c_double), ("seconds_open", C.c_double), ("bytes_read", C.c_uint64),
+                ("rows", C.c_uint32), ("threads", C.c_uint32), ("nnz_sparse", C.c_uint32), ("nnz_bm25", C.c_uint32),
+                ("reserved", C.c_uint32 * 2)]
+
+
 class SearchOpts(C.Structure):
     _fields_ = [("cands", C.c_uint32), ("flags", C.c_uint32), ("sparse_weight", C.c_float), ("bm25_weight", C.c_float),
                 ("dense_weight", C.c_float), ("kg_weight", C.c_float), ("arena_bytes", C.c_uint32),
@@ -123,6 +129,17 @@ class Index:
                                           _Csr(*map(_ptr, s)), _Csr(*map(_ptr, b)),
                                           C.c_uint32(CREATE_FOR_BUILD if for_build else 0)))
         return cls(h, dense.shape[0], device)
+
+    @classmethod
+    def from_files(cls, dense_path: str, sparse_path: str, bm25_path: str, device: int = 0, for_build: bool = False,
+                   threads: int = 0):
+        """Streams the reference's corpus files into a resident index.  Returns (index, IngestStats)."""
+        h = C.c_void_p()
+        st = IngestStats()
+        _check(lib().ap_index_create_files(C.byref(h), C.c_int(device), dense_path.encode(), sparse_path.encode(),
+                                           bm25_path.encode(), C.c_uint32(CREATE_FOR_BUILD if for_build else 0),
+                                           C.c_uint32(threads), C.byref(st)))
+        return cls(h, int(st.rows), device), st
 
     @classmethod
     def from_device(cls, dense, sparse, bm25, for_build: bool = False) -> "Index":

@@ -7,6 +7,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <functional>
 #include <string>
 #include <vector>
 
@@ -119,8 +120,16 @@ namespace apoe {
 
 // ---- internal entry points shared between translation units ------------------------------------
 int index_alloc(ap_index **out, int device, uint32_t n);
+// Source of the corpus arrays for index_pack when they are not in memory yet.  read(dst, which, offset, bytes) writes
+// bytes [offset, offset + bytes) of array `which` to dst (pinned or ordinary host memory) and may use threads of its
+// own.  which: 0 dense rows in .fvecs layout (u32 1024, then 1024 floats per row; offset counted from the first row),
+// 1 sparse ids, 2 sparse values, 3 BM25 ids, 4 BM25 values.
+struct CorpusFeed {
+    std::function<int(void *dst, int which, size_t offset, size_t bytes)> read;
+};
 int index_pack(ap_index *ix, const float *dense, const uint32_t *s_off, const uint32_t *s_idx, const float *s_val,
-               const uint32_t *b_off, const uint32_t *b_idx, const float *b_val, bool on_device, uint32_t flags);
+               const uint32_t *b_off, const uint32_t *b_idx, const float *b_val, bool on_device, uint32_t flags,
+               const CorpusFeed *feed = nullptr);
 int index_install_graph(ap_index *ix);  // graph + ep on device -> fat rows
 int ws_reserve(ap_index *ix, int slot, size_t bytes, void **out);
 

@@ -1,6 +1,11 @@
 // File-level drop-ins: the loaders and writers of the reference's on-disk formats and the two calls behind
 // hybrid_search.build_index / hybrid_search.search_index, implemented over the resident-index C ABI.
+#include <fcntl.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
 #include <algorithm>
+#include <atomic>
 #include <chrono>
 #include <cmath>
 #include <cstdio>
@@ -9,13 +14,11 @@
 #include <iostream>
 #include <sstream>
 #include <string>
+#include <thread>
 #include <vector>
 
-#include "../../include/allan_poe.h"
+#include "apoe_common.cuh"
 
-namespace apoe {
-int fail(int code, const char *fmt, ...);
-}
 using apoe::fail;
 
 namespace {
@@ -107,9 +110,116 @@ int load_id_lines(const char *path, uint32_t rows, std::vector<std::vector<uint3
     return AP_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------------
+// Streamed ingest.  The reference reads the corpus with one thread, one small read per row, into pageable
+// memory (include/utils.cuh:361-398) and uploads afterwards (src/index.cu:845-887).  Here the three files stay
+// open, byte ranges are fetched by several threads with pread() straight into pinned staging buffers, and the
+// upload and packing of one buffer run while the next one is being filled.
+// ---------------------------------------------------------------------------------------------------------
+struct CorpusFiles {
+    int fd[3] = {-1, -1, -1};          // dense, sparse, bm25
+    std::string path[3];
+    size_t size[3] = {0, 0, 0};
+    uint32_t n = 0, nnz[3] = {0, 0, 0};
+    std::vector<uint32_t> off[3];      // [1], [2]: row offsets of the two CSR files
+    uint32_t threads = 8;
+    std::atomic<unsigned long long> bytes_read{0};
+    ~CorpusFiles() { for (int f : fd) if (f >= 0) close(f); }
+
+    // bytes [offset, offset + bytes) of file f into dst, split over the reader threads
+    int read_range(int f, void *dst, size_t offset, size_t bytes) {
+        if (offset + bytes > size[f]) return fail(AP_ERR_IO, "%s: read of %zu bytes at %zu runs past the end (%zu bytes)", path[f].c_str(), bytes, offset, size[f]);
+        const size_t min_slice = (size_t)4 << 20;
+        const uint32_t parts = (uint32_t)std::max<size_t>(1, std::min<size_t>(threads, (bytes + min_slice - 1) / min_slice));
+        std::atomic<int> err{0};
+        auto work = [&](uint32_t p) {
+            size_t a = bytes * p / parts, b = bytes * (p + 1) / parts;
+            while (a < b) {
+                const ssize_t got = pread(fd[f], (char *)dst + a, b - a, (off_t)(offset + a));
+                if (got <= 0) { err = 1; return; }
+                a += (size_t)got;
+            }
+        };
+        if (parts == 1) work(0);
+        else {
+            std::vector<std::thread> pool;
+            for (uint32_t p = 1; p < parts; ++p) pool.emplace_back(work, p);
+            work(0);
+            for (auto &t : pool) t.join();
+        }
+        if (err) return fail(AP_ERR_IO, "%s: read failed or file truncated", path[f].c_str());
+        bytes_read += bytes;
+        return AP_OK;
+    }
+
+    int open_all(const char *dense_path, const char *sparse_path, const char *bm25_path) {
+        const char *p[3] = {dense_path, sparse_path, bm25_path};
+        for (int f = 0; f < 3; ++f) {
+            path[f] = p[f];
+            fd[f] = open(p[f], O_RDONLY);
+            struct stat sb;
+            if (fd[f] < 0 || fstat(fd[f], &sb) != 0) return fail(AP_ERR_IO, "cannot open %s", p[f]);
+            size[f] = (size_t)sb.st_size;
+        }
+        // ref: load_data, include/utils.cuh:361-378 -- every row is (int32 dim, dim floats); the row count is the file size
+        uint32_t dim = 0;
+        if (size[0] < 4 || pread(fd[0], &dim, 4, 0) != 4 || dim != AP_DIM) return fail(AP_ERR_IO, "%s: dimension %u, this index is built for %d", p[0], dim, AP_DIM);
+        const size_t rows = size[0] / ((size_t)(AP_DIM + 1) * 4);
+        if (rows == 0 || rows > 0x7FFFFFFFull) return fail(AP_ERR_IO, "%s: %zu rows", p[0], rows);
+        n = (uint32_t)rows;
+        // ref: load_sparse_data, include/utils.cuh:380-398 -- u32 nnz | u32 off[rows+1] | u32 idx[nnz] | f32 val[nnz]
+        for (int f = 1; f < 3; ++f) {
+            if (size[f] < 4 || pread(fd[f], &nnz[f], 4, 0) != 4) return fail(AP_ERR_IO, "%s: no header", p[f]);
+            const size_t need = 4 + (size_t)(n + 1) * 4 + (size_t)nnz[f] * 8;
+            if (size[f] < need) return fail(AP_ERR_IO, "%s: %zu bytes, %zu needed for %u rows and %u entries", p[f], size[f], need, n, nnz[f]);
+            off[f].resize((size_t)n + 1);
+            int rc = read_range(f, off[f].data(), 4, (size_t)(n + 1) * 4);
+            if (rc != AP_OK) return rc;
+            if (off[f][n] != nnz[f]) return fail(AP_ERR_IO, "%s: last offset %u differs from the entry count %u", p[f], off[f][n], nnz[f]);
+        }
+        return AP_OK;
+    }
+
+    // the reader index_pack asks for its arrays (see apoe::CorpusFeed)
+    int feed_read(void *dst, int which, size_t offset, size_t bytes) {
+        if (which == 0) return read_range(0, dst, offset, bytes);
+        const int f = which <= 2 ? 1 : 2;
+        const size_t base = 4 + (size_t)(n + 1) * 4 + ((which == 2 || which == 4) ? (size_t)nnz[f] * 4 : 0);
+        return read_range(f, dst, base + offset, bytes);
+    }
+};
+
 }  // namespace
 
 extern "C" {
+
+int ap_index_create_files(ap_index **out, int device, const char *dense_path, const char *sparse_path, const char *bm25_path,
+                          uint32_t flags, uint32_t threads, ap_ingest_stats *stats) {
+    if (!out || !dense_path || !sparse_path || !bm25_path) return fail(AP_ERR_ARG, "null argument");
+    const auto t0 = std::chrono::high_resolution_clock::now();
+    CorpusFiles cf;
+    cf.threads = threads ? std::min(threads, 64u) : std::min(16u, std::max(1u, std::thread::hardware_concurrency()));
+    int rc = cf.open_all(dense_path, sparse_path, bm25_path);
+    if (rc != AP_OK) return rc;
+    const auto t1 = std::chrono::high_resolution_clock::now();
+    rc = apoe::index_alloc(out, device, cf.n);
+    if (rc == AP_OK) {
+        apoe::CorpusFeed feed{[&cf](void *dst, int which, size_t offset, size_t bytes) { return cf.feed_read(dst, which, offset, bytes); }};
+        rc = apoe::index_pack(*out, nullptr, cf.off[1].data(), nullptr, nullptr, cf.off[2].data(), nullptr, nullptr, false, flags, &feed);
+    }
+    if (rc != AP_OK) { if (*out) ap_index_destroy(*out); *out = nullptr; return rc; }
+    const auto t2 = std::chrono::high_resolution_clock::now();
+    if (stats) {
+        memset(stats, 0, sizeof *stats);
+        stats->seconds_open = std::chrono::duration<double>(t1 - t0).count();
+        stats->seconds_total = std::chrono::duration<double>(t2 - t0).count();
+        stats->bytes_read = cf.bytes_read.load();
+        stats->rows = cf.n; stats->threads = cf.threads;
+        stats->nnz_sparse = cf.nnz[1]; stats->nnz_bm25 = cf.nnz[2];
+    }
+    return AP_OK;
+}
+
 
 // ref: cal_precision, src/query.cu:111-145
 double ap_ndcg(uint32_t nq, const uint32_t *results, uint32_t stride, uint32_t top_k, const uint32_t *qrel_off,
@@ -180,20 +290,14 @@ int ap_index_save_graph(const ap_index *ix, const char *path) {
 int ap_build_index(const char *dense_data_path, const char *sparse_data_path, const char *bm25_data_path,
                    const char *output_graph_path, int device, const ap_build_opts *opts, ap_build_stats *stats) {
     if (!dense_data_path || !sparse_data_path || !bm25_data_path || !output_graph_path) return fail(AP_ERR_ARG, "null path");
-    std::vector<float> dense; uint32_t n = 0;
-    CsrHost sp, bm;
     std::cout << "Loading dense data from " << dense_data_path << std::endl;
-    int rc = load_fvecs(dense_data_path, dense, &n);
-    if (rc == AP_OK) rc = load_csr(sparse_data_path, n, sp);
-    if (rc == AP_OK) rc = load_csr(bm25_data_path, n, bm);
-    if (rc != AP_OK) return rc;
-    std::cout << "Points: " << n << ", Dim: " << AP_DIM << std::endl;
-    uint32_t ms = 0, mb = 0;
-    for (uint32_t i = 0; i < n; ++i) { ms = std::max(ms, sp.off[i + 1] - sp.off[i]); mb = std::max(mb, bm.off[i + 1] - bm.off[i]); }
-    std::cout << "Max sparse dim: " << ms << ", Max bm25 dim: " << mb << std::endl;
     ap_index *ix = nullptr;
-    rc = ap_index_create_host(&ix, device, n, dense.data(), sp.view(), bm.view(), AP_CREATE_FOR_BUILD);
+    ap_ingest_stats ing{};
+    int rc = ap_index_create_files(&ix, device, dense_data_path, sparse_data_path, bm25_data_path, AP_CREATE_FOR_BUILD, 0, &ing);
     if (rc != AP_OK) return rc;
+    std::cout << "Non zero num: " << ing.nnz_sparse << std::endl << "Non zero num: " << ing.nnz_bm25 << std::endl;
+    std::cout << "Points: " << ix->n << ", Dim: " << AP_DIM << std::endl;
+    std::cout << "Max sparse dim: " << ix->max_ns << ", Max bm25 dim: " << ix->max_nb << std::endl;
     ap_build_stats st{};
     rc = ap_index_build(ix, opts, &st);
     if (rc == AP_OK) {
@@ -216,13 +320,15 @@ int ap_search_index(const char *dense_data_path, const char *dense_query_path, c
         !bm25_query_path || !graph_path)
         return fail(AP_ERR_ARG, "null path");
     if (top_k <= 0 || top_k > cands) return fail(AP_ERR_ARG, "top_k = %d must lie in [1, cands = %d]", top_k, cands);
-    std::vector<float> dense, qdense;
+    std::vector<float> qdense;
     uint32_t n = 0, nq_file = 0;
-    CsrHost sp, bm, qsp, qbm;
-    int rc = load_fvecs(dense_data_path, dense, &n);
-    if (rc == AP_OK) rc = load_fvecs(dense_query_path, qdense, &nq_file);
-    if (rc == AP_OK) rc = load_csr(sparse_data_path, n, sp);
-    if (rc == AP_OK) rc = load_csr(bm25_data_path, n, bm);
+    CsrHost qsp, qbm;
+    ap_index *ix = nullptr;
+    int rc = ap_index_create_files(&ix, device, dense_data_path, sparse_data_path, bm25_data_path, 0, 0, nullptr);
+    if (rc != AP_OK) return rc;
+    struct Guard { ap_index *&p; ~Guard() { if (p) { ap_index_destroy(p); p = nullptr; } } } guard{ix};
+    n = ix->n;
+    rc = load_fvecs(dense_query_path, qdense, &nq_file);
     if (rc == AP_OK) rc = load_csr(sparse_query_path, nq_file, qsp);
     if (rc == AP_OK) rc = load_csr(bm25_query_path, nq_file, qbm);
     if (rc != AP_OK) return rc;
@@ -254,9 +360,6 @@ int ap_search_index(const char *dense_data_path, const char *dense_query_path, c
     }
     std::cout << "Dense weight: " << dense_weight << ", Sparse weight: " << sparse_weight << ", BM25 weight: " << bm25_weight
               << ", KG weight: " << kg_weight << std::endl;
-    ap_index *ix = nullptr;
-    rc = ap_index_create_host(&ix, device, n, dense.data(), sp.view(), bm.view(), 0);
-    if (rc != AP_OK) return rc;
     rc = ap_index_load_graph(ix, graph_path);
     if (rc == AP_OK && use_kg) rc = ap_index_set_kg(ix, (uint32_t)e2e_off.size() - 1, e2e_off.data(), e2e_idx.data(), e2d_off.data(), e2d_idx.data());
     std::vector<uint32_t> ids((size_t)nq * cands);
@@ -299,7 +402,6 @@ int ap_search_index(const char *dense_data_path, const char *dense_query_path, c
             }
         }
     }
-    ap_index_destroy(ix);
     return rc;
 }
 

@@ -28,22 +28,31 @@ int fail(int code, const char *fmt, ...) {
 // ---------------------------------------------------------------------------------------------------------
 // One warp per document: dense fp32 -> (x scale) -> half, CSR rows -> interleaved (id, value) pairs.
 // ref for the conversions: src/index.cu:836-840 (x7 on fp32), include/utils.cuh:78-83 (__float2half).
-__global__ void pack_records_kernel(uint32_t row0, uint32_t rows, const float *__restrict__ dense /* rows x 1024 */,
+__global__ void pack_records_kernel(uint32_t row0, uint32_t rows, const float *__restrict__ dense /* rows x stride */,
                                     float scale, const uint32_t *__restrict__ s_off, const uint32_t *__restrict__ s_idx,
                                     const float *__restrict__ s_val, const uint32_t *__restrict__ b_off,
                                     const uint32_t *__restrict__ b_idx, const float *__restrict__ b_val,
-                                    const uint64_t *__restrict__ meta, uint8_t *__restrict__ rec, int write_sparse) {
+                                    const uint64_t *__restrict__ meta, uint8_t *__restrict__ rec, int write_sparse,
+                                    uint32_t stride = kDim, uint32_t *__restrict__ bad_header = nullptr) {
     const uint32_t w = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (w >= rows) return;
     const uint32_t d = row0 + w;
     const uint64_t m = meta[d];
     uint8_t *dst = rec + meta_off16(m) * 16ull;
-    const float4 *src = reinterpret_cast<const float4 *>(dense + (size_t)w * kDim);
     uint2 *dd = reinterpret_cast<uint2 *>(dst);
-    for (uint32_t i = lane; i < kDim / 4; i += 32) {
-        const float4 f = __ldg(src + i);
-        dd[i] = make_uint2(pack_half2(__fmul_rn(f.x, scale), __fmul_rn(f.y, scale)),
-                           pack_half2(__fmul_rn(f.z, scale), __fmul_rn(f.w, scale)));
+    if (stride == kDim) {
+        const float4 *src = reinterpret_cast<const float4 *>(dense + (size_t)w * kDim);
+        for (uint32_t i = lane; i < kDim / 4; i += 32) {
+            const float4 f = __ldg(src + i);
+            dd[i] = make_uint2(pack_half2(__fmul_rn(f.x, scale), __fmul_rn(f.y, scale)),
+                               pack_half2(__fmul_rn(f.z, scale), __fmul_rn(f.w, scale)));
+        }
+    } else {
+        // rows as they lie in an .fvecs file: one int32 dimension word, then the values (4-byte aligned only)
+        const float *src = dense + (size_t)w * stride;
+        if (lane == 0 && bad_header && __float_as_uint(src[0]) != kDim) atomicMin(bad_header, d);
+        __half *dh = reinterpret_cast<__half *>(dst);
+        for (uint32_t i = lane; i < kDim; i += 32) dh[i] = __float2half_rn(__fmul_rn(__ldg(src + 1 + i), scale));
     }
     if (!write_sparse) return;
     const uint32_t ns = meta_ns(m), nb = meta_nb(m);
@@ -132,10 +141,85 @@ int ws_reserve(ap_index *ix, int slot, size_t bytes, void **out) {
     return AP_OK;
 }
 
+// Two pinned host buffers (and, on request, two device buffers) used alternately, so that filling buffer c + 1 on
+// the host overlaps the upload (and packing) of buffer c on the stream.
+struct Staging {
+    void *pin[2] = {nullptr, nullptr}, *dev[2] = {nullptr, nullptr};
+    cudaEvent_t done[2] = {nullptr, nullptr};
+    cudaStream_t st = nullptr;
+    size_t bytes = 0;
+    uint32_t uses = 0;
+    int init(size_t b, bool with_dev) {
+        bytes = b;
+        AP_CUDA(cudaStreamCreateWithFlags(&st, cudaStreamNonBlocking));
+        for (int i = 0; i < 2; ++i) {
+            AP_CUDA(cudaMallocHost(&pin[i], bytes));
+            if (with_dev) AP_CUDA(cudaMalloc(&dev[i], bytes));
+            AP_CUDA(cudaEventCreateWithFlags(&done[i], cudaEventDisableTiming));
+        }
+        return AP_OK;
+    }
+    int acquire(int *b) {   // the buffer whose previous use (two turns ago) has left the stream
+        *b = (int)(uses & 1u);
+        if (uses >= 2) AP_CUDA(cudaEventSynchronize(done[*b]));
+        ++uses;
+        return AP_OK;
+    }
+    int release(int b) { AP_CUDA(cudaEventRecord(done[b], st)); return AP_OK; }
+    ~Staging() {
+        if (st) cudaStreamSynchronize(st);
+        for (int i = 0; i < 2; ++i) { if (pin[i]) cudaFreeHost(pin[i]); if (dev[i]) cudaFree(dev[i]); if (done[i]) cudaEventDestroy(done[i]); }
+        if (st) cudaStreamDestroy(st);
+    }
+};
+
+// One corpus array from the feed to device memory, through the staging buffers.
+static int stream_array(const CorpusFeed &feed, int which, size_t bytes, void *d_dst, Staging &sg) {
+    for (size_t o = 0; o < bytes; o += sg.bytes) {
+        const size_t len = std::min(sg.bytes, bytes - o);
+        int b;
+        AP_TRY(sg.acquire(&b));
+        AP_TRY(feed.read(sg.pin[b], which, o, len));
+        AP_CUDA(cudaMemcpyAsync((uint8_t *)d_dst + o, sg.pin[b], len, cudaMemcpyHostToDevice, sg.st));
+        AP_TRY(sg.release(b));
+    }
+    return AP_OK;
+}
+
+// Dense rows from the feed, in .fvecs layout (one dimension word, then 1024 floats per row), packed chunk by chunk.
+static int pack_from_feed(ap_index *ix, const CorpusFeed &feed, Staging &sg, bool for_build, const uint32_t *d_soff, const uint32_t *d_sidx,
+                          const float *d_sval, const uint32_t *d_boff, const uint32_t *d_bidx, const float *d_bval) {
+    const uint32_t n = ix->n, stride = kDim + 1;
+    const uint32_t chunk = (uint32_t)std::min<size_t>(n, sg.bytes / ((size_t)stride * 4));
+    uint32_t *bad = reinterpret_cast<uint32_t *>(ix->d_ctl + 2);
+    AP_CUDA(cudaMemsetAsync(bad, 0xFF, 4, sg.st));
+    for (uint32_t r0 = 0; r0 < n; r0 += chunk) {
+        const uint32_t rows = std::min(chunk, n - r0);
+        int b;
+        AP_TRY(sg.acquire(&b));
+        AP_TRY(feed.read(sg.pin[b], 0, (size_t)r0 * stride * 4, (size_t)rows * stride * 4));
+        AP_CUDA(cudaMemcpyAsync(sg.dev[b], sg.pin[b], (size_t)rows * stride * 4, cudaMemcpyHostToDevice, sg.st));
+        const uint32_t blocks = (rows + 7) / 8;
+        const float *src = (const float *)sg.dev[b];
+        pack_records_kernel<<<blocks, 256, 0, sg.st>>>(r0, rows, src, 1.0f, d_soff, d_sidx, d_sval, d_boff, d_bidx, d_bval, ix->meta, ix->rec, 1, stride, bad);
+        if (for_build)
+            pack_records_kernel<<<blocks, 256, 0, sg.st>>>(r0, rows, src, 7.0f, d_soff, d_sidx, d_sval, d_boff, d_bidx, d_bval, ix->meta, ix->rec_build, 1, stride, nullptr);
+        AP_CUDA(cudaGetLastError());
+        AP_TRY(sg.release(b));
+    }
+    AP_CUDA(cudaStreamSynchronize(sg.st));
+    uint32_t first_bad = 0xFFFFFFFFu;
+    AP_CUDA(cudaMemcpy(&first_bad, bad, 4, cudaMemcpyDeviceToHost));
+    AP_CUDA(cudaMemset(bad, 0, 4));
+    if (first_bad != 0xFFFFFFFFu) return fail(AP_ERR_IO, "dense row %u does not start with the dimension word %u", first_bad, kDim);
+    return AP_OK;
+}
+
 int index_pack(ap_index *ix, const float *dense, const uint32_t *s_off, const uint32_t *s_idx, const float *s_val,
-               const uint32_t *b_off, const uint32_t *b_idx, const float *b_val, bool on_device, uint32_t flags) {
+               const uint32_t *b_off, const uint32_t *b_idx, const float *b_val, bool on_device, uint32_t flags,
+               const CorpusFeed *feed) {
     const uint32_t n = ix->n;
-    if (!dense || !s_off || !b_off) return fail(AP_ERR_ARG, "null corpus pointer");
+    if ((!dense && !feed) || !s_off || !b_off) return fail(AP_ERR_ARG, "null corpus pointer");
     std::vector<uint32_t> hs(n + 1), hb(n + 1);
     if (on_device) {
         AP_CUDA(cudaMemcpy(hs.data(), s_off, (size_t)(n + 1) * 4, cudaMemcpyDeviceToHost));
@@ -146,7 +230,7 @@ int index_pack(ap_index *ix, const float *dense, const uint32_t *s_off, const ui
     }
     AP_TRY(validate_offsets(hs.data(), n, "sparse corpus", &ix->max_ns));
     AP_TRY(validate_offsets(hb.data(), n, "bm25 corpus", &ix->max_nb));
-    if ((hs[n] && (!s_idx || !s_val)) || (hb[n] && (!b_idx || !b_val))) return fail(AP_ERR_ARG, "null CSR pointer");
+    if (!feed && ((hs[n] && (!s_idx || !s_val)) || (hb[n] && (!b_idx || !b_val)))) return fail(AP_ERR_ARG, "null CSR pointer");
 
     std::vector<uint64_t> meta(n);
     uint64_t off16 = 0;
@@ -174,9 +258,17 @@ int index_pack(ap_index *ix, const float *dense, const uint32_t *s_off, const ui
     sm.s_idx.resize(sm.s_off[sm.n]); sm.s_val.resize(sm.s_off[sm.n]);
     sm.b_idx.resize(sm.b_off[sm.n]); sm.b_val.resize(sm.b_off[sm.n]);
     const cudaMemcpyKind k = on_device ? cudaMemcpyDeviceToHost : cudaMemcpyHostToHost;
-    AP_CUDA(cudaMemcpy(sm.dense.data(), dense, sm.dense.size() * 4, k));
-    if (!sm.s_idx.empty()) { AP_CUDA(cudaMemcpy(sm.s_idx.data(), s_idx, sm.s_idx.size() * 4, k)); AP_CUDA(cudaMemcpy(sm.s_val.data(), s_val, sm.s_val.size() * 4, k)); }
-    if (!sm.b_idx.empty()) { AP_CUDA(cudaMemcpy(sm.b_idx.data(), b_idx, sm.b_idx.size() * 4, k)); AP_CUDA(cudaMemcpy(sm.b_val.data(), b_val, sm.b_val.size() * 4, k)); }
+    if (feed) {
+        std::vector<float> rows((size_t)sm.n * (kDim + 1));
+        AP_TRY(feed->read(rows.data(), 0, 0, rows.size() * 4));
+        for (uint32_t i = 0; i < sm.n; ++i) memcpy(&sm.dense[(size_t)i * kDim], &rows[(size_t)i * (kDim + 1) + 1], (size_t)kDim * 4);
+        if (!sm.s_idx.empty()) { AP_TRY(feed->read(sm.s_idx.data(), 1, 0, sm.s_idx.size() * 4)); AP_TRY(feed->read(sm.s_val.data(), 2, 0, sm.s_val.size() * 4)); }
+        if (!sm.b_idx.empty()) { AP_TRY(feed->read(sm.b_idx.data(), 3, 0, sm.b_idx.size() * 4)); AP_TRY(feed->read(sm.b_val.data(), 4, 0, sm.b_val.size() * 4)); }
+    } else {
+        AP_CUDA(cudaMemcpy(sm.dense.data(), dense, sm.dense.size() * 4, k));
+        if (!sm.s_idx.empty()) { AP_CUDA(cudaMemcpy(sm.s_idx.data(), s_idx, sm.s_idx.size() * 4, k)); AP_CUDA(cudaMemcpy(sm.s_val.data(), s_val, sm.s_val.size() * 4, k)); }
+        if (!sm.b_idx.empty()) { AP_CUDA(cudaMemcpy(sm.b_idx.data(), b_idx, sm.b_idx.size() * 4, k)); AP_CUDA(cudaMemcpy(sm.b_val.data(), b_val, sm.b_val.size() * 4, k)); }
+    }
 
     // CSR arrays on the device
     const uint32_t *d_soff = s_off, *d_sidx = s_idx, *d_boff = b_off, *d_bidx = b_idx;
@@ -184,11 +276,12 @@ int index_pack(ap_index *ix, const float *dense, const uint32_t *s_off, const ui
     void *tmp[6] = {nullptr};
     auto up = [&](int slot, const void *src, size_t bytes, const void **dst) -> int {
         AP_CUDA(cudaMalloc(&tmp[slot], std::max<size_t>(bytes, 16)));
-        AP_CUDA(cudaMemcpy(tmp[slot], src, bytes, cudaMemcpyHostToDevice));
+        if (src) AP_CUDA(cudaMemcpy(tmp[slot], src, bytes, cudaMemcpyHostToDevice));
         *dst = tmp[slot];
         return AP_OK;
     };
     int rc = AP_OK;
+    Staging sg;
     if (!on_device) {
         rc = up(0, s_off, (size_t)(n + 1) * 4, (const void **)&d_soff);
         if (rc == AP_OK) rc = up(1, s_idx, (size_t)hs[n] * 4, (const void **)&d_sidx);
@@ -197,14 +290,22 @@ int index_pack(ap_index *ix, const float *dense, const uint32_t *s_off, const ui
         if (rc == AP_OK) rc = up(4, b_idx, (size_t)hb[n] * 4, (const void **)&d_bidx);
         if (rc == AP_OK) rc = up(5, b_val, (size_t)hb[n] * 4, (const void **)&d_bval);
     }
+    if (rc == AP_OK && feed) {   // the arrays the uploads above left empty come from the feed
+        rc = sg.init((size_t)16384 * (kDim + 1) * 4, true);
+        if (rc == AP_OK) rc = stream_array(*feed, 1, (size_t)hs[n] * 4, tmp[1], sg);
+        if (rc == AP_OK) rc = stream_array(*feed, 2, (size_t)hs[n] * 4, tmp[2], sg);
+        if (rc == AP_OK) rc = stream_array(*feed, 3, (size_t)hb[n] * 4, tmp[4], sg);
+        if (rc == AP_OK) rc = stream_array(*feed, 4, (size_t)hb[n] * 4, tmp[5], sg);
+        if (rc == AP_OK) rc = pack_from_feed(ix, *feed, sg, for_build, d_soff, d_sidx, d_sval, d_boff, d_bidx, d_bval);
+    }
     // dense: straight from device memory, or through a staging buffer in chunks of rows
     const uint32_t chunk = on_device ? n : std::min(n, 65536u);
     float *stage = nullptr;
-    if (rc == AP_OK && !on_device) {
+    if (rc == AP_OK && !on_device && !feed) {
         cudaError_t e = cudaMalloc(&stage, (size_t)chunk * kDim * 4);
         if (e != cudaSuccess) rc = fail(AP_ERR_CUDA, "cudaMalloc(staging) failed: %s", cudaGetErrorString(e));
     }
-    for (uint32_t r0 = 0; rc == AP_OK && r0 < n; r0 += chunk) {
+    for (uint32_t r0 = 0; rc == AP_OK && !feed && r0 < n; r0 += chunk) {
         const uint32_t rows = std::min(chunk, n - r0);
         const float *src = dense + (size_t)r0 * kDim;
         if (!on_device) {

@@ -47,6 +47,7 @@ def parse():
     ap.add_argument("--cpu-queries", type=int, default=256, help="queries of the bounded CPU brute-force sample")
     ap.add_argument("--ref-queries", type=int, default=2000, help="queries per step of the reference arm")
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--ingest-docs", type=int, default=200_000, help="documents of the file-ingest measurement (0 = skip it)")
     ap.add_argument("--curve", action="store_true", help="also sweep cands in {32,64,128,256} and the weight presets")
     return ap.parse_args()
 
@@ -135,6 +136,63 @@ def cpu_baseline(corpus_host, qsub, eff, threads_note=True):
     return ({"value": n / dt, "unit": "queries/s", "cores": thr, "kind": "port",
              "sample": f"exact OpenMP brute-force hybrid top-10 of {n} queries over {D.shape[0]} docs in {dt:.1f} s "
                        f"(term-major sparse postings, blocked dense dot products)"}, gt)
+
+
+def ingest_files(n_docs, dev):
+    """Writes a seeded synthetic corpus of n_docs documents in the reference's file formats to a temporary folder."""
+    import tempfile
+    import synth
+    d = tempfile.mkdtemp(prefix="apoe_ingest_")
+    c = synth.make_corpus(n_docs, seed=20261127, device=dev)
+    paths = [os.path.join(d, f) for f in ("dense.fvecs", "sparse.bin", "bm25.bin")]
+    synth.write_fvecs(paths[0], c.dense.cpu())
+    synth.write_csr(paths[1], c.sparse.to("cpu"))
+    synth.write_csr(paths[2], c.bm25.to("cpu"))
+    return d, paths
+
+
+def ingest_own(n_docs, dev):
+    """File ingest of this library: files (page cache) -> resident records, best of 3."""
+    import shutil
+    import apoe
+    d, paths = ingest_files(n_docs, dev)
+    try:
+        best = None
+        for _ in range(3):
+            ix, st = apoe.Index.from_files(*paths, device=dev.index or 0, for_build=True)
+            ix.close()
+            if best is None or st.seconds_total < best.seconds_total:
+                best = st
+        size = sum(os.path.getsize(p) for p in paths)
+        return {"docs": n_docs, "file_bytes": size, "seconds": round(best.seconds_total, 4), "gb_per_s": round(size / best.seconds_total / 1e9, 2),
+                "threads": int(best.threads), "what": "pread threads -> pinned staging -> H2D + pack, both record pools, files in page cache"}
+    finally:
+        shutil.rmtree(d, ignore_errors=True)
+
+
+def ingest_reference(n_docs, dev):
+    """The reference's loaders (one thread, one read per row) and uploads on the same files, best of 2."""
+    import shutil
+    import apoe_ref
+    d, paths = ingest_files(n_docs, dev)
+    try:
+        best = None
+        for _ in range(2):
+            sys.stdout.flush()
+            saved = os.dup(1)           # the reference's loaders print to stdout; this program's stdout is one JSON line
+            null = os.open(os.devnull, os.O_WRONLY)
+            os.dup2(null, 1)
+            try:
+                rows, t_load, t_all = apoe_ref.load_seconds(*paths)
+            finally:
+                os.dup2(saved, 1); os.close(saved); os.close(null)
+            if best is None or t_all < best[1]:
+                best = (t_load, t_all)
+        size = sum(os.path.getsize(p) for p in paths)
+        return {"docs": n_docs, "file_bytes": size, "seconds": round(best[1], 4), "seconds_load_only": round(best[0], 4),
+                "gb_per_s": round(size / best[1] / 1e9, 2), "threads": 1, "what": "load_data + load_sparse_data x2 + cudaMemcpy of every array, files in page cache"}
+    finally:
+        shutil.rmtree(d, ignore_errors=True)
 
 
 def algorithmic_bytes(st, nq, cands, qnnz):
@@ -292,6 +350,9 @@ def run_own(args):
         }
         if args.curve and not sharded:
             line["curve"] = curve(ix, queries, eff, mq, gt if cpu else None, dev, stream)
+        if world == 1 and args.ingest_docs > 0:
+            ix.close()   # the measurement wants the memory and the copy engines to itself
+            line["ingest"] = ingest_own(min(args.ingest_docs, n), dev)
     if world > 1:
         import torch.distributed as dist
         dist.barrier()
@@ -361,7 +422,9 @@ def run_reference(args):
         gt, _, _ = orc.bruteforce(D, S, B, qd[:m], orc.CsrNp(*sub(qs)), orc.CsrNp(*sub(qb)), 7, 10)
         recall = recall_at_10(ids[:m], gt[:m])
     qps = nq * args.steps / total
+    ingest = ingest_reference(min(args.ingest_docs, n), torch.device("cuda", local)) if args.ingest_docs > 0 else None
     print(json.dumps({
+        "ingest": ingest,
         "impl": "reference", "metric": "hybrid search QPS at recall@10>=0.95 (cands=128); index build sec per 1M docs",
         "value": round(qps, 1), "unit": "queries/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
         "ms_per_step": round(total / args.steps * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,

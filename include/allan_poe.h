@@ -156,6 +156,20 @@ int ap_search_index(const char *dense_data_path, const char *dense_query_path, c
 /* Corpus in host memory (ref: the uploads of src/query.cu:1901-1934). */
 int ap_index_create_host(ap_index **out, int device, uint32_t n, const float *dense, ap_csr sparse, ap_csr bm25,
                          uint32_t flags);
+/* Corpus straight from the reference's files (dense .fvecs, two CSR .bin): reader threads pread() byte ranges into
+ * pinned staging buffers while the previous buffer is uploaded and packed.  Replaces load_data + load_sparse_data
+ * (include/utils.cuh:361-398) followed by the uploads of src/index.cu:845-887 / src/query.cu:1901-1934.
+ * threads = 0 picks min(16, hardware threads). */
+typedef struct {
+    double seconds_total;   /* open + headers + offsets + streaming + packing, until the records are resident */
+    double seconds_open;    /* open, headers and row offsets */
+    uint64_t bytes_read;
+    uint32_t rows, threads;
+    uint32_t nnz_sparse, nnz_bm25;
+    uint32_t reserved[2];
+} ap_ingest_stats;
+int ap_index_create_files(ap_index **out, int device, const char *dense_path, const char *sparse_path,
+                          const char *bm25_path, uint32_t flags, uint32_t threads, ap_ingest_stats *stats);
 /* Corpus already in device memory of `device` (same layouts). */
 int ap_index_create_device(ap_index **out, int device, uint32_t n, const float *dense, ap_csr sparse, ap_csr bm25,
                            uint32_t flags);

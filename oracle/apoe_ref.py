@@ -75,3 +75,13 @@ def search(dense, s, b, qdense_scaled, qs, qb, graph, ep, cands, mode):
     if rc != 0:
         raise RuntimeError(f"ref_search failed with {rc}")
     return ids, dis, t_all.value, t_search.value
+
+
+def load_seconds(dense_path: str, sparse_path: str, bm25_path: str):
+    """The reference's corpus loaders and uploads on three files.  Returns (rows, load seconds, load + upload seconds)."""
+    rows = C.c_uint(0)
+    sec = (C.c_double * 2)()
+    rc = lib().ref_load(dense_path.encode(), sparse_path.encode(), bm25_path.encode(), C.byref(rows), sec)
+    if rc != 0:
+        raise RuntimeError(f"ref_load failed with {rc}")
+    return rows.value, sec[0], sec[1]

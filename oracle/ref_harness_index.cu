@@ -106,3 +106,34 @@ extern "C" int ref_build(unsigned points_num, const float *dense_unscaled, const
     cudaFree(data_power_dev);
     return err == cudaSuccess ? 0 : 3;
 }
+
+// The reference's corpus loaders (include/utils.cuh:361-398) followed by the uploads build_index_impl makes
+// (src/index.cu:845-887), timed: seconds[0] = the three loads, seconds[1] = loads + uploads.
+extern "C" int ref_load(const char *dense_path, const char *sparse_path, const char *bm25_path, unsigned *rows_out, double *seconds) {
+    auto t0 = std::chrono::high_resolution_clock::now();
+    float *data = nullptr, *sparse_val = nullptr, *bm25_val = nullptr;
+    unsigned *sparse_off = nullptr, *sparse_idx = nullptr, *bm25_off = nullptr, *bm25_idx = nullptr;
+    unsigned num = 0, dim = 0, nnz_s = 0, nnz_b = 0;
+    load_data(const_cast<char *>(dense_path), data, num, dim);
+    load_sparse_data(const_cast<char *>(sparse_path), sparse_off, sparse_idx, sparse_val, num + 1, nnz_s);
+    load_sparse_data(const_cast<char *>(bm25_path), bm25_off, bm25_idx, bm25_val, num + 1, nnz_b);
+    auto t1 = std::chrono::high_resolution_clock::now();
+    float *data_dev, *sv_dev, *bv_dev;
+    unsigned *so_dev, *si_dev, *bo_dev, *bi_dev;
+    cudaMalloc((void **)&data_dev, (size_t)num * dim * sizeof(float));
+    cudaMemcpy(data_dev, data, (size_t)num * dim * sizeof(float), cudaMemcpyHostToDevice);
+    cudaMalloc((void **)&so_dev, (size_t)(num + 1) * 4); cudaMemcpy(so_dev, sparse_off, (size_t)(num + 1) * 4, cudaMemcpyHostToDevice);
+    cudaMalloc((void **)&si_dev, (size_t)nnz_s * 4); cudaMemcpy(si_dev, sparse_idx, (size_t)nnz_s * 4, cudaMemcpyHostToDevice);
+    cudaMalloc((void **)&sv_dev, (size_t)nnz_s * 4); cudaMemcpy(sv_dev, sparse_val, (size_t)nnz_s * 4, cudaMemcpyHostToDevice);
+    cudaMalloc((void **)&bo_dev, (size_t)(num + 1) * 4); cudaMemcpy(bo_dev, bm25_off, (size_t)(num + 1) * 4, cudaMemcpyHostToDevice);
+    cudaMalloc((void **)&bi_dev, (size_t)nnz_b * 4); cudaMemcpy(bi_dev, bm25_idx, (size_t)nnz_b * 4, cudaMemcpyHostToDevice);
+    cudaMalloc((void **)&bv_dev, (size_t)nnz_b * 4); cudaMemcpy(bv_dev, bm25_val, (size_t)nnz_b * 4, cudaMemcpyHostToDevice);
+    cudaDeviceSynchronize();
+    auto t2 = std::chrono::high_resolution_clock::now();
+    const cudaError_t err = cudaGetLastError();
+    cudaFree(data_dev); cudaFree(so_dev); cudaFree(si_dev); cudaFree(sv_dev); cudaFree(bo_dev); cudaFree(bi_dev); cudaFree(bv_dev);
+    delete[] data; delete[] sparse_off; delete[] sparse_idx; delete[] sparse_val; delete[] bm25_off; delete[] bm25_idx; delete[] bm25_val;
+    if (rows_out) *rows_out = num;
+    if (seconds) { seconds[0] = std::chrono::duration<double>(t1 - t0).count(); seconds[1] = std::chrono::duration<double>(t2 - t0).count(); }
+    return err == cudaSuccess ? 0 : 3;
+}
