@@ -48,6 +48,15 @@ class IngestStats(C.Structure):
                 ("reserved", C.c_uint32 * 2)]
 
 
+class Bm25Opts(C.Structure):
+    _fields_ = [("k1", C.c_float), ("b", C.c_float), ("flags", C.c_uint32), ("reserved", C.c_uint32 * 5)]
+
+
+class PrepStats(C.Structure):
+    _fields_ = [("seconds", C.c_double), ("kernel_ms", C.c_float), ("avg_len", C.c_float), ("nnz", C.c_uint64),
+                ("rows_sorted", C.c_uint32), ("launches", C.c_uint32), ("reserved", C.c_uint32 * 2)]
+
+
 class SearchOpts(C.Structure):
     _fields_ = [("cands", C.c_uint32), ("flags", C.c_uint32), ("sparse_weight", C.c_float), ("bm25_weight", C.c_float),
                 ("dense_weight", C.c_float), ("kg_weight", C.c_float), ("arena_bytes", C.c_uint32),
@@ -112,6 +121,47 @@ def _csr_np(csr):
     off, idx, val = (csr.off, csr.idx, csr.val) if hasattr(csr, "off") else csr
     conv = lambda x: x.cpu().numpy() if hasattr(x, "cpu") else np.asarray(x)
     return _np(conv(off), np.uint32), _np(conv(idx), np.uint32), _np(conv(val), np.float32)
+
+
+PREP_RELABEL_BY_DF = 1
+
+
+def bm25_corpus(off, idx, tf, vocab: int, k1: float = 1.2, b: float = 0.75, relabel_by_df: bool = False, device: int = 0):
+    """BM25 weights of a corpus from raw term frequencies (host arrays).  Returns (idx, weight, df, idf, relabel, stats)."""
+    off, tf = _np(off, np.uint32), _np(tf, np.float32)
+    idx = _np(idx, np.uint32).copy()
+    rows = off.size - 1
+    w = np.empty(idx.size, dtype=np.float32)
+    df, idf = np.empty(vocab, dtype=np.uint32), np.empty(vocab, dtype=np.float32)
+    rl = np.empty(vocab, dtype=np.uint32) if relabel_by_df else None
+    o = Bm25Opts(k1=k1, b=b, flags=PREP_RELABEL_BY_DF if relabel_by_df else 0)
+    st = PrepStats()
+    _check(lib().ap_bm25_corpus_host(C.c_int(device), C.c_uint32(rows), C.c_uint32(vocab), _ptr(off), _ptr(idx), _ptr(tf), _ptr(w),
+                                     _ptr(df), _ptr(idf), _ptr(rl) if rl is not None else None, C.byref(o), C.byref(st)))
+    return idx, w, df, idf, rl, st
+
+
+def bm25_queries(off, idx, tf, idf, relabel=None, device: int = 0):
+    """BM25 query weights (idf x tf), ids renumbered with `relabel` and rows sorted.  Returns (idx, weight, stats)."""
+    off, tf, idf = _np(off, np.uint32), _np(tf, np.float32), _np(idf, np.float32)
+    idx = _np(idx, np.uint32).copy()
+    rl = _np(relabel, np.uint32) if relabel is not None else None
+    w = np.empty(idx.size, dtype=np.float32)
+    st = PrepStats()
+    _check(lib().ap_bm25_queries_host(C.c_int(device), C.c_uint32(off.size - 1), C.c_uint32(idf.size), _ptr(off), _ptr(idx), _ptr(tf),
+                                      _ptr(w), _ptr(idf), _ptr(rl) if rl is not None else None, C.byref(st)))
+    return idx, w, st
+
+
+def bm25_corpus_device(off_host, off, idx, tf, weight, df, idf, relabel=None, k1: float = 1.2, b: float = 0.75, stream=None):
+    """The same on CUDA tensors, in place (idx is renumbered / reordered, weight / df / idf / relabel are written)."""
+    off_host = _np(off_host, np.uint32)
+    o = Bm25Opts(k1=k1, b=b, flags=PREP_RELABEL_BY_DF if relabel is not None else 0)
+    st = PrepStats()
+    _check(lib().ap_bm25_corpus_device(C.c_int(idx.device.index or 0), C.c_uint32(off_host.size - 1), C.c_uint32(df.numel()), _ptr(off_host),
+                                       _ptr(off), _ptr(idx), _ptr(tf), _ptr(weight), _ptr(df), _ptr(idf),
+                                       _ptr(relabel) if relabel is not None else None, C.byref(o), C.c_void_p(stream or 0), C.byref(st)))
+    return st
 
 
 class Index:

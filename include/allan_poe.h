@@ -152,6 +152,43 @@ int ap_search_index(const char *dense_data_path, const char *dense_query_path, c
                     uint32_t max_queries, uint32_t *out_ids, float *out_dis, uint32_t *out_nq, double *out_ndcg,
                     ap_search_stats *stats);
 
+/* ---- input preparation ------------------------------------------------ */
+/* BM25 weights from raw term frequencies, on the device.  No counterpart in the reference, which expects pre-weighted
+ * rows with ascending term ids (README.md:73-77; its searches binary-search the rows, include/utils.cuh:299-340):
+ *   idf(t) = ln(1 + (N - df(t) + 0.5) / (df(t) + 0.5)),  w = idf * tf * (k1 + 1) / (tf + k1 * (1 - b + b * len / avglen)),
+ * len = sum of the row's tf; queries get w = idf * tf.  Rows come back sorted by term id; with AP_PREP_RELABEL_BY_DF the
+ * vocabulary is first renumbered by descending document frequency (ties by old id) and `relabel[old] = new` is
+ * returned, to be applied to the queries and to any other file that uses the same term ids. */
+#define AP_PREP_RELABEL_BY_DF 1u
+typedef struct {
+    float k1, b;        /* Okapi parameters; pass NULL options for 1.2 / 0.75 */
+    uint32_t flags;     /* AP_PREP_* */
+    uint32_t reserved[5];
+} ap_bm25_opts;
+typedef struct {
+    double seconds;       /* whole call, with the transfers of the host-pointer forms */
+    float kernel_ms;      /* device time of the kernels (CUDA events) */
+    float avg_len;
+    uint64_t nnz;
+    uint32_t rows_sorted; /* rows that were not ascending after the renumbering and went through the sort */
+    uint32_t launches;
+    uint32_t reserved[2];
+} ap_prep_stats;
+/* corpus, host pointers: idx is renumbered / reordered in place, weight[nnz], df[vocab], idf[vocab], relabel[vocab] out */
+int ap_bm25_corpus_host(int device, uint32_t rows, uint32_t vocab, const uint32_t *off, uint32_t *idx, const float *tf,
+                        float *weight, uint32_t *df, float *idf, uint32_t *relabel, const ap_bm25_opts *opts,
+                        ap_prep_stats *stats);
+/* queries, host pointers: idf (and relabel, may be NULL) as the corpus call returned them */
+int ap_bm25_queries_host(int device, uint32_t rows, uint32_t vocab, const uint32_t *off, uint32_t *idx, const float *tf,
+                         float *weight, const float *idf, const uint32_t *relabel, ap_prep_stats *stats);
+/* the same with every array in device memory (off_host: host copy of the offsets); `stream` is a cudaStream_t */
+int ap_bm25_corpus_device(int device, uint32_t rows, uint32_t vocab, const uint32_t *off_host, const uint32_t *off,
+                          uint32_t *idx, const float *tf, float *weight, uint32_t *df, float *idf, uint32_t *relabel,
+                          const ap_bm25_opts *opts, void *stream, ap_prep_stats *stats);
+int ap_bm25_queries_device(int device, uint32_t rows, uint32_t vocab, const uint32_t *off_host, const uint32_t *off,
+                           uint32_t *idx, const float *tf, float *weight, const float *idf, const uint32_t *relabel,
+                           void *stream, ap_prep_stats *stats);
+
 /* ---- resident index --------------------------------------------------- */
 /* Corpus in host memory (ref: the uploads of src/query.cu:1901-1934). */
 int ap_index_create_host(ap_index **out, int device, uint32_t n, const float *dense, ap_csr sparse, ap_csr bm25,

@@ -176,3 +176,42 @@ def prune(dense_h, sparse: CsrNp, bm25: CsrNp, knn, knn_dis, power, flags=0):
 
 def num_threads() -> int:
     return int(lib().orc_num_threads())
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Input preparation (BM25 weighting).  PARITY UNPINNED against the reference: it has no code for this step (it
+# expects pre-weighted rows, README.md:73-77); this restates the published Okapi BM25 formula in float32, step by
+# step in the order the device code uses, and is pinned only by the hand-computed case in tests/test_prep.py.
+# ---------------------------------------------------------------------------------------------------------
+def bm25_corpus(off, idx, tf, vocab, k1=1.2, b=0.75, relabel_by_df=False):
+    """Returns (idx_out, weight, df, idf, relabel): rows sorted by (renumbered) term id, float32 weights."""
+    off = np.asarray(off, dtype=np.int64); idx = np.asarray(idx, dtype=np.int64); tf = np.asarray(tf, dtype=np.float32)
+    rows = off.size - 1
+    f32 = np.float32
+    df = np.bincount(idx, minlength=vocab).astype(np.uint32)
+    d = df.astype(np.float32)
+    idf = np.log(f32(1.0) + (f32(rows) - d + f32(0.5)) / (d + f32(0.5))).astype(np.float32)
+    cnt = np.diff(off)
+    row_of = np.repeat(np.arange(rows), cnt)
+    length = np.zeros(rows, dtype=np.float64)
+    np.add.at(length, row_of, tf.astype(np.float64))
+    avglen = f32(length.sum() / rows)
+    norm = (f32(k1) * (f32(1.0) - f32(b) + f32(b) * length.astype(np.float32) / avglen)).astype(np.float32)
+    w = (idf[idx] * tf * (f32(k1) + f32(1.0)) / (tf + norm[row_of])).astype(np.float32)
+    relabel = None
+    new_idx = idx
+    if relabel_by_df:
+        order = np.lexsort((np.arange(vocab), -df.astype(np.int64)))   # descending df, ties by id
+        relabel = np.empty(vocab, dtype=np.uint32); relabel[order] = np.arange(vocab, dtype=np.uint32)
+        new_idx = relabel[idx].astype(np.int64)
+    perm = np.lexsort((new_idx, row_of))
+    return new_idx[perm].astype(np.uint32), w[perm], df, idf, relabel
+
+
+def bm25_queries(off, idx, tf, idf, relabel=None):
+    off = np.asarray(off, dtype=np.int64); idx = np.asarray(idx, dtype=np.int64); tf = np.asarray(tf, dtype=np.float32)
+    w = (np.asarray(idf, dtype=np.float32)[idx] * tf).astype(np.float32)
+    new_idx = np.asarray(relabel)[idx].astype(np.int64) if relabel is not None else idx
+    row_of = np.repeat(np.arange(off.size - 1), np.diff(off))
+    perm = np.lexsort((new_idx, row_of))
+    return new_idx[perm].astype(np.uint32), w[perm]
