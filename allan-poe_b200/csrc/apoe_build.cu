@@ -1709,6 +1709,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     float phase_ms[4] = {0, 0, 0, 0};  // sample + lists, dense tiles, sparse + proposals, merge
     uint32_t it = 0;
     unsigned long long prev_updates = 0;
+    const bool trace = getenv("APOE_BUILD_TRACE") != nullptr;   // per-round progress on stderr
     for (; it < iters; ++it) {
         AP_CUDA(cudaMemsetAsync(k.scnt, 0, (size_t)n * 16));
         AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
@@ -1735,6 +1736,8 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
         for (int ph = 0; ph < 4; ++ph) { float ms = 0.f; cudaEventElapsedTime(&ms, ev[ph], ev[ph + 1]); phase_ms[ph] += ms; }
         const unsigned long long upd = st[1] - prev_updates;
         prev_updates = st[1];
+        if (trace) fprintf(stderr, "round %u: %.2f %% of the list entries replaced, %llu distances so far, %llu proposals dropped\n", it,
+                           100.0 * (double)upd / ((double)n * kK), st[0], st[2]);
         if (it >= 3 && upd < (unsigned long long)n * kK / 1000) { ++it; break; }  // < 0.1 % of the entries changed
     }
     if (shared_pairs && (o.flags & AP_BUILD_REVERSE_PASS)) {
