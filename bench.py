@@ -458,9 +458,19 @@ def run_reference(args):
         gt, _, _ = orc.bruteforce(D, S, B, qd[:m], orc.CsrNp(*sub(qs)), orc.CsrNp(*sub(qb)), 7, 10)
         recall = recall_at_10(ids[:m], gt[:m])
     qps = nq * args.steps / total
+    ref_curve = None
+    if args.curve:   # the reference's kernels over its own graph at the other pool sizes (kernel-only time)
+        ref_curve = []
+        m = min(nq, args.cpu_queries)
+        gt_c = None if args.skip_cpu else orc.bruteforce(D, S, B, qd[:m], orc.CsrNp(*sub(qs)), orc.CsrNp(*sub(qb)), 7, 10)[0]
+        for cc in (32, 64, 128, 256):
+            for _ in range(2):
+                ids_c, _, t_all_c, t_search_c = apoe_ref.search(D, c3(S), c3(B), qd[:nq], sub(qs), sub(qb), graph, built["ep"], cc, 7)
+            ref_curve.append({"cands": cc, "qps_kernel_only": round(nq / t_search_c, 1), "qps": round(nq / t_all_c, 1),
+                              "recall_at_10": recall_at_10(ids_c[:m], gt_c[:m]) if gt_c is not None else None})
     ingest = ingest_reference(min(args.ingest_docs, n), torch.device("cuda", local)) if args.ingest_docs > 0 else None
     print(json.dumps({
-        "ingest": ingest,
+        "ingest": ingest, "curve": ref_curve,
         "impl": "reference", "metric": "hybrid search QPS at recall@10>=0.95 (cands=128); index build sec per 1M docs",
         "value": round(qps, 1), "unit": "queries/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
         "ms_per_step": round(total / args.steps * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
