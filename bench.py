@@ -385,6 +385,13 @@ def run_own(args):
         }
         if args.curve and not sharded:
             line["curve"] = curve(ix, queries, eff, mq, gt if cpu else None, dev, stream)
+        # single-query latency (kernel time by CUDA events, device-resident query), median of 30 different queries
+        lat = []
+        o1 = torch.empty(1, cands, dtype=torch.int32, device=dev); d1 = torch.empty(1, cands, dtype=torch.float32, device=dev)
+        for qi in range(min(30, nq)):
+            st1 = ix.search_device(queries.slice(qi, qi + 1), o1, d1, cands=cands, weights=eff, max_nnz=mq, stream=stream, stats=True)
+            lat.append(st1.kernel_ms)
+        line["latency_batch1_ms"] = round(float(np.median(lat)), 4)
         if world == 1 and args.ingest_docs > 0:
             ix.close()   # the measurement wants the memory and the copy engines to itself
             line["ingest"] = ingest_own(min(args.ingest_docs, n), dev)
@@ -468,9 +475,14 @@ def run_reference(args):
                 ids_c, _, t_all_c, t_search_c = apoe_ref.search(D, c3(S), c3(B), qd[:nq], sub(qs), sub(qb), graph, built["ep"], cc, 7)
             ref_curve.append({"cands": cc, "qps_kernel_only": round(nq / t_search_c, 1), "qps": round(nq / t_all_c, 1),
                               "recall_at_10": recall_at_10(ids_c[:m], gt_c[:m]) if gt_c is not None else None})
+    lat1 = []
+    one = lambda c, i: (c.off[i:i + 2] - c.off[i], c.idx[int(c.off[i]):int(c.off[i + 1])], c.val[int(c.off[i]):int(c.off[i + 1])])
+    for qi in range(min(10, nq)):
+        _, _, _, t1 = apoe_ref.search(D, c3(S), c3(B), qd[qi:qi + 1], one(qs, qi), one(qb, qi), graph, built["ep"], cands, 7)
+        lat1.append(t1 * 1e3)
     ingest = ingest_reference(min(args.ingest_docs, n), torch.device("cuda", local)) if args.ingest_docs > 0 else None
     print(json.dumps({
-        "ingest": ingest, "curve": ref_curve,
+        "ingest": ingest, "curve": ref_curve, "latency_batch1_ms": round(float(np.median(lat1)), 4),
         "impl": "reference", "metric": "hybrid search QPS at recall@10>=0.95 (cands=128); index build sec per 1M docs",
         "value": round(qps, 1), "unit": "queries/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
         "ms_per_step": round(total / args.steps * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
