@@ -1531,6 +1531,13 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
               uint32_t *d_kw, uint32_t *launches) {
     const uint32_t n = ix->n;
     if (n >= (1u << 27)) return fail(AP_ERR_LIMIT, "pruning supports up to 2^27 documents per index");
+    const bool trace = getenv("APOE_BUILD_TRACE") != nullptr;
+    const auto tr0 = std::chrono::high_resolution_clock::now();
+    auto mark = [&](const char *what) {
+        if (!trace) return;
+        cudaDeviceSynchronize();
+        fprintf(stderr, "prune: %.1f ms after %s\n", std::chrono::duration<double, std::milli>(std::chrono::high_resolution_clock::now() - tr0).count(), what);
+    };
     DevBuf db;
     uint32_t *detour, *nl = d_new_list, *kw = d_kw;
     AP_TRY(db.alloc(&detour, (size_t)n * AP_DEGREE));
@@ -1573,6 +1580,8 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
         pairs_kernel<<<n, kP2Threads, smem2>>>(q);
         AP_CUDA(cudaGetLastError());
         AP_CUDA(cudaMemcpy(&n_step, ovf_cnt, 4, cudaMemcpyDeviceToHost));
+        mark("the all-pairs kernel");
+        if (trace) fprintf(stderr, "prune: %u nodes left to the step-wise kernel\n", n_step);
         a.node_list = ovf_list;
         if (launches) ++*launches;
     }
@@ -1586,14 +1595,18 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
         if (ew) { cudaMemset(ix->d_ctl + 1, 0, 4); return fail(AP_ERR_DEVICE, "a pruning kernel raised error word %u (a bounded wait ran out)", ew); }
     }
 
+    mark("the step-wise kernel");
     const size_t total = (size_t)n * AP_DEGREE;
     unsigned long long *keys, *keys_s; uint32_t *vals, *vals_s, *indeg, *start;
     AP_TRY(db.alloc(&keys, total)); AP_TRY(db.alloc(&vals, total));
     AP_TRY(db.alloc(&indeg, n)); AP_TRY(db.alloc(&start, n));
     AP_CUDA(cudaMemsetAsync(indeg, 0, (size_t)n * 4));
     AP_CUDA(cudaMemsetAsync(start, 0, (size_t)n * 4));
+    mark("allocations");
     rev_keys_kernel<<<(uint32_t)((total + 255) / 256), 256>>>(n, nl, detour, keys, vals, indeg);
+    mark("edge keys");
     AP_TRY(sort_u64_pairs(db, keys, vals, total, 64, &keys_s, &vals_s));
+    mark("edge sort");
     seg_start_kernel<<<(uint32_t)((total + 255) / 256), 256>>>((uint32_t)total, keys_s, start);
     if (!ix->graph) AP_CUDA(cudaMalloc(&ix->graph, (size_t)n * AP_ROW * 4));
     if (!ix->ep) AP_CUDA(cudaMalloc(&ix->ep, AP_ENTRY_POINTS * 4));
@@ -1606,8 +1619,11 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
     ep_take_kernel<<<1, 32>>>(n, ek_s, ix->ep);
     AP_CUDA(cudaGetLastError());
     AP_CUDA(cudaDeviceSynchronize());
+    mark("reverse edges, rows and entry points");
     if (launches) *launches += 8;
-    return index_install_graph(ix);
+    const int rc_install = index_install_graph(ix);
+    mark("the fat rows");
+    return rc_install;
 }
 
 int join_dense_tc_launch(ap_index *ix, uint32_t node0, uint32_t nodes, const uint32_t *plist, const uint32_t *pcnt, float *D,
