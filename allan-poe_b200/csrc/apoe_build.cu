@@ -1720,8 +1720,12 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     AP_CUDA(cudaFuncSetAttribute(join_dense_simt_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)simt_smem));
 
     const uint32_t wblocks = (n + 7) / 8;  // warp-per-node kernels, 256 threads
-    cudaEvent_t ev[5];
-    for (auto &e : ev) AP_CUDA(cudaEventCreate(&e));
+    struct Events {   // released on every return path
+        cudaEvent_t e[5] = {nullptr, nullptr, nullptr, nullptr, nullptr};
+        ~Events() { for (auto x : e) if (x) cudaEventDestroy(x); }
+    } evs;
+    cudaEvent_t *ev = evs.e;
+    for (int i = 0; i < 5; ++i) AP_CUDA(cudaEventCreate(&ev[i]));
     float phase_ms[4] = {0, 0, 0, 0};  // sample + lists, dense tiles, sparse + proposals, merge
     uint32_t it = 0;
     unsigned long long prev_updates = 0;
@@ -1762,7 +1766,6 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
         knn_merge_kernel<<<(n + 3) / 4, 128>>>(k);
         launches += 2;
     }
-    for (auto &e : ev) cudaEventDestroy(e);
     AP_CUDA(cudaDeviceSynchronize());
     const auto t1 = std::chrono::high_resolution_clock::now();
 

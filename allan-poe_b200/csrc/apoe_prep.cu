@@ -274,8 +274,12 @@ static int bm25_device(bool corpus, uint32_t rows, uint32_t vocab, const uint32_
     AP_CUDA(cudaMemsetAsync(scratch, 0xFF, 4, st));
     AP_CUDA(cudaMemsetAsync(scratch + 1, 0, 8, st));
     AP_CUDA(cudaMemsetAsync(total, 0, 8, st));
-    cudaEvent_t e0, e1;
-    AP_CUDA(cudaEventCreate(&e0)); AP_CUDA(cudaEventCreate(&e1));
+    struct Events {   // released on every return path
+        cudaEvent_t a = nullptr, b = nullptr;
+        ~Events() { if (a) cudaEventDestroy(a); if (b) cudaEventDestroy(b); }
+    } ev;
+    AP_CUDA(cudaEventCreate(&ev.a)); AP_CUDA(cudaEventCreate(&ev.b));
+    cudaEvent_t e0 = ev.a, e1 = ev.b;
     AP_CUDA(cudaEventRecord(e0, st));
     uint32_t launches = 0;
     if (corpus) {
@@ -302,7 +306,6 @@ static int bm25_device(bool corpus, uint32_t rows, uint32_t vocab, const uint32_
     AP_CUDA(cudaStreamSynchronize(st));
     float ms = 0.f;
     cudaEventElapsedTime(&ms, e0, e1);
-    cudaEventDestroy(e0); cudaEventDestroy(e1);
     if (back[0] != 0xFFFFFFFFu) return fail(AP_ERR_ARG, "posting %u holds a term id outside the vocabulary of %u terms", back[0], vocab);
     const float avglen = corpus && rows ? (float)(tot / rows) : 0.f;
     if (corpus && !(avglen > 0.f)) return fail(AP_ERR_ARG, "the corpus has no term frequencies (average length %g)", avglen);

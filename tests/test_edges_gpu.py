@@ -56,6 +56,22 @@ def test_corpus_barely_larger_than_a_list():
     ix.close()
 
 
+@pytest.mark.parametrize("n", [3, 40])
+def test_corpus_smaller_than_a_list(n):
+    """Fewer documents than a k-NN list has slots: ids repeat inside the lists; the build still ends with well-formed
+    rows and the search over them equals the oracle's."""
+    ds = helpers.make_dataset(n, 5, seed=9, with_graph=False)
+    ix = apoe.Index.from_host(ds.D, ds.S, ds.B, for_build=True)
+    ix.build(seed=4)
+    rows, ep = ix.get_graph()
+    assert rows[:, :32].max() < n and rows[:, 32].max() <= 7 and ep.max() < n
+    eff, qdh, qs, qb, _ = helpers.scaled_queries(ds)
+    want_ids, want_dis, _ = orc.search(orc.f2h(ds.D), ds.S, ds.B, qdh, qs, qb, rows, ep, 32, 7)
+    ids, dis, _ = ix.search(ds.QD, ds.QS, ds.QB, cands=32)
+    assert np.array_equal(ids, want_ids) and np.array_equal(dis.view(np.uint32), want_dis.view(np.uint32))
+    ix.close()
+
+
 def test_batch_of_one_with_the_largest_pool(small):
     ix = apoe.Index.from_host(small.D, small.S, small.B)
     ix.set_graph(small.graph, small.ep)
