@@ -59,3 +59,33 @@ def test_errors_are_reported_not_fatal(built):
     assert e.value.code == 2 and "cannot open" in str(e.value)
     import numpy as np
     assert apoe.ndcg(np.array([[1, 2, 3]], dtype=np.uint32), 3, [[2, 9]]) > 0.0
+
+
+def test_corpus_files_are_validated_before_any_device_work(built, tmp_path):
+    """The streamed ingest reads headers and row offsets first: malformed files are refused with a message even where
+    no GPU is present (what it checks: the dimension word, the CSR sizes against the row count, the last offset)."""
+    import numpy as np
+    import apoe
+    p = lambda s: str(tmp_path / s)
+    n = 5
+    rows = np.zeros((n, 1025), dtype=np.float32)
+    rows.view(np.uint32)[:, 0] = 1024
+    rows.tofile(p("d.fvecs"))
+    def csr(path, off, nnz_header=None):
+        off = np.asarray(off, dtype=np.uint32)
+        nnz = int(off[-1]) if nnz_header is None else nnz_header
+        with open(path, "wb") as f:
+            np.array([nnz], dtype=np.uint32).tofile(f); off.tofile(f)
+            np.arange(int(off[-1]), dtype=np.uint32).tofile(f); np.ones(int(off[-1]), dtype=np.float32).tofile(f)
+    csr(p("ok.bin"), [0, 1, 2, 3, 4, 5])
+    bad = rows.copy(); bad.view(np.uint32)[0, 0] = 768; bad.tofile(p("dim.fvecs"))
+    with pytest.raises(apoe.ApoeError, match="dimension 768"):
+        apoe.Index.from_files(p("dim.fvecs"), p("ok.bin"), p("ok.bin"))
+    csr(p("short.bin"), [0, 1, 2])            # offsets of 2 rows only
+    with pytest.raises(apoe.ApoeError, match="needed for 5 rows"):
+        apoe.Index.from_files(p("d.fvecs"), p("short.bin"), p("ok.bin"))
+    csr(p("lying.bin"), [0, 1, 2, 3, 4, 5], nnz_header=4)   # header says 4 entries, the offsets end at 5
+    with pytest.raises(apoe.ApoeError, match="last offset 5 differs from the entry count 4"):
+        apoe.Index.from_files(p("d.fvecs"), p("ok.bin"), p("lying.bin"))
+    with pytest.raises(apoe.ApoeError, match="cannot open"):
+        apoe.Index.from_files(p("d.fvecs"), p("ok.bin"), p("missing.bin"))
