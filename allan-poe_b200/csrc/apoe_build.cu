@@ -318,7 +318,7 @@ __global__ void knn_sample_kernel(Knn k, uint32_t round) {
 
 // Participants of v's join: v itself, then the distinct new samples, then the distinct old samples not already
 // present; at most 32 new rows and 64 rows in total.  One warp per node.
-__global__ void knn_plist_kernel(Knn k) {
+__global__ void knn_plist_kernel(Knn k, const uint64_t *__restrict__ meta, uint32_t arena_bytes) {
     const uint32_t v = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (v >= k.n) return;
     __shared__ uint32_t sh[8][kPart];
@@ -345,6 +345,23 @@ __global__ void knn_plist_kernel(Knn k) {
         cnt = min(cnt + __popc(bal), cap);
         if (cls == 0) n_new = cnt;
         __syncwarp();
+    }
+    // Participants whose sparse sections would not fit the join's staging area are cut off here already (from the
+    // end, as the join kernel itself would do), so that their dense rows are not gathered for nothing.
+    {
+        uint32_t fit = cnt, run = 0;
+        for (uint32_t b0 = 0; b0 < cnt; b0 += 32) {
+            const uint32_t j = b0 + lane;
+            uint32_t sz = 0;
+            if (j < cnt) { const uint64_t m = meta[pl[j]]; sz = 8u * (pad2(meta_ns(m)) + pad2(meta_nb(m))); }
+            uint32_t incl = sz;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if ((int)lane >= o) incl += t; }
+            const uint32_t over = __ballot_sync(kFull, j < cnt && run + incl > arena_bytes);
+            if (over) { fit = b0 + (uint32_t)__ffs(over) - 1u; break; }
+            run += __shfl_sync(kFull, incl, 31);
+        }
+        cnt = fit; n_new = min(n_new, cnt);
     }
     for (uint32_t j = lane; j < kPart; j += 32) k.plist[(size_t)v * kPart + j] = j < cnt ? pl[j] : kEmpty;
     if (lane == 0) { k.pcnt[(size_t)v * 2] = n_new; k.pcnt[(size_t)v * 2 + 1] = cnt; }
@@ -1735,7 +1752,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
         AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
         AP_CUDA(cudaEventRecord(ev[0]));
         knn_sample_kernel<<<wblocks, 256>>>(k, it);
-        knn_plist_kernel<<<wblocks, 256>>>(k);
+        knn_plist_kernel<<<wblocks, 256>>>(k, ix->meta, ja.arena_bytes);
         launches += 2;
         AP_CUDA(cudaEventRecord(ev[1]));
         for (uint32_t node0 = 0; node0 < n; node0 += batch) {

@@ -104,6 +104,36 @@ __device__ __forceinline__ uint32_t vis_insert(uint32_t *tab, uint32_t mask, uin
 constexpr int kScoreBatch = 2;  // records a warp scores side by side (independent instruction streams)
 constexpr int kPerfectMax = 32; // query rows up to this many terms get a collision-free hash table
 
+// One section of R staged records against the query row's collision-free table: every lane takes the pairs
+// j = lane, lane + 32, ... in ascending order, NS per pass with all loads of a pass in flight together; a miss adds a
+// zero product, which leaves the lane's sum as the reference's per-term loop has it.
+template <int NS, int R, bool BM>
+__device__ __forceinline__ void table_pass(const uint2 *const (&pr)[R], const uint32_t (&cnt)[R], uint32_t nmax, const QRow &q,
+                                           uint32_t keymask, int lane, float (&part)[R], uint32_t (&hit)[R]) {
+    for (uint32_t j0 = 0; j0 < nmax; j0 += 32 * NS) {
+        uint2 pv[R][NS], e[R][NS];
+#pragma unroll
+        for (int t = 0; t < NS; ++t)
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const uint32_t j = j0 + 32 * t + lane;
+                pv[r][t] = j < cnt[r] ? pr[r][j] : make_uint2(kEmpty, 0u);  // padding never adds to the sum
+            }
+#pragma unroll
+        for (int t = 0; t < NS; ++t)
+#pragma unroll
+            for (int r = 0; r < R; ++r) e[r][t] = q.tab[(pv[r][t].x * q.mult) >> q.shift];
+#pragma unroll
+        for (int t = 0; t < NS; ++t)
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+                const bool match = (e[r][t].x & keymask) == pv[r][t].x;
+                part[r] = __fmaf_rn(match ? __uint_as_float(e[r][t].y) : 0.0f, __uint_as_float(pv[r][t].y), part[r]);
+                if (BM) hit[r] |= match ? (e[r][t].x >> 31) : 0u;
+            }
+    }
+}
+
 // Fused distances of R records staged in shared memory, computed by a full warp.  Valid in lane 0.
 //   dense : HFMA2 in the reference's lane / chunk association (src/query.cu:538-554);
 //   sparse: each lane walks the document's pairs j = lane, lane + 32, ... in ascending order, looks the id up in the
@@ -156,28 +186,9 @@ __device__ __forceinline__ void score_records(const uint8_t *const (&rec)[R], co
             part[r] = 0.0f;
         }
         if (q.mult != 0) {
-            for (uint32_t j0 = 0; j0 < nmax; j0 += 128) {
-                uint2 pv[R][4], e[R][4];
-#pragma unroll
-                for (int t = 0; t < 4; ++t)
-#pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        const uint32_t j = j0 + 32 * t + lane;
-                        pv[r][t] = j < cnt[r] ? pr[r][j] : make_uint2(kEmpty, 0u);  // padding never adds to the sum
-                    }
-#pragma unroll
-                for (int t = 0; t < 4; ++t)
-#pragma unroll
-                    for (int r = 0; r < R; ++r) e[r][t] = q.tab[(pv[r][t].x * q.mult) >> q.shift];
-#pragma unroll
-                for (int t = 0; t < 4; ++t)
-#pragma unroll
-                    for (int r = 0; r < R; ++r) {
-                        const bool match = (e[r][t].x & keymask) == pv[r][t].x;
-                        part[r] = __fmaf_rn(match ? __uint_as_float(e[r][t].y) : 0.0f, __uint_as_float(pv[r][t].y), part[r]);
-                        if (sec == 1) hit[r] |= match ? (e[r][t].x >> 31) : 0u;
-                    }
-            }
+            // sparse rows average ~120 terms (four per lane and pass), BM25 rows ~60 (two per lane and pass)
+            if (sec == 0) table_pass<4, R, false>(pr, cnt, nmax, q, keymask, lane, part, hit);
+            else table_pass<2, R, true>(pr, cnt, nmax, q, keymask, lane, part, hit);
         } else if (q.n != 0) {
             // ref: cal_sparse_dist / cal_bm25_dist -- lower bound of the document's id in the query row
             for (uint32_t j = lane; j < nmax; j += 32) {
@@ -317,7 +328,8 @@ __device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const u
                     __syncwarp();
                     if (inb) {
                         const uint32_t aoff = pre_start - b0;
-                        c.info[lane] = make_uint2(aoff, ns | (nb << 16));
+                        // entry k of the batch: arena offset and pool slot (lane) in one word, term counts in the other
+                        c.info[__popc(bm & ((1u << lane) - 1u))] = make_uint2(aoff | ((uint32_t)lane << 24), ns | (nb << 16));
                         const uint8_t *src = a.rec + meta_off16(my_meta) * 16ull;
                         uint8_t *dst = c.arena + aoff;
                         const uint32_t ps = 8u * pad2(ns), pb = 8u * pad2(nb);
@@ -355,9 +367,9 @@ __device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const u
                 for (int r = 0; r < kScoreBatch; ++r) {
                     const int k = g * kScoreBatch + r;
                     const bool valid = k < nb_batch;
-                    slot[r] = valid ? __fns(bm, 0, k + 1) : -1;
-                    const uint2 inf = valid ? c.info[slot[r]] : make_uint2(0u, 0u);
-                    rec[r] = c.arena + inf.x; rns[r] = inf.y & 0xFFFFu; rnb[r] = inf.y >> 16;
+                    const uint2 inf = valid ? c.info[k] : make_uint2(0u, 0u);
+                    slot[r] = valid ? (int)(inf.x >> 24) : -1;
+                    rec[r] = c.arena + (inf.x & 0xFFFFFFu); rns[r] = inf.y & 0xFFFFu; rnb[r] = inf.y >> 16;
                 }
                 score_records<F, kScoreBatch>(rec, rns, rnb, qreg, c.qs, c.qb, lane, d, hit);
 #pragma unroll
