@@ -31,7 +31,7 @@ DIM = 1024
 # DRAM bytes / algorithmic bytes of the search kernel (dram__bytes_read.sum + dram__bytes_write.sum of one launch over
 # the kernel's counted bytes), from the ncu capture of the 200k-document case summarised under profiles/; the full-size
 # launch is scaled by this ratio (both grow with the number of fused distances)
-TRAFFIC_RATIO = 0.884
+TRAFFIC_RATIO = 0.864
 
 
 def parse():
