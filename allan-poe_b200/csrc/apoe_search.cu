@@ -29,7 +29,7 @@ constexpr int kKeywordRing = 32;  // ref: KEYWORD, src/query.cu:18
 constexpr int kMergeMax = (AP_MAX_CANDS + 32 + kSearchThreads - 1) / kSearchThreads;
 
 enum : int { PF_DENSE = 1, PF_SPARSE = 2, PF_BM25 = 4, PF_KEYWORD = 8, PF_KG = 16, PF_UNFUSED = 32 };
-enum : int { CTL_QUERY = 0, CTL_SEL = 1, CTL_BATCH = 2, CTL_LAST = 3, CTL_MERGE = 4, CTL_SLOT = 5, CTL_KWNUM = 6, CTL_M = 7, CTL_MULT_S = 8, CTL_MULT_B = 9 };
+enum : int { CTL_QUERY = 0, CTL_SEL = 1, CTL_BATCH = 2 /* and 3: one word per arena half */, CTL_MERGE = 4, CTL_SLOT = 5, CTL_KWNUM = 6, CTL_M = 7, CTL_MULT_S = 8, CTL_MULT_B = 9 };
 
 struct SearchArgs {
     const FatEdge *fat;
@@ -51,6 +51,7 @@ struct SearchArgs {
     uint32_t *ctl;            // [0] next query, [1] error word
     unsigned long long *cnt;  // [0] expansions, [1] evaluations, [2] gathered bytes
     uint32_t arena_bytes;
+    uint32_t half_bytes, halves;   // the arena as one staging area or as two halves filled alternately
     uint32_t vis_mask;           // visited table size - 1
     uint32_t ts_slots, ts_shift; // collision-free table of the query's sparse row (0 slots: not allocated)
     uint32_t tb_slots, tb_shift; // same for the BM25 row
@@ -306,86 +307,100 @@ __device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const u
         pre_end = incl; pre_start = incl - sz;
         remaining = __ballot_sync(kFull, my_need);
     }
-    for (;;) {
-        if (c.warp == 0) {
-            uint32_t bm = 0;
-            if (remaining) {
-                const int first = __ffs(remaining) - 1;
-                const uint32_t b0 = __shfl_sync(kFull, pre_start, first);
-                const bool inb = ((remaining >> lane) & 1u) && (pre_end - b0 <= a.arena_bytes);
-                bm = __ballot_sync(kFull, inb);
-                if (bm == 0) {  // a record larger than the arena: the host sizes the arena so this cannot happen
-                    if (lane == 0) atomicExch(a.ctl + 1, 2u);
-                    remaining = 0;
-                } else {
-                    const int hi = 31 - __clz(bm);
-                    const uint32_t total = __shfl_sync(kFull, pre_end, hi) - b0;
-                    if (lane == 0) {
-                        mbar_arrive_expect_tx(c.mbar, total);
-                        c.c_bytes += total;
-                        c.c_eval += __popc(bm);
-                    }
-                    __syncwarp();
-                    if (inb) {
-                        const uint32_t aoff = pre_start - b0;
-                        // entry k of the batch: arena offset and pool slot (lane) in one word, term counts in the other
-                        c.info[__popc(bm & ((1u << lane) - 1u))] = make_uint2(aoff | ((uint32_t)lane << 24), ns | (nb << 16));
-                        const uint8_t *src = a.rec + meta_off16(my_meta) * 16ull;
-                        uint8_t *dst = c.arena + aoff;
-                        const uint32_t ps = 8u * pad2(ns), pb = 8u * pad2(nb);
-                        if (D && S && B) bulk_g2s(dst, src, kDenseBytes + ps + pb, c.mbar);
-                        else if (D && S) bulk_g2s(dst, src, kDenseBytes + ps, c.mbar);
-                        else if (D && B) { bulk_g2s(dst, src, kDenseBytes, c.mbar); if (pb) bulk_g2s(dst + kDenseBytes, src + kDenseBytes + ps, pb, c.mbar); }
-                        else if (D) bulk_g2s(dst, src, kDenseBytes, c.mbar);
-                        else if (S && B) { if (ps + pb) bulk_g2s(dst, src + kDenseBytes, ps + pb, c.mbar); }
-                        else if (S) { if (ps) bulk_g2s(dst, src + kDenseBytes, ps, c.mbar); }
-                        else { if (pb) bulk_g2s(dst, src + kDenseBytes + ps, pb, c.mbar); }
-                    }
-                    remaining &= ~bm;
+    // Warp 0: the next records that fit one arena half go there, one bulk copy each, completing on that half's
+    // mbarrier; the half's batch mask (0 = nothing left) goes to its control word.
+    auto issue = [&](int h) {
+        uint32_t bm = 0;
+        if (remaining) {
+            const int first = __ffs(remaining) - 1;
+            const uint32_t b0 = __shfl_sync(kFull, pre_start, first);
+            const bool inb = ((remaining >> lane) & 1u) && (pre_end - b0 <= a.half_bytes);
+            bm = __ballot_sync(kFull, inb);
+            if (bm == 0) {  // a record larger than the staging area: the host sizes it so this cannot happen
+                if (lane == 0) atomicExch(a.ctl + 1, 2u);
+                remaining = 0;
+            } else {
+                const int hi = 31 - __clz(bm);
+                const uint32_t total = __shfl_sync(kFull, pre_end, hi) - b0;
+                uint64_t *bar = c.mbar + h;
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(bar, total);
+                    c.c_bytes += total;
+                    c.c_eval += __popc(bm);
                 }
+                __syncwarp();
+                if (inb) {
+                    const uint32_t aoff = (uint32_t)h * a.half_bytes + (pre_start - b0);
+                    // entry k of the half's batch: arena offset and pool slot (lane) in one word, term counts in the other
+                    c.info[32 * h + __popc(bm & ((1u << lane) - 1u))] = make_uint2(aoff | ((uint32_t)lane << 24), ns | (nb << 16));
+                    const uint8_t *src = a.rec + meta_off16(my_meta) * 16ull;
+                    uint8_t *dst = c.arena + aoff;
+                    const uint32_t ps = 8u * pad2(ns), pb = 8u * pad2(nb);
+                    if (D && S && B) bulk_g2s(dst, src, kDenseBytes + ps + pb, bar);
+                    else if (D && S) bulk_g2s(dst, src, kDenseBytes + ps, bar);
+                    else if (D && B) { bulk_g2s(dst, src, kDenseBytes, bar); if (pb) bulk_g2s(dst + kDenseBytes, src + kDenseBytes + ps, pb, bar); }
+                    else if (D) bulk_g2s(dst, src, kDenseBytes, bar);
+                    else if (S && B) { if (ps + pb) bulk_g2s(dst, src + kDenseBytes, ps + pb, bar); }
+                    else if (S) { if (ps) bulk_g2s(dst, src + kDenseBytes, ps, bar); }
+                    else { if (pb) bulk_g2s(dst, src + kDenseBytes + ps, pb, bar); }
+                }
+                remaining &= ~bm;
             }
-            if (lane == 0) { c.ctl[CTL_BATCH] = bm; c.ctl[CTL_LAST] = (remaining == 0) ? 1u : 0u; }
         }
-        __syncthreads();
-        const uint32_t bm = c.ctl[CTL_BATCH];
-        const bool last = c.ctl[CTL_LAST] != 0;
-        if (bm) {
-            // warp 0 alone polls the mbarrier; the other warps park on the CTA barrier (no spinning instructions)
-            long long tw0 = 0;
-            if (c.warp == 0) { tw0 = clock64(); mbar_wait_bounded(c.mbar, c.phase, a.ctl + 1, 1u); }
-            c.phase ^= 1u;
-            __syncthreads();
-            long long tw1 = 0;
-            if (c.tid == 0) { tw1 = clock64(); c.t_wait += tw1 - tw0; }
-            const int nb_batch = __popc(bm);
-            for (int g = c.warp; g * kScoreBatch < nb_batch; g += kSearchWarps) {  // groups of records, round-robin over warps
-                const uint8_t *rec[kScoreBatch];
-                uint32_t rns[kScoreBatch], rnb[kScoreBatch], hit[kScoreBatch];
-                int slot[kScoreBatch];
-                float d[kScoreBatch];
-#pragma unroll
-                for (int r = 0; r < kScoreBatch; ++r) {
-                    const int k = g * kScoreBatch + r;
-                    const bool valid = k < nb_batch;
-                    const uint2 inf = valid ? c.info[k] : make_uint2(0u, 0u);
-                    slot[r] = valid ? (int)(inf.x >> 24) : -1;
-                    rec[r] = c.arena + (inf.x & 0xFFFFFFu); rns[r] = inf.y & 0xFFFFu; rnb[r] = inf.y >> 16;
-                }
-                score_records<F, kScoreBatch>(rec, rns, rnb, qreg, c.qs, c.qb, lane, d, hit);
-#pragma unroll
-                for (int r = 0; r < kScoreBatch; ++r) {
-                    const uint32_t h = KW ? __ballot_sync(kFull, hit[r] != 0) : 0u;
-                    if (lane == 0 && slot[r] >= 0) {
-                        c.pool_dis[base + slot[r]] = d[r];
-                        if (KW && h) c.pool_id[base + slot[r]] |= 0x40000000u;
-                    }
-                }
-            }
-            if (c.tid == 0) c.t_score += clock64() - tw1;
-        }
-        __syncthreads();
-        if (!bm || last) break;
+        if (lane == 0) c.ctl[CTL_BATCH + h] = bm;
+    };
+    if (c.warp == 0) {
+        issue(0);
+        if (a.halves == 2) issue(1);
+        else if (lane == 0) c.ctl[CTL_BATCH + 1] = 0;
     }
+    __syncthreads();
+    // Batches are consumed in the order they were issued, halves alternating; while one half is scored the copies
+    // into the other are in flight.
+    for (int cur = 0;;) {
+        const uint32_t bm = c.ctl[CTL_BATCH + cur];
+        if (!bm) break;
+        // every warp waits for the half on its own (one polling lane), so a warp that comes late -- warp 0 after a
+        // refill -- holds nobody up; with two halves the copies have usually landed already
+        long long tw0 = 0;
+        if (c.tid == 0) tw0 = clock64();
+        if (lane == 0) mbar_wait_bounded(c.mbar + cur, (c.phase >> cur) & 1u, a.ctl + 1, 1u);
+        __syncwarp();
+        c.phase ^= 1u << cur;
+        long long tw1 = 0;
+        if (c.tid == 0) { tw1 = clock64(); c.t_wait += tw1 - tw0; }
+        const int nb_batch = __popc(bm);
+        // groups of records round-robin over the warps, warp 0 last: it is the one that issues the refills
+        for (int g = (c.warp + kSearchWarps - 1) % kSearchWarps; g * kScoreBatch < nb_batch; g += kSearchWarps) {
+            const uint8_t *rec[kScoreBatch];
+            uint32_t rns[kScoreBatch], rnb[kScoreBatch], hit[kScoreBatch];
+            int slot[kScoreBatch];
+            float d[kScoreBatch];
+#pragma unroll
+            for (int r = 0; r < kScoreBatch; ++r) {
+                const int k = g * kScoreBatch + r;
+                const bool valid = k < nb_batch;
+                const uint2 inf = valid ? c.info[32 * cur + k] : make_uint2(0u, 0u);
+                slot[r] = valid ? (int)(inf.x >> 24) : -1;
+                rec[r] = c.arena + (inf.x & 0xFFFFFFu); rns[r] = inf.y & 0xFFFFu; rnb[r] = inf.y >> 16;
+            }
+            score_records<F, kScoreBatch>(rec, rns, rnb, qreg, c.qs, c.qb, lane, d, hit);
+#pragma unroll
+            for (int r = 0; r < kScoreBatch; ++r) {
+                const uint32_t h = KW ? __ballot_sync(kFull, hit[r] != 0) : 0u;
+                if (lane == 0 && slot[r] >= 0) {
+                    c.pool_dis[base + slot[r]] = d[r];
+                    if (KW && h) c.pool_id[base + slot[r]] |= 0x40000000u;
+                }
+            }
+        }
+        if (c.tid == 0) c.t_score += clock64() - tw1;
+        __syncthreads();                       // everyone is done with this half
+        if (c.warp == 0) issue(cur);           // refill it; the word is read again two turns from now
+        if (a.halves == 2) cur ^= 1;
+        else __syncthreads();                  // one staging area: the refill's word is read next
+    }
+    __syncthreads();
 }
 
 // Block-wide restatement of the reference's shared-memory bitonic network for an arbitrary length
@@ -446,7 +461,7 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
     uint32_t *stg_id = pool_id + topm;
     float *stg_dis = pool_dis + topm;
 
-    if (tid == 0) { mbar_init(c.mbar, 1); mbar_fence_init(); }
+    if (tid == 0) { mbar_init(c.mbar, 1); mbar_init(c.mbar + 1, 1); mbar_fence_init(); }
     __syncthreads();
 
     for (;;) {
@@ -898,7 +913,7 @@ static uint32_t layout(SearchArgs &a, const ap_index *ix, uint32_t warps, uint32
     const uint32_t vis = (cands + 32 + 3 * 32) * 2 <= 1024 ? 1024u : 2048u;
     a.vis_mask = vis - 1;
     a.o_vis = take(4 * vis, 16);
-    a.o_info = take(8 * 32, 16);
+    a.o_info = take(8 * 64, 16);   // batch entries of the two arena halves
     a.o_sq = take((flags & PF_SPARSE) ? 8 * std::max(1u, max_qs) : 0, 16);
     a.o_bq = take((flags & PF_BM25) ? 8 * std::max(1u, max_qb) : 0, 16);
     // collision-free tables for short query rows: 16 slots per term keeps the search for a multiplier short
@@ -930,6 +945,9 @@ static int launch_one(ap_index *ix, SearchArgs &a, uint32_t fixed, uint32_t want
     }
     arena = std::min(arena, 512u * 1024u);  // the mbarrier transaction count is 20 bits wide
     a.arena_bytes = arena;
+    // two halves filled alternately when the largest record fits one of them, else one staging area
+    a.halves = (arena / 2) / 128 * 128 >= need_bytes ? 2u : 1u;
+    a.half_bytes = a.halves == 2 ? (arena / 2) / 128 * 128 : arena;
     const size_t smem = fixed + arena;
     AP_CUDA(cudaFuncSetAttribute(search_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int occ = 0;
