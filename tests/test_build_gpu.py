@@ -77,6 +77,13 @@ def test_prune_kernels_agree_with_long_rows():
     want = orc.prune(ds.D7h, S, B2, knn, dis, power)
     got = ix.prune(knn, dis, power)
     assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1]) and np.array_equal(got[2], want[2])
+    # the whole build on the same corpus (wide term tables, fewer of them per join): well-formed rows, and the rows are
+    # what the oracle makes of the lists the build ended with
+    ix.build(flags=apoe.BUILD_KEEP_KNN, seed=5)
+    ids, kdis, kpow = ix.get_knn()
+    rows, ep = ix.get_graph()
+    assert rows[:, :32].max() < ds.n and np.array_equal(kpow.view(np.uint32), power.view(np.uint32))
+    assert np.array_equal(rows, orc.prune(ds.D7h, S, B2, ids, kdis, kpow)[2])
     ix.close()
 
 
