@@ -391,6 +391,7 @@ def run_own(args):
         }
         if args.curve and not sharded:
             line["curve"] = curve(ix, queries, eff, mq, gt if cpu else None, dev, stream)
+            line["variants"] = variants(ix, queries, eff, mq, dev, stream, n, cands)
         # single-query latency (kernel time by CUDA events, device-resident query), median of 30 different queries
         lat = []
         o1 = torch.empty(1, cands, dtype=torch.int32, device=dev); d1 = torch.empty(1, cands, dtype=torch.float32, device=dev)
@@ -420,6 +421,37 @@ def curve(ix, queries, eff, mq, gt, dev, stream):
             st = ix.search_device(queries, oi, od, cands=cands, weights=eff, max_nnz=mq, stream=stream)
         rec = recall_at_10(oi[:gt.shape[0]].cpu().numpy().view(np.uint32), gt) if gt is not None else None
         out.append({"cands": cands, "qps": round(nq / st.kernel_ms * 1e3, 1), "recall_at_10": rec})
+    return out
+
+
+def flag_keywords(queries_host, synth):
+    """Query BM25 ids with bit 31 set on the required terms (ref: src/query.cu:1828-1843), as a numpy array."""
+    kws = synth.make_keywords(queries_host)
+    off = queries_host.bm25.off.numpy().astype(np.int64)
+    idx = queries_host.bm25.idx.numpy().astype(np.uint32)
+    for q, req in enumerate(kws):
+        row = idx[off[q]:off[q + 1]]
+        row[np.isin(row, np.asarray(req, dtype=np.uint32))] |= np.uint32(0x80000000)
+    return idx
+
+
+def variants(ix, queries, eff, mq, dev, stream, n, cands):
+    """The keyword-constrained and the knowledge-graph searches on the benchmark corpus (kernel time, resident queries)."""
+    import apoe
+    import synth
+    nq = queries.nq
+    out = {}
+    oi = torch.empty(nq, cands, dtype=torch.int32, device=dev); od = torch.empty(nq, cands, dtype=torch.float32, device=dev)
+    qh = host_queries(queries)
+    kq = synth.Queries(queries.dense, queries.sparse, synth.Csr(queries.bm25.off, torch.from_numpy(flag_keywords(qh, synth).view(np.int32)).to(dev), queries.bm25.val))
+    for _ in range(2):
+        st = ix.search_device(kq, oi, od, cands=cands, weights=eff, max_nnz=mq, stream=stream, flags=apoe.SEARCH_KEYWORD)
+    out["keyword"] = {"qps": round(nq / st.kernel_ms * 1e3, 1), "cands": cands, "queries": nq, "what": "1-4 required BM25 terms per query, keyword-edge recycling on"}
+    kg = synth.make_kg(n, nq, device=dev)
+    ix.set_kg(kg.e2e_off, kg.e2e_idx, kg.e2d_off, kg.e2d_idx)
+    for _ in range(2):
+        st = ix.search_device(queries, oi, od, cands=cands, weights=eff, max_nnz=mq, stream=stream, kg_weight=40.0, ent=(kg.qe_off, kg.qe_idx))
+    out["kg"] = {"qps": round(nq / st.kernel_ms * 1e3, 1), "cands": cands, "queries": nq, "what": "500 k entities, 1-3 seed entities per query, kg_weight 40"}
     return out
 
 
@@ -481,6 +513,16 @@ def run_reference(args):
                 ids_c, _, t_all_c, t_search_c = apoe_ref.search(D, c3(S), c3(B), qd[:nq], sub(qs), sub(qb), graph, built["ep"], cc, 7)
             ref_curve.append({"cands": cc, "qps_kernel_only": round(nq / t_search_c, 1), "qps": round(nq / t_all_c, 1),
                               "recall_at_10": recall_at_10(ids_c[:m], gt_c[:m]) if gt_c is not None else None})
+    ref_variants = None
+    if args.curve:   # the reference's keyword kernel on the same flagged queries (its KG kernel is not run: it reads an unset index)
+        class _Q:   # host queries in the shape flag_keywords expects
+            pass
+        qh = _Q(); qh.bm25 = _Q(); qh.nq = nq
+        qh.bm25.off = torch.from_numpy(QB.off[:nq + 1].astype(np.int64)); qh.bm25.idx = torch.from_numpy(QB.idx[:int(QB.off[nq])].astype(np.int64))
+        kidx = flag_keywords(qh, synth)
+        for _ in range(2):
+            _, _, t_all_k, t_search_k = apoe_ref.search(D, c3(S), c3(B), qd[:nq], sub(qs), (qb.off[:nq + 1], kidx, qb.val[:int(qb.off[nq])]), graph, built["ep"], cands, 7 | 8)
+        ref_variants = {"keyword": {"qps_kernel_only": round(nq / t_search_k, 1), "qps": round(nq / t_all_k, 1), "cands": cands, "queries": nq}}
     lat1 = []
     one = lambda c, i: (c.off[i:i + 2] - c.off[i], c.idx[int(c.off[i]):int(c.off[i + 1])], c.val[int(c.off[i]):int(c.off[i + 1])])
     for qi in range(min(10, nq)):
@@ -488,7 +530,7 @@ def run_reference(args):
         lat1.append(t1 * 1e3)
     ingest = ingest_reference(min(args.ingest_docs, n), torch.device("cuda", local)) if args.ingest_docs > 0 else None
     print(json.dumps({
-        "ingest": ingest, "curve": ref_curve, "latency_batch1_ms": round(float(np.median(lat1)), 4),
+        "ingest": ingest, "curve": ref_curve, "variants": ref_variants, "latency_batch1_ms": round(float(np.median(lat1)), 4),
         "impl": "reference", "metric": "hybrid search QPS at recall@10>=0.95 (cands=128); index build sec per 1M docs",
         "value": round(qps, 1), "unit": "queries/s", "n_gpus": 1, "steps": args.steps, "warmup": max(args.warmup, 1),
         "ms_per_step": round(total / args.steps * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
