@@ -460,6 +460,8 @@ def run_reference(args):
     rank, world, local = dist_env()
     if rank != 0:
         return
+    if world > 1:   # the launcher pins every rank to one OpenMP thread; this arm works on rank 0 alone and may use the host
+        os.environ["OMP_NUM_THREADS"] = str(min(32, os.cpu_count() or 1))
     sys.path.insert(0, os.path.join(ROOT, "oracle"))
     import apoe_ref
     if not apoe_ref.available():
