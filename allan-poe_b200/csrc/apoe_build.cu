@@ -129,9 +129,16 @@ __device__ __forceinline__ float ord2f(uint32_t o);
 // evaluated directly and offered to both sides, and a merge turns the offers into the first sorted lists.
 // (The reference starts from random lists only, src/index.cu:99-106; random entries stay behind the seeds.)
 // ---------------------------------------------------------------------------------------------------------
-__global__ void inv_count_kernel(uint32_t n, const uint64_t *__restrict__ meta, uint32_t *__restrict__ cnt) {
+__global__ void inv_count_kernel(uint32_t n, const uint64_t *__restrict__ meta, uint32_t *__restrict__ cnt, unsigned long long *__restrict__ total) {
+    __shared__ unsigned long long part;
+    if (threadIdx.x == 0) part = 0;
+    __syncthreads();
     const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
-    if (i <= n) cnt[i] = i < n ? meta_nb(meta[i]) : 0u;
+    const uint32_t c = i < n ? meta_nb(meta[i]) : 0u;
+    if (i <= n) cnt[i] = c;
+    if (c) atomicAdd(&part, (unsigned long long)c);
+    __syncthreads();
+    if (threadIdx.x == 0 && part) atomicAdd(total, part);   // 64-bit count of all postings
 }
 __global__ void inv_keys_kernel(uint32_t n, const uint64_t *__restrict__ meta, const uint8_t *__restrict__ rec,
                                 const uint32_t *__restrict__ off, unsigned long long *__restrict__ keys) {
@@ -1646,23 +1653,24 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
 int join_dense_tc_launch(ap_index *ix, uint32_t node0, uint32_t nodes, const uint32_t *plist, const uint32_t *pcnt, float *D,
                          cudaStream_t stream);  // apoe_join_tc.cu
 
-// Term-seeded first lists (see seed_cand_kernel).  Skipped when the corpus has no BM25 terms or more than 2^31 - 1.
+// Term-seeded first lists (see seed_cand_kernel).  Skipped when the corpus has no BM25 postings or 2^31 and more
+// (about 35 M documents of the benchmark's shape): the build then starts from the random lists alone.
 static int seed_run(ap_index *ix, const Knn &k, uint32_t take, uint32_t shared_pairs, uint32_t *launches) {
     const uint32_t n = ix->n;
     DevBuf db;
     uint32_t *cnt, *off, *cand;
-    AP_TRY(db.alloc(&cnt, (size_t)n + 1)); AP_TRY(db.alloc(&off, (size_t)n + 1));
-    inv_count_kernel<<<n / 256 + 1, 256>>>(n, ix->meta, cnt);
+    unsigned long long *total64;
+    AP_TRY(db.alloc(&cnt, (size_t)n + 1)); AP_TRY(db.alloc(&off, (size_t)n + 1)); AP_TRY(db.alloc(&total64, 1));
+    AP_CUDA(cudaMemset(total64, 0, 8));
+    inv_count_kernel<<<n / 256 + 1, 256>>>(n, ix->meta, cnt, total64);
+    unsigned long long all = 0;
+    AP_CUDA(cudaMemcpy(&all, total64, 8, cudaMemcpyDeviceToHost));
+    if (all == 0 || all >= (1ull << 31)) return AP_OK;   // nothing to seed from, or more postings than one sort call takes
     size_t tmp_bytes = 0;
     AP_CUDA(cub::DeviceScan::ExclusiveSum(nullptr, tmp_bytes, cnt, off, (int)(n + 1)));
     uint8_t *tmp; AP_TRY(db.alloc(&tmp, tmp_bytes));
     AP_CUDA(cub::DeviceScan::ExclusiveSum(tmp, tmp_bytes, cnt, off, (int)(n + 1)));
-    // the 32-bit running sum wraps on huge corpora; the per-document counts are <= 16383, so the check below on
-    // the host-side total of max_nb * n is exact enough to rule that out
-    if ((unsigned long long)ix->max_nb * n >= (1ull << 31)) return AP_OK;
-    uint32_t total = 0;
-    AP_CUDA(cudaMemcpy(&total, off + n, 4, cudaMemcpyDeviceToHost));
-    if (total == 0) return AP_OK;
+    const uint32_t total = (uint32_t)all;
     unsigned long long *keys, *keys_s;
     AP_TRY(db.alloc(&keys, total));
     inv_keys_kernel<<<(n + 7) / 8, 256>>>(n, ix->meta, ix->rec_build, off, keys);
