@@ -17,6 +17,7 @@ _LIB = None
 AP_OK = 0
 CREATE_FOR_BUILD = 1
 BUILD_SIMT_JOIN, BUILD_KEEP_KNN, BUILD_RANDOM_START, BUILD_SHARED_PAIRS, BUILD_REVERSE_PASS = 1, 2, 4, 8, 16
+BUILD_PRUNE_STEPWISE, BUILD_TRACE, BUILD_DETERMINISTIC = 32, 64, 128
 SEARCH_KEYWORD, SEARCH_KG, SEARCH_RAW_WEIGHTS, SEARCH_UNFUSED_DENSE = 1, 2, 4, 8
 DIM, ROW, DEGREE, KNN, ENTRY_POINTS = 1024, 40, 32, 64, 32
 
@@ -192,6 +193,17 @@ class Index:
         return cls(h, int(st.rows), device), st
 
     @classmethod
+    def from_files_range(cls, dense_path: str, sparse_path: str, bm25_path: str, row_start: int, row_count: int, device: int = 0,
+                         for_build: bool = False, threads: int = 0):
+        """Documents [row_start, row_start + row_count) of the corpus files only (a shard; local ids start at 0)."""
+        h = C.c_void_p()
+        st = IngestStats()
+        _check(lib().ap_index_create_files_range(C.byref(h), C.c_int(device), dense_path.encode(), sparse_path.encode(), bm25_path.encode(),
+                                                 C.c_uint32(row_start), C.c_uint32(row_count), C.c_uint32(CREATE_FOR_BUILD if for_build else 0),
+                                                 C.c_uint32(threads), C.byref(st)))
+        return cls(h, int(st.rows), device), st
+
+    @classmethod
     def from_device(cls, dense, sparse, bm25, for_build: bool = False) -> "Index":
         """dense: CUDA float32 [n, 1024]; sparse / bm25: objects with CUDA int32 .off/.idx and float32 .val."""
         assert dense.is_cuda and dense.is_contiguous()
@@ -255,13 +267,13 @@ class Index:
         _check(lib().ap_index_norms(self._h, _ptr(out)))
         return out
 
-    def prune(self, knn_ids, knn_dis, power):
+    def prune(self, knn_ids, knn_dis, power, flags: int = 0):
         knn_ids, knn_dis, power = _np(knn_ids, np.uint32), _np(knn_dis, np.float32), _np(power, np.float32)
         new_list = np.empty((self.n, DEGREE), dtype=np.uint32)
         kw = np.empty((self.n, 33), dtype=np.uint32)
         rows = np.empty((self.n, ROW), dtype=np.uint32)
-        _check(lib().ap_index_prune(self._h, _ptr(knn_ids), _ptr(knn_dis), _ptr(power), _ptr(new_list), _ptr(kw),
-                                    _ptr(rows)))
+        _check(lib().ap_index_prune(self._h, _ptr(knn_ids), _ptr(knn_dis), _ptr(power), C.c_uint32(flags), _ptr(new_list),
+                                    _ptr(kw), _ptr(rows)))
         return new_list, kw, rows
 
     def set_kg(self, e2e_off, e2e_idx, e2d_off, e2d_idx) -> None:
@@ -323,6 +335,34 @@ class Index:
         _check(lib().ap_search_host_static(self._h, C.byref(q), C.byref(o), _ptr(ids), _ptr(dis), C.byref(st)))
         return ids, dis, st
 
+    def search_shard_device(self, queries, out_keys, id_base: int, top_k: int = 10, cands=128, weights=(1.0, 1.0, 1.0), flags=0,
+                            max_nnz=(0, 0), stream=None, stats=False, out_ids=None, out_dis=None):
+        """This shard's part of a corpus-sharded search on device tensors: out_keys (int64 [nq, top_k]) receives the
+        best top_k results of every query as (ordered distance << 32 | local id + id_base) words, written by the
+        search kernel itself.  The weights must be the ones every shard uses."""
+        q = Queries(nq=queries.dense.shape[0], dense=_ptr(queries.dense),
+                    sparse=_Csr(_ptr(queries.sparse.off), _ptr(queries.sparse.idx), _ptr(queries.sparse.val)),
+                    bm25=_Csr(_ptr(queries.bm25.off), _ptr(queries.bm25.idx), _ptr(queries.bm25.val)),
+                    max_sparse_nnz=max_nnz[0], max_bm25_nnz=max_nnz[1])
+        o = SearchOpts(cands=cands, flags=flags | SEARCH_RAW_WEIGHTS, sparse_weight=weights[0], bm25_weight=weights[1],
+                       dense_weight=weights[2])
+        st = SearchStats()
+        _check(lib().ap_search_shard_device(self._h, C.byref(q), C.byref(o), C.c_uint32(id_base), C.c_uint32(top_k), _ptr(out_keys),
+                                            _ptr(out_ids), _ptr(out_dis), C.c_void_p(stream or 0), C.byref(st) if stats else None))
+        return st
+
+    def search_shard(self, qdense, qsparse, qbm25, id_base: int, top_k: int = 10, cands=128, weights=(1.0, 1.0, 1.0), flags=0):
+        """Host buffers in, exchange keys out (uint64 [nq, top_k]); weights are used as given."""
+        q, keep = self._host_queries(qdense, qsparse, qbm25)
+        o = SearchOpts(cands=cands, flags=flags | SEARCH_RAW_WEIGHTS, sparse_weight=weights[0], bm25_weight=weights[1], dense_weight=weights[2])
+        keys = np.empty((q.nq, top_k), dtype=np.uint64)
+        ids = np.empty((q.nq, cands), dtype=np.uint32)
+        dis = np.empty((q.nq, cands), dtype=np.float32)
+        st = SearchStats()
+        _check(lib().ap_search_shard_host(self._h, C.byref(q), C.byref(o), C.c_uint32(id_base), C.c_uint32(top_k), _ptr(keys), _ptr(ids),
+                                          _ptr(dis), C.byref(st)))
+        return keys, ids, dis, st
+
     def search_device(self, queries, out_ids, out_dis, cands=128, weights=(1.0, 1.0, 1.0), kg_weight=0.0, flags=0,
                       ent=None, max_nnz=(0, 0), stream=None, stats=True, arena_bytes=0, ctas_per_sm=0):
         """Device tensors in and out (queries: object with CUDA .dense and .sparse/.bm25 CSRs).  The weights are
@@ -339,6 +379,13 @@ class Index:
         _check(lib().ap_search_device(self._h, C.byref(q), C.byref(o), _ptr(out_ids), _ptr(out_dis),
                                       C.c_void_p(stream or 0), C.byref(st) if stats else None))
         return st
+
+    def check_status(self) -> None:
+        """Raises ApoeError(6) when a kernel of an earlier asynchronous call raised its error word."""
+        _check(lib().ap_index_check_status(self._h))
+
+    def debug_wait_timeout(self, polls: int = 64) -> None:
+        _check(lib().ap_debug_wait_timeout(self._h, C.c_uint32(polls)))
 
     def debug_counters(self):
         out = np.zeros(8, dtype=np.uint64)
@@ -383,6 +430,41 @@ def search_index(dense_data_path, dense_query_path, sparse_data_path, sparse_que
     return ids[:nq.value], dis[:nq.value], ndcg.value, st
 
 
+def read_fvecs(path: str) -> np.ndarray:
+    rows = C.c_uint32(0)
+    _check(lib().ap_file_read_fvecs(path.encode(), C.byref(rows), None, C.c_size_t(0)))
+    out = np.empty((rows.value, DIM), dtype=np.float32)
+    _check(lib().ap_file_read_fvecs(path.encode(), C.byref(rows), _ptr(out), C.c_size_t(out.shape[0])))
+    return out
+
+
+def read_csr(path: str, rows: int = 0):
+    """(off, idx, val) of a CSR .bin file; rows = 0 derives the row count from the file size."""
+    r, nnz = C.c_uint32(rows), C.c_uint32(0)
+    _check(lib().ap_file_read_csr(path.encode(), C.byref(r), C.byref(nnz), None, None, None))
+    off, idx, val = np.empty(r.value + 1, np.uint32), np.empty(nnz.value, np.uint32), np.empty(nnz.value, np.float32)
+    _check(lib().ap_file_read_csr(path.encode(), C.byref(r), C.byref(nnz), _ptr(off), _ptr(idx), _ptr(val)))
+    return off, idx, val
+
+
+def read_kg(path: str):
+    """(off, idx) of a knowledge-graph CSR file (entities + 1 offsets)."""
+    n_off, nnz = C.c_uint32(0), C.c_uint32(0)
+    _check(lib().ap_file_read_kg(path.encode(), C.byref(n_off), C.byref(nnz), None, None))
+    off, idx = np.empty(n_off.value, np.uint32), np.empty(nnz.value, np.uint32)
+    _check(lib().ap_file_read_kg(path.encode(), C.byref(n_off), C.byref(nnz), _ptr(off), _ptr(idx)))
+    return off, idx
+
+
+def read_id_lines(path: str, rows: int):
+    """(off, ids): line r of a text file = the ids of row r (keyword files, relevance files)."""
+    off, total = np.zeros(rows + 1, np.uint32), C.c_size_t(0)
+    _check(lib().ap_file_read_id_lines(path.encode(), C.c_uint32(rows), _ptr(off), None, C.c_size_t(0), C.byref(total)))
+    ids = np.empty(total.value, np.uint32)
+    _check(lib().ap_file_read_id_lines(path.encode(), C.c_uint32(rows), _ptr(off), _ptr(ids), C.c_size_t(ids.size), C.byref(total)))
+    return off, ids
+
+
 def ndcg(results, top_k, qrels) -> float:
     results = _np(results, np.uint32)
     off = np.zeros(len(qrels) + 1, dtype=np.uint32)
@@ -390,6 +472,69 @@ def ndcg(results, top_k, qrels) -> float:
     flat = np.asarray([t for r in qrels for t in r], dtype=np.uint32)
     return float(lib().ap_ndcg(C.c_uint32(results.shape[0]), _ptr(results), C.c_uint32(results.shape[1]),
                                C.c_uint32(top_k), _ptr(off), _ptr(flat)))
+
+
+def shard_range(n: int, shard: int, shards: int):
+    a, c = C.c_uint32(0), C.c_uint32(0)
+    lib().ap_shard_range(C.c_uint32(n), C.c_uint32(shard), C.c_uint32(shards), C.byref(a), C.byref(c))
+    return a.value, c.value
+
+
+def build_index_shard(dense_path, sparse_path, bm25_path, graph_prefix, shard, shards, device=0, iterations=0, seed=0, flags=0) -> BuildStats:
+    """Builds the graph of one corpus shard from its rows of the files and writes <graph_prefix>.<shard>.poe (shard 0
+    also writes <graph_prefix>.manifest)."""
+    o = BuildOpts(iterations=iterations, seed=seed, flags=flags)
+    st = BuildStats()
+    _check(lib().ap_build_index_shard(dense_path.encode(), sparse_path.encode(), bm25_path.encode(), graph_prefix.encode(),
+                                      C.c_uint32(shard), C.c_uint32(shards), C.c_int(device), C.byref(o), C.byref(st)))
+    return st
+
+
+def write_shard_manifest(path, n_docs, shards, graph_prefix) -> None:
+    _check(lib().ap_shard_manifest_write(path.encode(), C.c_uint32(n_docs), C.c_uint32(shards), graph_prefix.encode()))
+
+
+def read_shard_manifest(path):
+    """Returns (n_docs, [(first document, documents, graph file name), ...])."""
+    n, g = C.c_uint32(0), C.c_uint32(0)
+    _check(lib().ap_shard_manifest_read(path.encode(), C.byref(n), C.byref(g), None, None, None, C.c_uint32(0)))
+    starts, counts = np.zeros(g.value, np.uint32), np.zeros(g.value, np.uint32)
+    names = C.create_string_buffer(g.value * 256)
+    _check(lib().ap_shard_manifest_read(path.encode(), C.byref(n), C.byref(g), _ptr(starts), _ptr(counts), names, C.c_uint32(g.value)))
+    raw = names.raw
+    return n.value, [(int(starts[i]), int(counts[i]), raw[i * 256:(i + 1) * 256].split(b"\0")[0].decode()) for i in range(g.value)]
+
+
+def search_index_shard(dense_data_path, dense_query_path, sparse_data_path, sparse_query_path, bm25_data_path, bm25_query_path,
+                       manifest_path, shard, top_k, cands, sparse_weight, bm25_weight, dense_weight, device=0, max_queries=0):
+    """One shard's part of a file-level sharded search: exchange keys (uint64 [nq, top_k]) and the SearchStats."""
+    nq_cap = os.path.getsize(dense_query_path) // ((DIM + 1) * 4)
+    keys = np.empty((nq_cap, top_k), dtype=np.uint64)
+    nq, st = C.c_uint32(0), SearchStats()
+    _check(lib().ap_search_index_shard(dense_data_path.encode(), dense_query_path.encode(), sparse_data_path.encode(), sparse_query_path.encode(),
+                                       bm25_data_path.encode(), bm25_query_path.encode(), manifest_path.encode(), C.c_uint32(shard),
+                                       C.c_int(top_k), C.c_int(cands), C.c_float(sparse_weight), C.c_float(bm25_weight), C.c_float(dense_weight),
+                                       C.c_int(device), C.c_uint32(max_queries), _ptr(keys), C.byref(nq), C.byref(st)))
+    return keys[:nq.value], st
+
+
+def merge_shard_keys(keys, top_k, out_ids, out_dis, stream=None) -> None:
+    """keys: CUDA int64 tensor [shards, nq, per_shard] (the receive buffer of the all-gather); out_*: [nq, top_k]."""
+    shards, nq, per = keys.shape
+    _check(lib().ap_merge_shard_keys(C.c_int(keys.device.index or 0), C.c_uint32(shards), C.c_uint32(nq), C.c_uint32(per), _ptr(keys),
+                                     C.c_uint32(top_k), _ptr(out_ids), _ptr(out_dis), C.c_void_p(stream or 0)))
+
+
+def unpack_shard_keys(keys):
+    """Exchange keys (numpy uint64) -> (global ids uint32, fused distances float32); empty slots give (0xFFFFFFFF, 1e6)."""
+    keys = np.ascontiguousarray(keys, dtype=np.uint64)
+    ids = (keys & np.uint64(0xFFFFFFFF)).astype(np.uint32)
+    o = (keys >> np.uint64(32)).astype(np.uint32)
+    bits = np.where(o & np.uint32(0x80000000), o & np.uint32(0x7FFFFFFF), ~o)
+    dis = bits.astype(np.uint32).view(np.float32).copy()
+    empty = keys == np.uint64(0xFFFFFFFFFFFFFFFF)
+    dis[empty] = np.float32(1e6)
+    return ids, dis
 
 
 def merge_shard_results(in_ids, in_dis, top_k, out_ids, out_dis, stream=None) -> None:

@@ -1552,10 +1552,10 @@ int norms_run(ap_index *ix, float *d_power) {
 
 // prune + reverse edges + final rows + entry points, on device k-NN lists; installs the graph.
 int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const float *d_power, uint32_t *d_new_list,
-              uint32_t *d_kw, uint32_t *launches) {
+              uint32_t *d_kw, uint32_t *launches, uint32_t flags) {
     const uint32_t n = ix->n;
     if (n >= (1u << 27)) return fail(AP_ERR_LIMIT, "pruning supports up to 2^27 documents per index");
-    const bool trace = getenv("APOE_BUILD_TRACE") != nullptr;
+    const bool trace = (flags & AP_BUILD_TRACE) != 0;
     const auto tr0 = std::chrono::high_resolution_clock::now();
     auto mark = [&](const char *what) {
         if (!trace) return;
@@ -1578,7 +1578,7 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
     AP_CUDA(cudaFuncSetAttribute(prune_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
 
     // all-pairs kernel first; the step-wise kernel takes the nodes it lists (or all of them when the tables alone
-    // leave no room for a staging area, or when APOE_PRUNE_KERNEL=stepwise asks for it)
+    // leave no room for a staging area, or when AP_BUILD_PRUNE_STEPWISE asks for it)
     Prune2Args q{};
     q.p = a;
     q.o_ip = 0; q.o_kw = kK * kK * 4; q.p.o_own = q.o_kw + kK * kK;
@@ -1589,8 +1589,7 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
     while (groups > 1 && q.p.o_tab + (size_t)groups * tabn * 8 + 96 * 1024 > avail) groups >>= 1;   // key lines are 1, 2 or 4 wide
     q.groups = groups;
     q.o_region = (uint32_t)((q.p.o_tab + (size_t)groups * tabn * 8 + 127) / 128 * 128);
-    const char *force = getenv("APOE_PRUNE_KERNEL");
-    const bool pairs_ok = avail >= (size_t)q.o_region + 64 * 1024 && !(force && !strcmp(force, "stepwise"));
+    const bool pairs_ok = avail >= (size_t)q.o_region + 64 * 1024 && !(flags & AP_BUILD_PRUNE_STEPWISE);
     uint32_t n_step = n;
     uint32_t *ovf_list = nullptr, *ovf_cnt = nullptr;
     if (pairs_ok) {
@@ -1754,7 +1753,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     float phase_ms[4] = {0, 0, 0, 0};  // sample + lists, dense tiles, sparse + proposals, merge
     uint32_t it = 0;
     unsigned long long prev_updates = 0;
-    const bool trace = getenv("APOE_BUILD_TRACE") != nullptr;   // per-round progress on stderr
+    const bool trace = (o.flags & AP_BUILD_TRACE) != 0;   // per-round progress on stderr
     for (; it < iters; ++it) {
         AP_CUDA(cudaMemsetAsync(k.scnt, 0, (size_t)n * 16));
         AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
@@ -1799,7 +1798,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     if (!ix->knn_dis) AP_CUDA(cudaMalloc(&ix->knn_dis, (size_t)n * kK * 4));
     knn_finish_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k, knn_ids); ++launches;
     AP_CUDA(cudaMemcpyAsync(ix->knn_dis, k.dis, (size_t)n * kK * 4, cudaMemcpyDeviceToDevice));
-    AP_TRY(prune_run(ix, knn_ids, ix->knn_dis, power, nullptr, nullptr, &launches));
+    AP_TRY(prune_run(ix, knn_ids, ix->knn_dis, power, nullptr, nullptr, &launches, o.flags));
     const auto t2 = std::chrono::high_resolution_clock::now();
 
     uint32_t ew = 0;
@@ -1855,8 +1854,8 @@ int ap_index_norms(ap_index *ix, float *out) {
     return AP_OK;
 }
 
-int ap_index_prune(ap_index *ix, const uint32_t *knn_ids, const float *knn_dis, const float *power, uint32_t *new_list,
-                   uint32_t *keyword_edges, uint32_t *rows) {
+int ap_index_prune(ap_index *ix, const uint32_t *knn_ids, const float *knn_dis, const float *power, uint32_t flags,
+                   uint32_t *new_list, uint32_t *keyword_edges, uint32_t *rows) {
     if (!ix || !knn_ids || !knn_dis || !power) return fail(AP_ERR_ARG, "null argument");
     const uint32_t n = ix->n;
     for (size_t i = 0; i < (size_t)n * kK; ++i)
@@ -1871,7 +1870,7 @@ int ap_index_prune(ap_index *ix, const uint32_t *knn_ids, const float *knn_dis, 
     AP_CUDA(cudaMemcpy(d_dis, knn_dis, (size_t)n * kK * 4, cudaMemcpyHostToDevice));
     AP_CUDA(cudaMemcpy(d_pow, power, (size_t)n * 4, cudaMemcpyHostToDevice));
     uint32_t launches = 0;
-    AP_TRY(prune_run(ix, d_knn, d_dis, d_pow, d_nl, d_kw, &launches));
+    AP_TRY(prune_run(ix, d_knn, d_dis, d_pow, d_nl, d_kw, &launches, flags));
     if (new_list) AP_CUDA(cudaMemcpy(new_list, d_nl, (size_t)n * AP_DEGREE * 4, cudaMemcpyDeviceToHost));
     if (keyword_edges) AP_CUDA(cudaMemcpy(keyword_edges, d_kw, (size_t)n * 33 * 4, cudaMemcpyDeviceToHost));
     if (rows) AP_CUDA(cudaMemcpy(rows, ix->graph, (size_t)n * AP_ROW * 4, cudaMemcpyDeviceToHost));

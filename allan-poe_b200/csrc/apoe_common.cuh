@@ -147,6 +147,8 @@ struct SearchLaunch {
     uint32_t *out_ids;
     float *out_dis;
     cudaStream_t stream;
+    unsigned long long *out_keys = nullptr;   // sharded search: nq x key_top_k packed (ordered distance, global id) words
+    uint32_t key_top_k = 0, id_base = 0;
     uint32_t *ctl = nullptr;            // control words of the kernel (next query, error word); null = the index's own
     unsigned long long *cnt = nullptr;  // counters; null = the index's own
 };
@@ -156,7 +158,7 @@ int distances_launch(ap_index *ix, const SearchLaunch &L, size_t n_pairs, const 
 
 int build_run(ap_index *ix, const ap_build_opts *opts, ap_build_stats *stats);
 int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const float *d_power, uint32_t *d_new_list,
-              uint32_t *d_kw, uint32_t *launches);
+              uint32_t *d_kw, uint32_t *launches, uint32_t flags);
 int norms_run(ap_index *ix, float *d_power);
 int ensure_build_copy(ap_index *ix, float scale);
 

@@ -90,6 +90,16 @@ __global__ void fat_graph_kernel(uint32_t n, const uint32_t *__restrict__ graph,
     fat[i] = e;
 }
 
+// Test hook for the bounded waits: one thread waits on an mbarrier that nothing ever completes.  After `limit`
+// polls the wait gives up, raises the error word and the kernel returns normally -- the path every copy wait of
+// the search and build kernels takes when its data does not arrive.
+__global__ void wait_timeout_kernel(uint32_t *err_word, uint32_t limit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait_bounded(&bar, 0, err_word, 1u, limit);
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // creation
 // ---------------------------------------------------------------------------------------------------------
@@ -538,6 +548,28 @@ int ap_index_set_kg(ap_index *ix, uint32_t n_entities, const uint32_t *e2e_off, 
     return AP_OK;
 }
 
+int ap_index_check_status(ap_index *ix) {
+    if (!ix) return fail(AP_ERR_ARG, "null index");
+    AP_CUDA(cudaSetDevice(ix->device));
+    uint32_t word = 0;
+    AP_CUDA(cudaMemcpy(&word, ix->d_ctl + 1, 4, cudaMemcpyDeviceToHost));   // default stream: after the work queued there
+    if (word != 0) {
+        AP_CUDA(cudaMemset(ix->d_ctl + 1, 0, 4));
+        return fail(AP_ERR_DEVICE, "a kernel raised error word %u (%s)", word,
+                    word == 1 ? "a bulk copy did not complete within the wait limit" : word == 2 ? "a record is larger than the staging arena" : "a bounded wait ran out");
+    }
+    return AP_OK;
+}
+
+int ap_debug_wait_timeout(ap_index *ix, uint32_t polls) {
+    if (!ix) return fail(AP_ERR_ARG, "null index");
+    AP_CUDA(cudaSetDevice(ix->device));
+    wait_timeout_kernel<<<1, 32>>>(ix->d_ctl + 1, polls > 4096u ? 4096u : polls);
+    AP_CUDA(cudaGetLastError());
+    AP_CUDA(cudaDeviceSynchronize());
+    return AP_OK;
+}
+
 int ap_effective_weights(const ap_index *ix, const ap_queries *q, float *sparse_weight, float *bm25_weight, float *dense_weight) {
     if (!ix || !q || !sparse_weight || !bm25_weight || !dense_weight) return fail(AP_ERR_ARG, "null argument");
     return effective_weights_host(ix, q, sparse_weight, bm25_weight, dense_weight);
@@ -557,11 +589,12 @@ static int host_query_limits(const ap_index *ix, const ap_queries *q, uint32_t f
     return AP_OK;
 }
 
-int ap_search_host(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids, float *out_dis,
-                   ap_search_stats *stats) {
+static int search_host_impl(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids, float *out_dis,
+                            unsigned long long *out_keys, uint32_t key_top_k, uint32_t id_base, ap_search_stats *stats) {
     const auto t0 = std::chrono::high_resolution_clock::now();
     AP_TRY(check_search_args(ix, q, opts));
-    if (!out_ids || !out_dis) return fail(AP_ERR_ARG, "null output pointer");
+    if ((!out_ids || !out_dis) && !out_keys) return fail(AP_ERR_ARG, "null output pointer");
+    if (out_keys && (key_top_k == 0 || key_top_k > opts->cands)) return fail(AP_ERR_ARG, "top_k = %u must lie in [1, cands = %u]", key_top_k, opts->cands);
     AP_CUDA(cudaSetDevice(ix->device));
     float ws = opts->sparse_weight, wb = opts->bm25_weight, wd = opts->dense_weight;
     if (!(opts->flags & AP_SEARCH_RAW_WEIGHTS)) AP_TRY(effective_weights_host(ix, q, &ws, &wb, &wd));
@@ -595,8 +628,15 @@ int ap_search_host(ap_index *ix, const ap_queries *q, const ap_search_opts *opts
         AP_TRY(upload(7, q->ent_off, (size_t)(nq + 1) * 4, (const void **)&L.qe_off));
         AP_TRY(upload(8, q->ent_idx, (size_t)q->ent_off[nq] * 4, (const void **)&L.qe_idx));
     }
-    AP_TRY(ws_reserve(ix, 9, (size_t)nq * cands * 4, &p)); L.out_ids = (uint32_t *)p;
-    AP_TRY(ws_reserve(ix, 10, (size_t)nq * cands * 4, &p)); L.out_dis = (float *)p;
+    const bool want_lists = out_ids && out_dis;
+    if (want_lists) {
+        AP_TRY(ws_reserve(ix, 9, (size_t)nq * cands * 4, &p)); L.out_ids = (uint32_t *)p;
+        AP_TRY(ws_reserve(ix, 10, (size_t)nq * cands * 4, &p)); L.out_dis = (float *)p;
+    }
+    if (out_keys) {
+        AP_TRY(ws_reserve(ix, 14, (size_t)nq * key_top_k * 8, &p)); L.out_keys = (unsigned long long *)p;
+        L.key_top_k = key_top_k; L.id_base = id_base;
+    }
     L.nq = nq; L.max_qs = mqs; L.max_qb = mqb;
     L.w_sparse = ws; L.w_bm25 = wb; L.w_dense = wd; L.kg_weight = opts->kg_weight;
     L.cands = cands; L.flags = (opts->flags & ~(AP_SEARCH_KEYWORD | AP_SEARCH_KG)) | mode; L.path = path;
@@ -606,15 +646,18 @@ int ap_search_host(ap_index *ix, const ap_queries *q, const ap_search_opts *opts
     AP_CUDA(cudaEventRecord(ix->ev0, st));
     AP_TRY(search_launch(ix, L, &launches));
     AP_CUDA(cudaEventRecord(ix->ev1, st));
-    AP_CUDA(cudaMemcpyAsync(out_ids, L.out_ids, (size_t)nq * cands * 4, cudaMemcpyDeviceToHost, st));
-    AP_CUDA(cudaMemcpyAsync(out_dis, L.out_dis, (size_t)nq * cands * 4, cudaMemcpyDeviceToHost, st));
+    if (want_lists) {
+        AP_CUDA(cudaMemcpyAsync(out_ids, L.out_ids, (size_t)nq * cands * 4, cudaMemcpyDeviceToHost, st));
+        AP_CUDA(cudaMemcpyAsync(out_dis, L.out_dis, (size_t)nq * cands * 4, cudaMemcpyDeviceToHost, st));
+    }
+    if (out_keys) AP_CUDA(cudaMemcpyAsync(out_keys, L.out_keys, (size_t)nq * key_top_k * 8, cudaMemcpyDeviceToHost, st));
     AP_TRY(read_back_status(ix, stats, st));
     if (stats) {
         float ms = 0.f;
         AP_CUDA(cudaEventElapsedTime(&ms, ix->ev0, ix->ev1));
         stats->kernel_ms = ms;
         stats->eff_sparse = ws; stats->eff_bm25 = wb; stats->eff_dense = wd; stats->path = path; stats->launches = launches;
-        const size_t d2h = (size_t)nq * cands * 8;
+        const size_t d2h = (want_lists ? (size_t)nq * cands * 8 : 0) + (out_keys ? (size_t)nq * key_top_k * 8 : 0);
         stats->h2d_bytes_lo = (uint32_t)h2d; stats->h2d_bytes_hi = (uint32_t)((uint64_t)h2d >> 32);
         stats->d2h_bytes_lo = (uint32_t)d2h; stats->d2h_bytes_hi = (uint32_t)((uint64_t)d2h >> 32);
         stats->total_ms = std::chrono::duration<double, std::milli>(std::chrono::high_resolution_clock::now() - t0).count();
@@ -622,11 +665,25 @@ int ap_search_host(ap_index *ix, const ap_queries *q, const ap_search_opts *opts
     return AP_OK;
 }
 
-int ap_search_device(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids, float *out_dis,
-                     void *stream, ap_search_stats *stats) {
+int ap_search_host(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids, float *out_dis,
+                   ap_search_stats *stats) {
+    if (!out_ids || !out_dis) return fail(AP_ERR_ARG, "null output pointer");
+    return search_host_impl(ix, q, opts, out_ids, out_dis, nullptr, 0, 0, stats);
+}
+
+int ap_search_shard_host(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t id_base, uint32_t top_k,
+                         unsigned long long *out_keys, uint32_t *out_ids, float *out_dis, ap_search_stats *stats) {
+    if (!out_keys) return fail(AP_ERR_ARG, "null output pointer");
+    if (ix && (uint64_t)id_base + ix->n > 0xFFFFFFFFull) return fail(AP_ERR_ARG, "id base %u + %u documents leaves the 32-bit id range", id_base, ix->n);
+    return search_host_impl(ix, q, opts, out_ids, out_dis, out_keys, top_k, id_base, stats);
+}
+
+static int search_device_impl(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids, float *out_dis,
+                              unsigned long long *out_keys, uint32_t key_top_k, uint32_t id_base, void *stream, ap_search_stats *stats) {
     const auto t0 = std::chrono::high_resolution_clock::now();
     AP_TRY(check_search_args(ix, q, opts));
-    if (!out_ids || !out_dis) return fail(AP_ERR_ARG, "null output pointer");
+    if ((!out_ids || !out_dis) && !out_keys) return fail(AP_ERR_ARG, "null output pointer");
+    if (out_keys && (key_top_k == 0 || key_top_k > opts->cands)) return fail(AP_ERR_ARG, "top_k = %u must lie in [1, cands = %u]", key_top_k, opts->cands);
     AP_CUDA(cudaSetDevice(ix->device));
     cudaStream_t st = (cudaStream_t)stream;
     const float ws = opts->sparse_weight, wb = opts->bm25_weight, wd = opts->dense_weight;
@@ -650,7 +707,8 @@ int ap_search_device(ap_index *ix, const ap_queries *q, const ap_search_opts *op
     L.w_sparse = ws; L.w_bm25 = wb; L.w_dense = wd; L.kg_weight = opts->kg_weight;
     L.cands = opts->cands; L.flags = (opts->flags & ~(AP_SEARCH_KEYWORD | AP_SEARCH_KG)) | mode; L.path = path;
     L.arena_bytes = opts->arena_bytes; L.ctas_per_sm = opts->ctas_per_sm; L.stream = st;
-    L.out_ids = out_ids; L.out_dis = out_dis;
+    L.out_ids = out_dis ? out_ids : nullptr; L.out_dis = out_ids ? out_dis : nullptr;
+    L.out_keys = out_keys; L.key_top_k = key_top_k; L.id_base = id_base;
     uint32_t launches = 0;
     AP_CUDA(cudaMemsetAsync(ix->d_cnt, 0, 64, st));
     if (stats) AP_CUDA(cudaEventRecord(ix->ev0, st));
@@ -665,6 +723,19 @@ int ap_search_device(ap_index *ix, const ap_queries *q, const ap_search_opts *op
         stats->total_ms = std::chrono::duration<double, std::milli>(std::chrono::high_resolution_clock::now() - t0).count();
     }
     return AP_OK;
+}
+
+int ap_search_device(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids, float *out_dis,
+                     void *stream, ap_search_stats *stats) {
+    if (!out_ids || !out_dis) return fail(AP_ERR_ARG, "null output pointer");
+    return search_device_impl(ix, q, opts, out_ids, out_dis, nullptr, 0, 0, stream, stats);
+}
+
+int ap_search_shard_device(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t id_base, uint32_t top_k,
+                           unsigned long long *out_keys, uint32_t *out_ids, float *out_dis, void *stream, ap_search_stats *stats) {
+    if (!out_keys) return fail(AP_ERR_ARG, "null output pointer");
+    if (ix && (uint64_t)id_base + ix->n > 0xFFFFFFFFull) return fail(AP_ERR_ARG, "id base %u + %u documents leaves the 32-bit id range", id_base, ix->n);
+    return search_device_impl(ix, q, opts, out_ids, out_dis, out_keys, top_k, id_base, stream, stats);
 }
 
 int ap_fused_distances(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, size_t n_pairs,

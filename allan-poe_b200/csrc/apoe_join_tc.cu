@@ -225,11 +225,8 @@ int join_dense_tc_launch(ap_index *ix, uint32_t node0, uint32_t nodes, const uin
                          cudaStream_t stream) {
     TcArgs a{node0, nodes, plist, pcnt, ix->meta, ix->rec_build, D, ix->d_ctl + 1};
     const size_t smem = (size_t)kStages * kStageBytes + 1024;
-    static bool configured = false;
-    if (!configured) {
-        AP_CUDA(cudaFuncSetAttribute(join_dense_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-        configured = true;
-    }
+    // the attribute belongs to the current device's context, so it is set on every launch (builds on several GPUs in one process)
+    AP_CUDA(cudaFuncSetAttribute(join_dense_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const uint32_t tiles = (nodes + 1) / 2;
     const uint32_t grid = std::min<uint32_t>(tiles, (uint32_t)ix->num_sms);
     if (grid == 0) return AP_OK;

@@ -48,6 +48,8 @@ struct SearchArgs {
     uint32_t cands;
     uint32_t *out_ids;
     float *out_dis;
+    unsigned long long *out_keys;  // corpus-sharded search: nq x key_top_k packed (ordered distance, global id), or null
+    uint32_t key_top_k, id_base;   // global id = local id + id_base
     uint32_t *ctl;            // [0] next query, [1] error word
     unsigned long long *cnt;  // [0] expansions, [1] evaluations, [2] gathered bytes
     uint32_t arena_bytes;
@@ -100,6 +102,15 @@ __device__ __forceinline__ uint32_t vis_insert(uint32_t *tab, uint32_t mask, uin
         idx = (idx + 1) & mask;
     }
     return 0;
+}
+
+// order-preserving map of a float onto unsigned integers (ascending floats -> ascending words)
+__device__ __forceinline__ uint32_t f2ord_s(float f) { const uint32_t b = __float_as_uint(f); return (b & 0x80000000u) ? ~b : (b | 0x80000000u); }
+__device__ __forceinline__ float ord2f_s(uint32_t o) { return __uint_as_float((o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o); }
+// One result of a shard as the exchange step ships it: (ordered distance, global id) in one word, so that keys of
+// different shards compare like (distance, id); an empty pool slot becomes the all-ones word.
+__device__ __forceinline__ unsigned long long shard_key(uint32_t local_id, float dis, uint32_t n, uint32_t id_base) {
+    return local_id < n ? (((unsigned long long)f2ord_s(dis) << 32) | (unsigned long long)(local_id + id_base)) : ~0ull;
 }
 
 constexpr int kScoreBatch = 2;  // records a warp scores side by side (independent instruction streams)
@@ -787,8 +798,10 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
         // ---- results (ref: src/query.cu:566-569; keyword ordering :1465-1481) ---------------------------------
         if (!KW) {
             for (uint32_t i = tid; i < topm; i += kSearchThreads) {
-                a.out_ids[(size_t)qi * topm + i] = pool_id[i] & 0x7FFFFFFFu;
-                a.out_dis[(size_t)qi * topm + i] = pool_dis[i];
+                const uint32_t id = pool_id[i] & 0x7FFFFFFFu;
+                const float d = pool_dis[i];
+                if (a.out_ids) { a.out_ids[(size_t)qi * topm + i] = id; a.out_dis[(size_t)qi * topm + i] = d; }
+                if (a.out_keys && i < a.key_top_k) a.out_keys[(size_t)qi * a.key_top_k + i] = shard_key(id, d, a.n, a.id_base);
             }
         } else {
             if (warp == 0) {
@@ -803,16 +816,18 @@ __global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchA
                     const uint32_t bal = __ballot_sync(kFull, h);
                     if (h) {
                         const uint32_t o = nout + __popc(bal & ((1u << lane) - 1u));
-                        a.out_ids[(size_t)qi * topm + o] = pid & 0x3FFFFFFFu;
-                        a.out_dis[(size_t)qi * topm + o] = pool_dis[b0 + lane];
+                        if (a.out_ids) { a.out_ids[(size_t)qi * topm + o] = pid & 0x3FFFFFFFu; a.out_dis[(size_t)qi * topm + o] = pool_dis[b0 + lane]; }
+                        if (a.out_keys && o < a.key_top_k) a.out_keys[(size_t)qi * a.key_top_k + o] = shard_key(pid & 0x3FFFFFFFu, pool_dis[b0 + lane], a.n, a.id_base);
                     }
                     nout += __popc(bal);
                 }
                 __syncwarp();
                 for (uint32_t i = nout + lane; i < topm; i += 32) {
                     const uint32_t s = i - nout;
-                    a.out_ids[(size_t)qi * topm + i] = s < kKeywordRing ? (c.kw_id[s] & 0x3FFFFFFFu) : 0x3FFFFFFFu;
-                    a.out_dis[(size_t)qi * topm + i] = s < kKeywordRing ? c.kw_dis[s] : kInfDis;
+                    const uint32_t id = s < kKeywordRing ? (c.kw_id[s] & 0x3FFFFFFFu) : 0x3FFFFFFFu;
+                    const float d = s < kKeywordRing ? c.kw_dis[s] : kInfDis;
+                    if (a.out_ids) { a.out_ids[(size_t)qi * topm + i] = id; a.out_dis[(size_t)qi * topm + i] = d; }
+                    if (a.out_keys && i < a.key_top_k) a.out_keys[(size_t)qi * a.key_top_k + i] = shard_key(id, d, a.n, a.id_base);
                 }
             }
         }
@@ -967,6 +982,7 @@ static void fill_args(ap_index *ix, const SearchLaunch &L, SearchArgs &a) {
     a.qe_off = L.qe_off; a.qe_idx = L.qe_idx;
     a.nq = L.nq; a.w_sparse = L.w_sparse; a.w_bm25 = L.w_bm25; a.w_dense = L.w_dense; a.kg_weight = L.kg_weight;
     a.cands = L.cands; a.out_ids = L.out_ids; a.out_dis = L.out_dis;
+    a.out_keys = L.out_keys; a.key_top_k = L.key_top_k; a.id_base = L.id_base;
     a.ctl = L.ctl ? L.ctl : ix->d_ctl; a.cnt = L.cnt ? L.cnt : ix->d_cnt;
 }
 
@@ -1036,8 +1052,6 @@ int distances_launch(ap_index *ix, const SearchLaunch &L, size_t n_pairs, const 
 // query; the k smallest (distance, id) keys are extracted in ascending order, each round taking the smallest key
 // above the previous one (document ids are unique across shards, so keys are distinct).
 // ---------------------------------------------------------------------------------------------------------
-__device__ __forceinline__ uint32_t f2ord_s(float f) { const uint32_t b = __float_as_uint(f); return (b & 0x80000000u) ? ~b : (b | 0x80000000u); }
-
 __global__ void merge_shards_kernel(uint32_t shards, uint32_t nq, uint32_t per, const uint32_t *__restrict__ in_ids,
                                     const float *__restrict__ in_dis, uint32_t top_k, uint32_t *__restrict__ out_ids,
                                     float *__restrict__ out_dis) {
@@ -1070,7 +1084,45 @@ __global__ void merge_shards_kernel(uint32_t shards, uint32_t nq, uint32_t per, 
     }
 }
 
+// The same merge on packed keys, as the sharded search ships them (one all-gather of shards x nq x per words): one
+// thread per key counts the keys that precede it -- smaller, or equal with a lower position, which only empty slots
+// are -- and writes itself to that rank when it is below top_k.  A single pass over shards x per keys per query,
+// independent of any order inside the lists.
+__global__ void merge_shard_keys_kernel(uint32_t shards, uint32_t nq, uint32_t per, const unsigned long long *__restrict__ keys,
+                                        uint32_t top_k, uint32_t *__restrict__ out_ids, float *__restrict__ out_dis) {
+    const uint32_t total = shards * per;
+    const size_t t = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (t >= (size_t)nq * total) return;
+    const uint32_t q = (uint32_t)(t / total), e = (uint32_t)(t % total);
+    const uint32_t s = e / per, j = e % per;
+    const unsigned long long mine = keys[((size_t)s * nq + q) * per + j];
+    uint32_t rank = 0;
+    for (uint32_t s2 = 0; s2 < shards; ++s2) {
+        const unsigned long long *row = keys + ((size_t)s2 * nq + q) * per;
+        for (uint32_t j2 = 0; j2 < per; ++j2) {
+            const unsigned long long other = __ldg(row + j2);
+            rank += (other < mine) || (other == mine && s2 * per + j2 < e);
+        }
+    }
+    if (rank < top_k) {
+        out_ids[(size_t)q * top_k + rank] = mine == ~0ull ? kEmpty : (uint32_t)mine;
+        out_dis[(size_t)q * top_k + rank] = mine == ~0ull ? kInfDis : ord2f_s((uint32_t)(mine >> 32));
+    }
+}
+
 }  // namespace apoe
+
+extern "C" int ap_merge_shard_keys(int device, uint32_t shards, uint32_t nq, uint32_t per_shard, const unsigned long long *keys,
+                                   uint32_t top_k, uint32_t *out_ids, float *out_dis, void *stream) {
+    using namespace apoe;
+    if (!keys || !out_ids || !out_dis) return fail(AP_ERR_ARG, "null pointer");
+    if (shards == 0 || nq == 0 || per_shard == 0 || top_k == 0 || top_k > shards * per_shard) return fail(AP_ERR_ARG, "empty merge or top_k beyond the gathered entries");
+    AP_CUDA(cudaSetDevice(device));
+    const size_t threads = (size_t)nq * shards * per_shard;
+    merge_shard_keys_kernel<<<(uint32_t)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(shards, nq, per_shard, keys, top_k, out_ids, out_dis);
+    AP_CUDA(cudaGetLastError());
+    return AP_OK;
+}
 
 extern "C" int ap_merge_shard_results(int device, uint32_t shards, uint32_t nq, uint32_t per_shard, const uint32_t *in_ids,
                                       const float *in_dis, uint32_t top_k, uint32_t *out_ids, float *out_dis, void *stream) {

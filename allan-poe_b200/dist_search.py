@@ -50,6 +50,24 @@ def merge_topk_reference(g_ids: torch.Tensor, g_dis: torch.Tensor, top_k: int):
     return torch.gather(ids_s, 1, order).to(torch.int32), torch.gather(dis_s, 1, order).to(torch.float32)
 
 
+def exchange_and_merge(g_keys: torch.Tensor, rank: int, out_ids: torch.Tensor, out_dis: torch.Tensor, top_k: int, group=None) -> None:
+    """The exchange step of the sharded search on packed keys.  g_keys: int64 [world, nq, per]; slice `rank` already
+    holds this shard's keys (the search kernel wrote them there).  One all-gather in place, then one merge kernel."""
+    import apoe
+    dist.all_gather_into_tensor(g_keys.view(-1), g_keys[rank].view(-1), group=group)
+    apoe.merge_shard_keys(g_keys, top_k, out_ids, out_dis, torch.cuda.current_stream().cuda_stream)
+
+
+def merge_keys_reference(g_keys: torch.Tensor, top_k: int):
+    """Plain torch restatement of the key merge: the top_k smallest keys of every query as unsigned 64-bit words (int64
+    tensors hold them; flipping the sign bit makes the signed order the unsigned one).  Returns the merged keys
+    [nq, top_k] as int64 bit patterns."""
+    w, nq, per = g_keys.shape
+    flat = g_keys.permute(1, 0, 2).reshape(nq, w * per)
+    flipped = flat ^ torch.iinfo(torch.int64).min
+    return (torch.sort(flipped, dim=1).values[:, :top_k]) ^ torch.iinfo(torch.int64).min
+
+
 def gather_and_merge(local_ids, local_dis, shard_start, g_ids, g_dis, out_ids, out_dis, top_k, shard_size=None, group=None):
     """One exchange step of the sharded search, on device tensors."""
     import apoe

@@ -22,6 +22,7 @@ import threading
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
 sys.path.insert(0, os.path.join(ROOT, "allan-poe_b200"))
 
 import numpy as np  # noqa: E402

@@ -58,6 +58,11 @@ typedef struct {
                                      and its reverse-edge half (src/index.cu:699-711) carry different neighbours */
 #define AP_BUILD_REVERSE_PASS 16u /* with AP_BUILD_SHARED_PAIRS: closing reverse merge as merge_reverse_plus
                                      (src/index.cu:386-478) */
+#define AP_BUILD_PRUNE_STEPWISE 32u /* prune every node with the step-wise kernel (the form of src/index.cu:613-676) instead
+                                     of the all-pairs kernel; same result, used to cross-check the two */
+#define AP_BUILD_TRACE 64u        /* per-round and per-phase progress lines on stderr */
+#define AP_BUILD_DETERMINISTIC 128u /* one seed, one graph: reverse samples and proposals are kept by an order-independent
+                                     rule (smallest key per hashed slot) instead of first come, first served */
 
 typedef struct {
     uint32_t iterations;   /* NN-Descent rounds; 0 = library default (8) */
@@ -207,6 +212,11 @@ typedef struct {
 } ap_ingest_stats;
 int ap_index_create_files(ap_index **out, int device, const char *dense_path, const char *sparse_path,
                           const char *bm25_path, uint32_t flags, uint32_t threads, ap_ingest_stats *stats);
+/* The same for documents [row_start, row_start + row_count) of the files only (a corpus shard; ids inside the index
+ * are local: document row_start becomes id 0).  row_count = 0 reads everything. */
+int ap_index_create_files_range(ap_index **out, int device, const char *dense_path, const char *sparse_path,
+                                const char *bm25_path, uint32_t row_start, uint32_t row_count, uint32_t flags,
+                                uint32_t threads, ap_ingest_stats *stats);
 /* Corpus already in device memory of `device` (same layouts). */
 int ap_index_create_device(ap_index **out, int device, uint32_t n, const float *dense, ap_csr sparse, ap_csr bm25,
                            uint32_t flags);
@@ -234,7 +244,8 @@ int ap_index_norms(ap_index *ix, float *out);
  * (n x 33: count + 32 ids) and final rows (n x 40) to host memory; any output may be NULL.  Also installs the rows
  * and the entry points derived from `power` as the index's graph. */
 int ap_index_prune(ap_index *ix, const uint32_t *knn_ids, const float *knn_dis, const float *power,
-                   uint32_t *new_list, uint32_t *keyword_edges, uint32_t *rows);
+                   uint32_t flags /* AP_BUILD_PRUNE_STEPWISE | AP_BUILD_TRACE */, uint32_t *new_list,
+                   uint32_t *keyword_edges, uint32_t *rows);
 
 /* Knowledge graph for AP_SEARCH_KG (ref: load_kg_graph src/query.cu:89-108 and the uploads of :1963-1980).
  * Host pointers; entity->entity and entity->doc CSRs over n_entities rows. */
@@ -250,10 +261,16 @@ int ap_effective_weights(const ap_index *ix, const ap_queries *q, float *sparse_
 int ap_search_host(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids, float *out_dis,
                    ap_search_stats *stats);
 /* Same with every query and result pointer in device memory; `stream` is a cudaStream_t (NULL = default stream).
- * Weights are used as given unless the host-side normalisation sample is available (see AP_SEARCH_RAW_WEIGHTS).
- * Asynchronous with respect to the host unless stats != NULL. */
+ * The weights are used as given (the auto-normalisation needs host copies of the first 100 queries: run
+ * ap_effective_weights on those and pass its result).  With stats == NULL the call only enqueues the kernel and
+ * returns: a device-side error (AP_ERR_DEVICE) of such a call is reported by the next call that passes stats, or by
+ * ap_index_check_status. */
 int ap_search_device(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t *out_ids, float *out_dis,
                      void *stream, ap_search_stats *stats);
+
+/* Waits for the work queued on the default stream and reports (and clears) the kernels' error word: AP_ERR_DEVICE when
+ * a bounded wait of an earlier asynchronous call gave up or a record did not fit its staging area, else AP_OK. */
+int ap_index_check_status(ap_index *ix);
 
 /* No counterpart in the reference.  ap_search_host for callers that cannot allocate device memory while they serve:
  * a process whose GPU memory is entirely owned by another pool (cudaMalloc would fail), or a query loop that cannot
@@ -272,9 +289,63 @@ int ap_search_host_static(ap_index *ix, const ap_queries *q, const ap_search_opt
 int ap_fused_distances(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, size_t n_pairs,
                        const uint32_t *pair_query, const uint32_t *pair_doc, float *out);
 
-/* ref: cal_precision, src/query.cu:111-145.  results: nq x stride ids (first top_k used); qrels: CSR of relevant ids. */
+/* ref: cal_precision, src/query.cu:111-145, with its float arithmetic (the printed figure has the reference's digits).
+ * results: nq x stride ids (first top_k used); qrels: CSR of relevant ids.  A query without relevant ids adds nothing
+ * (the reference divides 0 by 0 there). */
 double ap_ndcg(uint32_t nq, const uint32_t *results, uint32_t stride, uint32_t top_k, const uint32_t *qrel_off,
                const uint32_t *qrel_ids);
+
+/* ---- the reference's file formats, parsed into host memory (no device needed) ------------------------- */
+/* Each call may be made with null arrays first to learn the sizes.
+ * ref: load_data, include/utils.cuh:361-378 (.fvecs: per row an int32 dimension word and 1024 floats). */
+int ap_file_read_fvecs(const char *path, uint32_t *rows, float *out /* rows x 1024 */, size_t cap_rows);
+/* ref: load_sparse_data, include/utils.cuh:380-398 (u32 nnz | u32 off[rows+1] | u32 idx[nnz] | f32 val[nnz]).  The file
+ * does not store its row count (the reference takes it from the dense file): pass it in *rows, or 0 to have it derived
+ * from the file size. */
+int ap_file_read_csr(const char *path, uint32_t *rows, uint32_t *nnz, uint32_t *off, uint32_t *idx, float *val);
+/* ref: load_kg_graph, src/query.cu:89-108 (u32 n_off | u32 nnz | u32 off[n_off] | u32 idx[nnz]; n_off = entities + 1). */
+int ap_file_read_kg(const char *path, uint32_t *n_off, uint32_t *nnz, uint32_t *off, uint32_t *idx);
+/* ref: load_txt, src/query.cu:65-86 (text, line r = the ids of row r: required keywords or relevant documents).
+ * off: rows + 1 entries; ids (capacity cap, may be NULL): the ids of all rows back to back; *total their number. */
+int ap_file_read_id_lines(const char *path, uint32_t rows, uint32_t *off, uint32_t *ids, size_t cap, size_t *total);
+
+/* ---- corpus-sharded search ------------------------------------------------------------------------------ */
+/* No counterpart in the reference (one GPU, one index).  Documents [start, start + count) of an n-document corpus belong to
+ * shard `shard` of `shards`: contiguous ranges whose sizes differ by at most one. */
+void ap_shard_range(uint32_t n, uint32_t shard, uint32_t shards, uint32_t *start, uint32_t *count);
+/* ap_search_device on one shard, with the exchange format written by the search kernel itself: for every query the
+ * best top_k pool entries as 64-bit keys (order-preserving bits of the fused distance << 32 | local id + id_base; an
+ * empty slot is the all-ones word), out_keys: nq x top_k, device.  out_ids / out_dis (nq x cands) may be NULL.  The
+ * effective weights must be the same on every shard (ap_effective_weights on global documents 0..99). */
+int ap_search_shard_device(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t id_base, uint32_t top_k,
+                           unsigned long long *out_keys, uint32_t *out_ids, float *out_dis, void *stream, ap_search_stats *stats);
+/* The same with host buffers (queries in, keys out: nq x top_k), through the staging of ap_search_host. */
+int ap_search_shard_host(ap_index *ix, const ap_queries *q, const ap_search_opts *opts, uint32_t id_base, uint32_t top_k,
+                         unsigned long long *out_keys, uint32_t *out_ids, float *out_dis, ap_search_stats *stats);
+/* Shards on disk: one index.poe per shard (local ids, the byte layout of src/index.cu:928-939) named
+ * <graph_prefix>.<shard>.poe, and the text manifest <graph_prefix>.manifest (written by shard 0) that lists the
+ * document range and the file of every shard.  ap_build_index_shard reads only its own rows of the corpus files. */
+#define AP_SHARD_NAME_BYTES 256
+int ap_build_index_shard(const char *dense_data_path, const char *sparse_data_path, const char *bm25_data_path,
+                         const char *graph_prefix, uint32_t shard, uint32_t shards, int device, const ap_build_opts *opts,
+                         ap_build_stats *stats);
+int ap_shard_manifest_write(const char *manifest_path, uint32_t n_docs, uint32_t shards, const char *graph_prefix);
+/* starts / counts: cap_shards entries, names: cap_shards x AP_SHARD_NAME_BYTES characters; all three may be NULL to
+ * learn *n_docs and *shards first.  Rejects manifests whose ranges leave gaps or overlap. */
+int ap_shard_manifest_read(const char *manifest_path, uint32_t *n_docs, uint32_t *shards, uint32_t *starts, uint32_t *counts,
+                           char *names, uint32_t cap_shards);
+/* One shard's part of a sharded search_index call: loads the shard's documents and its graph file (looked up in the
+ * manifest), normalises the weights on global documents 0..99 (so every shard scores alike), searches every query
+ * and returns the exchange keys (host, nq x top_k) that ap_merge_shard_keys turns into the global top-k. */
+int ap_search_index_shard(const char *dense_data_path, const char *dense_query_path, const char *sparse_data_path,
+                          const char *sparse_query_path, const char *bm25_data_path, const char *bm25_query_path,
+                          const char *manifest_path, uint32_t shard, int top_k, int cands, float sparse_weight, float bm25_weight,
+                          float dense_weight, int device, uint32_t max_queries, unsigned long long *out_keys, uint32_t *out_nq,
+                          ap_search_stats *stats);
+/* Global top-k of the gathered keys (keys: shards x nq x per_shard, device, e.g. the receive buffer of one
+ * all-gather): ascending (distance, id); out: nq x top_k ids (0xFFFFFFFF when fewer results exist) and distances. */
+int ap_merge_shard_keys(int device, uint32_t shards, uint32_t nq, uint32_t per_shard, const unsigned long long *keys,
+                        uint32_t top_k, uint32_t *out_ids, float *out_dis, void *stream);
 
 /* Merge per-shard result lists into a global top-k on the device (corpus-sharded search).
  * in_ids/in_dis: shards x nq x per_shard (ids already global), device; out: nq x top_k, device. */
@@ -285,6 +356,11 @@ int ap_merge_shard_results(int device, uint32_t shards, uint32_t nq, uint32_t pe
  * participant lists (host: nodes x 64 ids; nodes x 2 counts = new rows, rows), computed by the tcgen05 kernel
  * (use_tc != 0) or by the CUDA-core kernel.  out: nodes x 64 x 32 floats, host.  Needs AP_CREATE_FOR_BUILD. */
 int ap_debug_join_dense(ap_index *ix, uint32_t nodes, const uint32_t *plist, const uint32_t *pcnt, int use_tc, float *out);
+
+/* Test hook for the error path of the bounded waits: runs a one-thread kernel that waits at most `polls` (<= 4096)
+ * polls on a barrier nothing completes, so the wait gives up and raises the index's error word; the kernel returns
+ * normally and the context stays usable.  ap_index_check_status then returns AP_ERR_DEVICE once. */
+int ap_debug_wait_timeout(ap_index *ix, uint32_t polls);
 
 /* Profiling hook: counters of the last search on this index -- expansions, evaluations, gathered bytes, then clock
  * cycles (thread 0 of every CTA, summed) spent in control, waiting for copies, scoring, sorting, merging. */

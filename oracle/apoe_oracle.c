@@ -897,5 +897,52 @@ int orc_prune(uint32_t n, const uint16_t *dense, const uint32_t *s_off, const ui
     return 0;
 }
 
+
+/* ------------------------------------------------------------------ */
+/* nDCG@k as the reference prints it: cal_precision, src/query.cu:111-145.
+ * results: nq x stride ids (the first top_k of a row are used, as the host
+ * copies them at src/query.cu:2070-2075); qrels as a CSR of relevant ids.
+ * Everything accumulates in float, `1 / log2(float(j + 2))` per position,
+ * DCG over the intersection of the sorted result ids and the sorted
+ * relevant ids (multiset semantics of std::set_intersection), each common id
+ * credited at its first position in the result row; a query without relevant
+ * ids divides 0 by 0 exactly as the reference does (the figure becomes NaN). */
+static int u32_cmp(const void *a, const void *b) {
+    const uint32_t x = *(const uint32_t *)a, y = *(const uint32_t *)b;
+    return x < y ? -1 : (x > y ? 1 : 0);
+}
+float orc_cal_precision(uint32_t nq, const uint32_t *results, uint32_t stride, uint32_t top_k, const uint32_t *qrel_off,
+                        const uint32_t *qrel_ids) {
+    float ndcg = 0.0f;
+    uint32_t *tmp = (uint32_t *)malloc(sizeof(uint32_t) * (top_k ? top_k : 1));
+    for (uint32_t i = 0; i < nq; ++i) {
+        const uint32_t nrel = qrel_off[i + 1] - qrel_off[i];
+        uint32_t *rel = (uint32_t *)malloc(sizeof(uint32_t) * (nrel ? nrel : 1));
+        float idcg = 0.0f;
+        for (uint32_t j = 0; j < nrel; ++j) idcg += (1 / log2f((float)(j + 2)));
+        const uint32_t *row = results + (size_t)i * stride;
+        memcpy(tmp, row, sizeof(uint32_t) * top_k);
+        memcpy(rel, qrel_ids + qrel_off[i], sizeof(uint32_t) * nrel);
+        qsort(tmp, top_k, sizeof(uint32_t), u32_cmp);
+        qsort(rel, nrel, sizeof(uint32_t), u32_cmp);
+        float dcg = 0.0f;
+        uint32_t a = 0, b = 0;
+        while (a < top_k && b < nrel) {           /* std::set_intersection */
+            if (tmp[a] < rel[b]) ++a;
+            else if (rel[b] < tmp[a]) ++b;
+            else {
+                const uint32_t x = tmp[a];
+                for (uint32_t it = 0; it < top_k; ++it)
+                    if (row[it] == x) { dcg += (1 / log2f((float)(it + 2))); break; }
+                ++a; ++b;
+            }
+        }
+        ndcg += (dcg / idcg);
+        free(rel);
+    }
+    free(tmp);
+    return ndcg / (float)nq;
+}
+
 int orc_num_threads(void) { return omp_get_max_threads(); }
 int orc_version(void) { return 1; }

@@ -174,6 +174,18 @@ def prune(dense_h, sparse: CsrNp, bm25: CsrNp, knn, knn_dis, power, flags=0):
     return new_list, kw, graph, det
 
 
+def cal_precision(results, top_k, qrels) -> float:
+    """nDCG@k with the reference's float arithmetic (src/query.cu:111-145); qrels: list of id lists."""
+    results = _u32(results)
+    off = np.zeros(len(qrels) + 1, dtype=np.uint32)
+    off[1:] = np.cumsum([len(r) for r in qrels])
+    flat = np.asarray([t for r in qrels for t in r], dtype=np.uint32)
+    f = lib().orc_cal_precision
+    f.restype = C.c_float
+    return float(f(C.c_uint32(results.shape[0]), _p(results, np.uint32), C.c_uint32(results.shape[1]), C.c_uint32(top_k),
+                   _p(off, np.uint32), _p(flat, np.uint32)))
+
+
 def num_threads() -> int:
     return int(lib().orc_num_threads())
 

@@ -85,3 +85,101 @@ def load_seconds(dense_path: str, sparse_path: str, bm25_path: str):
     if rc != 0:
         raise RuntimeError(f"ref_load failed with {rc}")
     return rows.value, sec[0], sec[1]
+
+
+# ---------------------------------------------------------------------------------------------------------
+# Host-only calls (no GPU needed): the reference's file readers and its nDCG figure.
+# ---------------------------------------------------------------------------------------------------------
+def load_graph(path: str):
+    """The reference's load_graph (src/query.cu:35-62) on an index.poe file.  Returns (flat rows, entry points)."""
+    nw, ne = C.c_uint(0), C.c_uint(0)
+    with _quiet():
+        lib().ref_load_graph(path.encode(), None, C.c_size_t(0), None, C.c_uint(0), C.byref(nw), C.byref(ne))
+    rows, ep = np.empty(nw.value, np.uint32), np.empty(ne.value, np.uint32)
+    with _quiet():
+        rc = lib().ref_load_graph(path.encode(), C.c_void_p(rows.ctypes.data), C.c_size_t(rows.size), C.c_void_p(ep.ctypes.data),
+                                  C.c_uint(ep.size), C.byref(nw), C.byref(ne))
+    if rc != 0:
+        raise RuntimeError(f"ref_load_graph failed with {rc}")
+    return rows, ep
+
+
+class _quiet:
+    """Sends the process's stdout (file descriptor 1: the reference prints with std::cout) to a temporary file for the
+    duration of the block; `.text` holds what was printed."""
+
+    def __enter__(self):
+        import sys
+        import tempfile
+        sys.stdout.flush()
+        self._tmp = tempfile.TemporaryFile(mode="w+b")
+        self._saved = os.dup(1)
+        os.dup2(self._tmp.fileno(), 1)
+        return self
+
+    def __exit__(self, *exc):
+        os.dup2(self._saved, 1)
+        os.close(self._saved)
+        self._tmp.seek(0)
+        self.text = self._tmp.read().decode(errors="replace")
+        self._tmp.close()
+        return False
+
+
+def cal_precision_text(results, top_k: int, qrels) -> str:
+    """What the reference's cal_precision (src/query.cu:111-145) prints for these results and relevant ids."""
+    results = np.ascontiguousarray(results, dtype=np.uint32)
+    off = np.zeros(len(qrels) + 1, dtype=np.uint32)
+    off[1:] = np.cumsum([len(r) for r in qrels])
+    flat = np.asarray([t for r in qrels for t in r], dtype=np.uint32)
+    with _quiet() as q:
+        lib().ref_cal_precision(C.c_uint(results.shape[0]), C.c_void_p(results.ctypes.data), C.c_uint(results.shape[1]), C.c_uint(top_k),
+                                C.c_void_p(off.ctypes.data), C.c_void_p(flat.ctypes.data))
+    return q.text.strip()
+
+
+def load_kg(path: str):
+    n_off, nnz = C.c_uint(0), C.c_uint(0)
+    with _quiet():
+        lib().ref_load_kg(path.encode(), None, C.c_size_t(0), None, C.c_size_t(0), C.byref(n_off), C.byref(nnz))
+    off, idx = np.empty(n_off.value, np.uint32), np.empty(nnz.value, np.uint32)
+    with _quiet():
+        rc = lib().ref_load_kg(path.encode(), C.c_void_p(off.ctypes.data), C.c_size_t(off.size), C.c_void_p(idx.ctypes.data),
+                               C.c_size_t(idx.size), C.byref(n_off), C.byref(nnz))
+    if rc != 0:
+        raise RuntimeError(f"ref_load_kg failed with {rc}")
+    return off, idx
+
+
+def load_txt(path: str, rows: int):
+    total = C.c_uint(0)
+    off = np.zeros(rows + 1, np.uint32)
+    lib().ref_load_txt(path.encode(), C.c_uint(rows), C.c_void_p(off.ctypes.data), None, C.c_size_t(0), C.byref(total))
+    ids = np.empty(total.value, np.uint32)
+    rc = lib().ref_load_txt(path.encode(), C.c_uint(rows), C.c_void_p(off.ctypes.data), C.c_void_p(ids.ctypes.data), C.c_size_t(ids.size), C.byref(total))
+    if rc != 0:
+        raise RuntimeError(f"ref_load_txt failed with {rc}")
+    return off, ids
+
+
+def load_fvecs(path: str):
+    num, dim = C.c_uint(0), C.c_uint(0)
+    lib().ref_load_fvecs(path.encode(), None, C.c_size_t(0), C.byref(num), C.byref(dim))
+    out = np.empty((num.value, dim.value), np.float32)
+    rc = lib().ref_load_fvecs(path.encode(), C.c_void_p(out.ctypes.data), C.c_size_t(out.size), C.byref(num), C.byref(dim))
+    if rc != 0:
+        raise RuntimeError(f"ref_load_fvecs failed with {rc}")
+    return out
+
+
+def load_csr(path: str, rows: int):
+    nnz = C.c_uint(0)
+    with _quiet():
+        lib().ref_load_csr(path.encode(), C.c_uint(rows), None, None, None, C.c_size_t(0), C.byref(nnz))
+    off, idx, val = np.empty(rows + 1, np.uint32), np.empty(nnz.value, np.uint32), np.empty(nnz.value, np.float32)
+    with _quiet():
+        rc = lib().ref_load_csr(path.encode(), C.c_uint(rows), C.c_void_p(off.ctypes.data), C.c_void_p(idx.ctypes.data),
+                                C.c_void_p(val.ctypes.data), C.c_size_t(nnz.value), C.byref(nnz))
+    if rc != 0:
+        raise RuntimeError(f"ref_load_csr failed with {rc}")
+    return off, idx, val

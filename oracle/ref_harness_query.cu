@@ -87,3 +87,96 @@ extern "C" int ref_search(unsigned points_num, const float *data_load, const uns
     for (void *p : bufs) cudaFree(p);
     return rc;
 }
+
+// ---------------------------------------------------------------------------------------------------------
+// Host-only exports: the reference's own file readers and its nDCG figure, callable without a GPU, so that the
+// library's loaders and its evaluation step can be compared with the reference itself (not only with the oracle).
+// Each one calls the reference function where it is defined (src/query.cu, include/utils.cuh) and copies the result
+// into caller buffers; nothing is re-implemented here.
+// ---------------------------------------------------------------------------------------------------------
+
+// load_graph, src/query.cu:35-62.  rows_out holds cap_rows x width words; *num and *width come back even when the
+// buffers are too small (return 1), so a caller can size them with a first call.
+extern "C" int ref_load_graph(const char *path, unsigned *rows_out, size_t cap_words, unsigned *ep_out, unsigned cap_ep,
+                              unsigned *num_words, unsigned *num_ep) {
+    std::vector<unsigned> g, ep;
+    load_graph(path, g, ep);
+    if (num_words) *num_words = (unsigned)g.size();
+    if (num_ep) *num_ep = (unsigned)ep.size();
+    if (g.size() > cap_words || ep.size() > cap_ep) return 1;
+    if (rows_out) memcpy(rows_out, g.data(), g.size() * sizeof(unsigned));
+    if (ep_out) memcpy(ep_out, ep.data(), ep.size() * sizeof(unsigned));
+    return 0;
+}
+
+// cal_precision, src/query.cu:111-145: prints "nDCG@10: <v>" on stdout (the caller captures it).  v1 = the first top_k
+// ids of every result row, as search_index_impl builds it (src/query.cu:2070-2075); v2 = the relevant ids.
+extern "C" int ref_cal_precision(unsigned nq, const unsigned *results, unsigned stride, unsigned top_k, const unsigned *qrel_off,
+                                 const unsigned *qrel_ids) {
+    std::vector<std::vector<unsigned>> v1(nq), v2(nq);
+    for (unsigned i = 0; i < nq; i++) {
+        for (unsigned j = 0; j < top_k; j++) v1[i].push_back(results[(size_t)i * stride + j]);
+        for (unsigned j = qrel_off[i]; j < qrel_off[i + 1]; j++) v2[i].push_back(qrel_ids[j]);
+    }
+    cal_precision(v1, v2);
+    std::cout.flush();
+    return 0;
+}
+
+// load_kg_graph, src/query.cu:89-108
+extern "C" int ref_load_kg(const char *path, unsigned *off_out, size_t cap_off, unsigned *idx_out, size_t cap_idx, unsigned *n_off,
+                           unsigned *nnz) {
+    unsigned *off = nullptr, *idx = nullptr, num = 0;
+    load_kg_graph(const_cast<char *>(path), off, idx, num);
+    const unsigned nz = num ? off[num - 1] : 0;
+    if (n_off) *n_off = num;
+    if (nnz) *nnz = nz;
+    int rc = 0;
+    if (num > cap_off || nz > cap_idx) rc = 1;
+    else { if (off_out) memcpy(off_out, off, (size_t)num * 4); if (idx_out) memcpy(idx_out, idx, (size_t)nz * 4); }
+    delete[] off; delete[] idx;
+    return rc;
+}
+
+// load_txt, src/query.cu:65-86: one line of ids per row; off_out has rows + 1 entries
+extern "C" int ref_load_txt(const char *path, unsigned rows, unsigned *off_out, unsigned *ids_out, size_t cap_ids, unsigned *total) {
+    std::vector<std::vector<unsigned>> res(rows);
+    load_txt(const_cast<char *>(path), res, rows);
+    size_t n = 0;
+    for (auto &r : res) n += r.size();
+    if (total) *total = (unsigned)n;
+    if (n > cap_ids) return 1;
+    unsigned o = 0;
+    for (unsigned i = 0; i < rows; i++) { off_out[i] = o; for (unsigned x : res[i]) ids_out[o++] = x; }
+    off_out[rows] = o;
+    return 0;
+}
+
+// load_data, include/utils.cuh:361-378
+extern "C" int ref_load_fvecs(const char *path, float *out, size_t cap_floats, unsigned *num, unsigned *dim) {
+    float *data = nullptr; unsigned n = 0, d = 0;
+    load_data(const_cast<char *>(path), data, n, d);
+    if (num) *num = n;
+    if (dim) *dim = d;
+    int rc = 0;
+    if ((size_t)n * d > cap_floats) rc = 1;
+    else if (out) memcpy(out, data, (size_t)n * d * 4);
+    delete[] data;
+    return rc;
+}
+
+// load_sparse_data, include/utils.cuh:380-398 (rows + 1 offsets are read, as the callers pass num + 1)
+extern "C" int ref_load_csr(const char *path, unsigned rows, unsigned *off_out, unsigned *idx_out, float *val_out, size_t cap_nnz, unsigned *nnz) {
+    unsigned *off = nullptr, *idx = nullptr, nz = 0; float *val = nullptr;
+    load_sparse_data(const_cast<char *>(path), off, idx, val, rows + 1, nz);
+    if (nnz) *nnz = nz;
+    int rc = 0;
+    if (nz > cap_nnz) rc = 1;
+    else {
+        if (off_out) memcpy(off_out, off, (size_t)(rows + 1) * 4);
+        if (idx_out) memcpy(idx_out, idx, (size_t)nz * 4);
+        if (val_out) memcpy(val_out, val, (size_t)nz * 4);
+    }
+    delete[] off; delete[] idx; delete[] val;
+    return rc;
+}

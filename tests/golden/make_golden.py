@@ -11,6 +11,7 @@ import sys
 import numpy as np
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
 for p in ("allan-poe_b200", "oracle", "tests"):
     sys.path.insert(0, os.path.join(ROOT, p))
 import apoe_oracle as orc  # noqa: E402

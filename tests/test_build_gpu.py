@@ -24,15 +24,15 @@ def test_norms_match_oracle_bitwise(tiny, bix):
 
 
 @pytest.fixture(params=["pairs", "stepwise"])
-def prune_kernel(request, monkeypatch):
-    """Both pruning kernels: the all-pairs one (default) and the step-wise one it falls back to."""
-    monkeypatch.setenv("APOE_PRUNE_KERNEL", request.param)
-    return request.param
+def prune_kernel(request):
+    """Both pruning kernels: the all-pairs one (default) and the step-wise one it falls back to; the value is the
+    build-flag word that selects it."""
+    return apoe.BUILD_PRUNE_STEPWISE if request.param == "stepwise" else 0
 
 
 def test_prune_and_rows_match_oracle_bitwise(tiny, bix, prune_kernel):
     """Same pre-pruning k-NN lists in -> same forward lists, keyword-edge lists and 40-wide rows out."""
-    new_list, kw, rows = bix.prune(tiny.knn, tiny.knn_dis, tiny.power)
+    new_list, kw, rows = bix.prune(tiny.knn, tiny.knn_dis, tiny.power, flags=prune_kernel)
     assert np.array_equal(new_list, tiny.new_list)
     assert np.array_equal(kw, tiny.kw_edge)
     assert np.array_equal(rows, tiny.graph)
@@ -49,7 +49,7 @@ def test_prune_on_perturbed_lists(tiny, bix, prune_kernel):
     knn[rows, 40] = knn[rows, 10]
     dis[rows, 40] = dis[rows, 39]
     want = orc.prune(tiny.D7h, tiny.S, tiny.B, knn, dis, tiny.power)
-    got = bix.prune(knn, dis, tiny.power)
+    got = bix.prune(knn, dis, tiny.power, flags=prune_kernel)
     assert np.array_equal(got[0], want[0]) and np.array_equal(got[1], want[1]) and np.array_equal(got[2], want[2])
 
 
@@ -180,4 +180,48 @@ def test_build_index_file_round_trip(tiny, tmp_path):
     ix.load_graph(p("index.poe"))
     g2, ep2 = ix.get_graph()
     assert np.array_equal(g2, rows) and np.array_equal(ep2, ep)
+    ix.close()
+
+
+def _graph_recall(ix, ds, gt):
+    got, _, _ = ix.search(ds.QD, ds.QS, ds.QB, cands=128)
+    return helpers.recall_at(got, gt)
+
+
+def test_reverse_pass_and_random_start_options():
+    """AP_BUILD_SHARED_PAIRS | AP_BUILD_REVERSE_PASS (the closing reverse merge, ref merge_reverse_plus
+    src/index.cu:386-478) and AP_BUILD_RANDOM_START (ref initialize_graph src/index.cu:99-106): list invariants hold
+    and the graphs search about as well as the default build's."""
+    ds = helpers.make_dataset(5000, 100, seed=23, with_graph=False)
+    eff, qdh, qs, qb, qd = helpers.scaled_queries(ds)
+    gt, _, _ = orc.bruteforce(ds.D, ds.S, ds.B, qd, qs, qb, 7, 10)
+    ix = apoe.Index.from_host(ds.D, ds.S, ds.B, for_build=True)
+    ix.build(flags=apoe.BUILD_KEEP_KNN, seed=3)
+    base = _graph_recall(ix, ds, gt)
+    knn_exact, _ = helpers.exact_knn(ds.D, ds.S, ds.B)
+
+    def list_recall(ids):
+        return float(np.mean([len(set(ids[i].tolist()) & set(knn_exact[i, :32].tolist())) / 32 for i in range(0, ds.n, 9)]))
+
+    # classic NN-Descent without and with the closing reverse merge
+    ix.build(flags=apoe.BUILD_KEEP_KNN | apoe.BUILD_SHARED_PAIRS, seed=3)
+    ids0, dis0, _ = ix.get_knn()
+    st = ix.build(flags=apoe.BUILD_KEEP_KNN | apoe.BUILD_SHARED_PAIRS | apoe.BUILD_REVERSE_PASS, seed=3)
+    ids1, dis1, power = ix.get_knn()
+    assert np.all(np.diff(dis1, axis=1) >= 0) and ids1.max() < ds.n
+    for i in range(0, ds.n, 11):                                  # no self loops, no repeated neighbour
+        row = ids1[i][dis1[i] < 1e5]
+        assert i not in row and len(set(row.tolist())) == len(row)
+    # the reverse merge can only improve a list: its 64th distance does not grow (up to run-to-run proposal order)
+    assert np.mean(dis1[:, -1] <= dis0[:, -1] + 1e-3) > 0.9
+    assert list_recall(ids1) >= list_recall(ids0) - 0.02
+    rows, _ = ix.get_graph()
+    assert np.array_equal(rows, orc.prune(ds.D7h, ds.S, ds.B, ids1, dis1, power)[2])
+    assert _graph_recall(ix, ds, gt) >= base - 0.08
+    # random initial lists only
+    st_r = ix.build(flags=apoe.BUILD_KEEP_KNN | apoe.BUILD_RANDOM_START, seed=3, iterations=12)
+    ids2, dis2, _ = ix.get_knn()
+    assert np.all(np.diff(dis2, axis=1) >= 0)
+    assert st_r.iterations_run >= 4                               # no head start: more rounds before the lists settle
+    assert _graph_recall(ix, ds, gt) >= base - 0.08
     ix.close()

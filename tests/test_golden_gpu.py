@@ -38,7 +38,9 @@ def test_search_equals_reference_kernels(gsearch, name):
     assert np.array_equal(dis.view(np.uint32), g[name + "_dis"].view(np.uint32))
 
 
-def test_effective_weights_equal_reference(gsearch):
+def test_effective_weights_equal_oracle_values_of_the_fixture(gsearch):
+    """The fixture's `*_eff` entries were written by the oracle (the reference computes them in host code that prints
+    nothing); this compares the library's normalisation with those floats."""
     g, ds, ix = gsearch
     for name, (w, _, _, _) in COMBOS.items():
         eff = ix.effective_weights(ds.QD, ds.QS, ds.QB, *w)

@@ -204,3 +204,104 @@ def test_file_level_drop_in(small, tmp_path):
                     keyword_id_path="", knowledge_path="", entity2doc_path="", query_entity_path="",
                     graph_path=p("index.poe"), ground_truth_path=p("qrels.txt"), top_k=10, cands=128,
                     sparse_weight=1.0, bm25_weight=1.0, dense_weight=1.0, kg_weight=0.0)
+
+
+def _write_search_files(small, p):
+    synth.write_fvecs(p("d.fvecs"), small.corpus.dense)
+    synth.write_fvecs(p("q.fvecs"), small.queries.dense)
+    synth.write_csr(p("s.bin"), small.corpus.sparse)
+    synth.write_csr(p("b.bin"), small.corpus.bm25)
+    synth.write_csr(p("qs.bin"), small.queries.sparse)
+    synth.write_csr(p("qb.bin"), small.queries.bm25)
+    synth.write_poe(p("index.poe"), small.graph, small.ep)
+
+
+def test_file_level_keyword_search_equals_in_memory_call(small, index, tmp_path):
+    """keyword_id_path: the text file of required term ids is parsed (ref: load_txt, src/query.cu:65-86), bit 31 goes on
+    the matching query terms (src/query.cu:1828-1843) and the keyword kernel runs -- same bits as flagging by hand."""
+    p = lambda s: str(tmp_path / s)
+    _write_search_files(small, p)
+    kws = synth.make_keywords(small.queries, seed=5)
+    synth.write_keywords(p("kw.txt"), kws)
+    ids, dis, _, st = apoe.search_index(p("d.fvecs"), p("q.fvecs"), p("s.bin"), p("qs.bin"), p("b.bin"), p("qb.bin"), p("kw.txt"),
+                                        "", "", "", p("index.poe"), "", 10, 128, 1.0, 1.0, 1.0, 0.0)
+    qb_idx = small.QB.idx.copy()
+    for q, req in enumerate(kws):
+        row = qb_idx[small.QB.off[q]:small.QB.off[q + 1]]
+        row[np.isin(row, np.asarray(req, dtype=np.uint32))] |= np.uint32(0x80000000)
+    want_ids, want_dis, _ = index.search(small.QD, small.QS, orc.CsrNp(small.QB.off, qb_idx, small.QB.val), cands=128, flags=apoe.SEARCH_KEYWORD)
+    assert np.array_equal(ids, want_ids) and np.array_equal(dis.view(np.uint32), want_dis.view(np.uint32))
+    plain, _, _ = index.search(small.QD, small.QS, small.QB, cands=128)
+    assert not np.array_equal(ids, plain)          # the keyword path was really taken
+
+
+def test_file_level_kg_search_equals_in_memory_call(small, index, tmp_path):
+    """knowledge_path / entity2doc_path / query_entity_path: the three CSR files are parsed (ref: load_kg_graph,
+    src/query.cu:89-108) and the knowledge-graph kernel runs -- same bits as handing the arrays over in memory."""
+    p = lambda s: str(tmp_path / s)
+    _write_search_files(small, p)
+    kg = synth.make_kg(small.n, small.nq, entities=5000, seed=9)
+    synth.write_kg_csr(p("kg.bin"), kg.e2e_off, kg.e2e_idx)
+    synth.write_kg_csr(p("e2d.bin"), kg.e2d_off, kg.e2d_idx)
+    synth.write_kg_csr(p("qe.bin"), kg.qe_off, kg.qe_idx)
+    ids, dis, _, st = apoe.search_index(p("d.fvecs"), p("q.fvecs"), p("s.bin"), p("qs.bin"), p("b.bin"), p("qb.bin"), "",
+                                        p("kg.bin"), p("e2d.bin"), p("qe.bin"), p("index.poe"), "", 10, 128, 1.0, 1.0, 1.0, 40.0)
+    index.set_kg(kg.e2e_off, kg.e2e_idx, kg.e2d_off, kg.e2d_idx)
+    want_ids, want_dis, _ = index.search(small.QD, small.QS, small.QB, cands=128, kg_weight=40.0,
+                                         ent=(kg.qe_off.numpy().view(np.uint32), kg.qe_idx.numpy().view(np.uint32)))
+    assert np.array_equal(ids, want_ids) and np.array_equal(dis.view(np.uint32), want_dis.view(np.uint32))
+    # kg_weight without the files is refused, as the reference launches nothing then (src/query.cu:2042-2047)
+    with pytest.raises(apoe.ApoeError):
+        apoe.search_index(p("d.fvecs"), p("q.fvecs"), p("s.bin"), p("qs.bin"), p("b.bin"), p("qb.bin"), "", "", "", "", p("index.poe"),
+                          "", 10, 128, 1.0, 1.0, 1.0, 40.0)
+
+
+def test_kg_bonus_lifts_entity_linked_documents(small, index):
+    """Quality of the knowledge-graph path, the one check its undefined reference behaviour leaves: the documents of
+    the query's own seed entities get the bonus of src/query.cu:1638 and move up the pool -- with kg_weight 40 (the
+    example's value; fused scores of the best documents are around -80 here) a tenth of the top entries are such
+    documents, with kg_weight 400 most of them, without the bonus hardly any."""
+    kg = synth.make_kg(small.n, small.nq, entities=5000, seed=9)
+    index.set_kg(kg.e2e_off, kg.e2e_idx, kg.e2d_off, kg.e2d_idx)
+    qe_off, qe_idx = kg.qe_off.numpy().view(np.uint32), kg.qe_idx.numpy().view(np.uint32)
+    e2d_off, e2d_idx = kg.e2d_off.numpy().view(np.uint32), kg.e2d_idx.numpy().view(np.uint32)
+    ids_plain, dis_plain, _ = index.search(small.QD, small.QS, small.QB, cands=128)
+
+    def linked_fraction(ids):
+        out = []
+        for q in range(small.nq):
+            linked = set()
+            for e in qe_idx[qe_off[q]:qe_off[q + 1]]:
+                linked |= set(e2d_idx[e2d_off[e]:e2d_off[e + 1]].tolist())
+            k = min(10, len(linked))
+            out.append(len(linked & set(ids[q, :k].tolist())) / k)
+        return float(np.mean(out))
+
+    base = linked_fraction(ids_plain)
+    ids_40, dis_40, _ = index.search(small.QD, small.QS, small.QB, cands=128, kg_weight=40.0, ent=(qe_off, qe_idx))
+    ids_400, dis_400, _ = index.search(small.QD, small.QS, small.QB, cands=128, kg_weight=400.0, ent=(qe_off, qe_idx))
+    assert base <= 0.02 and linked_fraction(ids_40) >= base + 0.05 and linked_fraction(ids_400) >= 0.6, \
+        (base, linked_fraction(ids_40), linked_fraction(ids_400))
+    assert np.all(dis_40[:, 0] <= dis_plain[:, 0]) and np.all(dis_400[:, 0] <= dis_40[:, 0])   # a bonus only lowers the best distance
+
+
+def test_device_error_word_is_reported_and_cleared(small, index):
+    """A bounded wait that runs out raises the error word without faulting anything; the next status check reports
+    AP_ERR_DEVICE once and the index keeps working."""
+    index.check_status()
+    index.debug_wait_timeout(64)
+    with pytest.raises(apoe.ApoeError) as e:
+        index.check_status()
+    assert e.value.code == 6
+    index.check_status()
+    ids, dis, _ = index.search(small.QD, small.QS, small.QB, cands=128)
+    eff, qdh, qs, qb, _ = helpers.scaled_queries(small, (1.0, 1.0, 1.0))
+    want_ids, _, _ = orc.search(small.Dh, small.S, small.B, qdh, qs, qb, small.graph, small.ep, 128, 7)
+    assert np.array_equal(ids, want_ids)
+    # the same through a search that passes statistics: the sticky word surfaces there
+    index.debug_wait_timeout(8)
+    with pytest.raises(apoe.ApoeError) as e:
+        index.search(small.QD, small.QS, small.QB, cands=128)
+    assert e.value.code == 6
+    ids, _, _ = index.search(small.QD, small.QS, small.QB, cands=128)
+    assert np.array_equal(ids, want_ids)

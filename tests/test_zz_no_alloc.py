@@ -44,6 +44,20 @@ def test_static_search_equals_regular_search_twice_in_a_row(ds, index):
     assert np.array_equal(ids, want_ids) and np.array_equal(dis.view(np.uint32), want_dis.view(np.uint32))
 
 
+def test_static_search_allocates_no_device_memory(ds, index):
+    """The property the entry point exists for: once the first call on the device has looked up the array's address,
+    a call leaves the device's free memory exactly as it found it (the regular call may grow its staging buffers)."""
+    import torch
+    index.search_static(ds.QD, ds.QS, ds.QB, cands=128)          # first call on this device: address lookup
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for cands in (128, 256, 64):                                 # sizes the regular path would have to grow buffers for
+        index.search_static(ds.QD, ds.QS, ds.QB, cands=cands)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, (free_before, free_after)
+
+
 def test_static_search_rejects_batches_beyond_its_area(ds, index):
     reps = 30                                    # 96 x 30 queries x 4 KB of dense rows alone exceed 8 MiB
     QD = np.tile(ds.QD, (reps, 1))
