@@ -84,11 +84,38 @@ struct Knn {
     uint2 *prop;     // n x kPropCap (distance bits, id)
     uint32_t *propn; // n
     unsigned long long *stats;  // [0] distance evaluations, [1] list updates, [2] proposal overflows
+    uint32_t det;    // deterministic mode: reverse samples and proposals are kept by key, not by arrival (see offer_proposal)
 };
 
 __device__ __forceinline__ uint32_t mix32(uint32_t x) {
     x ^= x >> 16; x *= 0x7feb352du; x ^= x >> 15; x *= 0x846ca68bu; x ^= x >> 16;
     return x;
+}
+// mix32 is a bijection of the 32-bit words; this is its inverse (the multipliers' inverses modulo 2^32)
+__device__ __forceinline__ uint32_t unmix32(uint32_t x) {
+    x ^= x >> 16; x *= 0x43021123u; x = x ^ (x >> 15) ^ (x >> 30); x *= 0x1d69e2a5u; x ^= x >> 16;
+    return x;
+}
+__device__ __forceinline__ uint32_t f2ord(float f);
+
+// A proposal (distance d to document `other`) for `target`'s list.
+//   default: appended to the target's inbox in arrival order; the inbox holds kPropCap entries per round, later ones
+//            are dropped (counted in stats[2]) -- which ones depends on the order the CTAs happen to run in;
+//   deterministic: the inbox is a table of kPropCap slots, a proposal goes to the slot its source id hashes to and the
+//            smallest (distance, id) word per slot survives (64-bit atomicMin).  The outcome is a function of the set
+//            of proposals alone; repeated proposals of one pair collapse, different sources that share a slot
+//            compete and the closer one stays.  Entry layout in this mode: x = id, y = ordered distance bits.
+__device__ __forceinline__ void offer_proposal(uint32_t det, uint2 *prop, uint32_t *propn, unsigned long long *stats,
+                                               uint32_t target, float d, uint32_t other) {
+    if (det) {
+        const unsigned long long key = ((unsigned long long)f2ord(d) << 32) | other;
+        atomicMin(reinterpret_cast<unsigned long long *>(prop + (size_t)target * kPropCap + mix32(other ^ 0x2545F491u) % (uint32_t)kPropCap), key);
+        atomicAdd(&propn[target], 1u);
+        return;
+    }
+    const uint32_t t = atomicAdd(&propn[target], 1u);
+    if (t < (uint32_t)kPropCap) prop[(size_t)target * kPropCap + t] = make_uint2(__float_as_uint(d), other);
+    else if (stats) atomicAdd(stats + 2, 1ull);
 }
 
 // Pair ownership: an evaluated pair is offered to exactly one of its ends, chosen by a hash of the two ids, unless
@@ -270,14 +297,8 @@ __global__ void __launch_bounds__(kSeedWarps * 32) seed_dist_kernel(Knn k, const
         for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(kFull, acc, o);
         if (lane == 0) {
             const float d = 1.0f - acc;
-            if (pair_owned(shared_pairs, v, c)) {
-                const uint32_t t = atomicAdd(&k.propn[v], 1u);
-                if (t < kPropCap) k.prop[(size_t)v * kPropCap + t] = make_uint2(__float_as_uint(d), c);
-            }
-            if (pair_owned(shared_pairs, c, v)) {
-                const uint32_t t2 = atomicAdd(&k.propn[c], 1u);
-                if (t2 < kPropCap) k.prop[(size_t)c * kPropCap + t2] = make_uint2(__float_as_uint(d), v);
-            }
+            if (pair_owned(shared_pairs, v, c)) offer_proposal(k.det, k.prop, k.propn, nullptr, v, d, c);
+            if (pair_owned(shared_pairs, c, v)) offer_proposal(k.det, k.prop, k.propn, nullptr, c, d, v);
         }
         ++evals;
     }
@@ -308,19 +329,40 @@ __global__ void knn_sample_kernel(Knn k, uint32_t round) {
         if (isnew && rn < kSample && id < k.n) {
             k.samp[(size_t)v * 64 + rn] = id;
             k.ids[(size_t)v * kK + slot] = id;  // now "old"
-            const uint32_t t = atomicAdd(&k.scnt[(size_t)id * 4 + 1], 1u);
-            if (t < kSample) k.samp[(size_t)id * 64 + 16 + t] = v;
-            else { const uint32_t r = mix32(v ^ (round * 0x9e3779b9u) ^ t) % (t + 1); if (r < kSample) k.samp[(size_t)id * 64 + 16 + r] = v; }
+            if (k.det) {   // the slot this source hashes to keeps the smallest scrambled source id (decoded by knn_rev_decode_kernel)
+                const uint32_t scr = mix32(v ^ (round * 0x9e3779b9u));
+                if (scr != kEmpty) atomicMin(&k.samp[(size_t)id * 64 + 16 + (mix32(v + 0x632BE5ABu) & 15u)], scr);
+            } else {
+                const uint32_t t = atomicAdd(&k.scnt[(size_t)id * 4 + 1], 1u);
+                if (t < kSample) k.samp[(size_t)id * 64 + 16 + t] = v;
+                else { const uint32_t r = mix32(v ^ (round * 0x9e3779b9u) ^ t) % (t + 1); if (r < kSample) k.samp[(size_t)id * 64 + 16 + r] = v; }
+            }
         }
         if (oldpick && ro < kSample && id < k.n) {
             k.samp[(size_t)v * 64 + 32 + ro] = id;
-            const uint32_t t = atomicAdd(&k.scnt[(size_t)id * 4 + 3], 1u);
-            if (t < kSample) k.samp[(size_t)id * 64 + 48 + t] = v;
-            else { const uint32_t r = mix32(v ^ (round * 0x85ebca6bu) ^ t) % (t + 1); if (r < kSample) k.samp[(size_t)id * 64 + 48 + r] = v; }
+            if (k.det) {
+                const uint32_t scr = mix32(v ^ (round * 0x9e3779b9u));
+                if (scr != kEmpty) atomicMin(&k.samp[(size_t)id * 64 + 48 + (mix32(v + 0x632BE5ABu) & 15u)], scr);
+            } else {
+                const uint32_t t = atomicAdd(&k.scnt[(size_t)id * 4 + 3], 1u);
+                if (t < kSample) k.samp[(size_t)id * 64 + 48 + t] = v;
+                else { const uint32_t r = mix32(v ^ (round * 0x85ebca6bu) ^ t) % (t + 1); if (r < kSample) k.samp[(size_t)id * 64 + 48 + r] = v; }
+            }
         }
         nn += __popc(bn); no += __popc(bo);
     }
     if (lane == 0) { k.scnt[(size_t)v * 4 + 0] = min(nn, (uint32_t)kSample); k.scnt[(size_t)v * 4 + 2] = min(no, (uint32_t)kSample); }
+}
+
+// Deterministic mode: the reverse-sample slots hold scrambled source ids (or 0xFFFFFFFF); turn them back into ids and
+// set the reverse counts to the slot count (empty slots are skipped by knn_plist_kernel's id check).
+__global__ void knn_rev_decode_kernel(Knn k, uint32_t round) {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= k.n * 32u) return;
+    const uint32_t v = i >> 5, s = i & 31u, slot = s < 16 ? 16 + s : 32 + s;   // [16, 32) and [48, 64)
+    const uint32_t x = k.samp[(size_t)v * 64 + slot];
+    if (x != kEmpty) k.samp[(size_t)v * 64 + slot] = unmix32(x) ^ (round * 0x9e3779b9u);
+    if (s == 0) { k.scnt[(size_t)v * 4 + 1] = kSample; k.scnt[(size_t)v * 4 + 3] = kSample; }
 }
 
 // Participants of v's join: v itself, then the distinct new samples, then the distinct old samples not already
@@ -500,6 +542,7 @@ struct JoinArgs {
     uint32_t tab_mask, tab_shift, groups;  // hash table of one new row's terms; rows hashed per round
     uint32_t prop_per;                     // partners proposed to each participant (<= kPropPerMax)
     uint32_t shared_pairs;                 // see pair_owned
+    uint32_t det;                          // see offer_proposal
     uint32_t o_tab, o_dm, o_arena;
 };
 constexpr int kJoinThreads = 512;
@@ -694,11 +737,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
             if (c[1] == best) c[1] = ~0ull;
             if (lane == q) mine = best;
         }
-        if (mine != ~0ull) {
-            const uint32_t t = atomicAdd(&a.propn[me], 1u);
-            if (t < kPropCap) a.prop[(size_t)me * kPropCap + t] = make_uint2(__float_as_uint(ord2f((uint32_t)(mine >> 32))), s_id[(uint32_t)mine & 63u]);
-            else atomicAdd(a.stats + 2, 1ull);
-        }
+        if (mine != ~0ull) offer_proposal(a.det, a.prop, a.propn, a.stats, me, ord2f((uint32_t)(mine >> 32)), s_id[(uint32_t)mine & 63u]);
     }
     if (evals) atomicAdd(a.stats + 0, evals);
 }
@@ -728,8 +767,8 @@ __global__ void __launch_bounds__(128, 8) knn_merge_kernel(Knn k) {
     __shared__ unsigned long long keys[4][kMergeLen];
     const uint32_t v = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
     if (v >= k.n) return;
-    const uint32_t np = min(k.propn[v], (uint32_t)kPropCap);
-    if (np == 0) return;
+    if (k.propn[v] == 0) return;
+    const uint32_t np = k.det ? (uint32_t)kPropCap : min(k.propn[v], (uint32_t)kPropCap);   // deterministic: every slot of the table
     unsigned long long *key = keys[threadIdx.x >> 5];
     // pass 1 key: id (30 bits) | origin (0 = sampled list entry, 1 = unsampled list entry, 2 = proposal) | distance
     // order bits -> equal ids become adjacent with the existing entry first
@@ -740,7 +779,8 @@ __global__ void __launch_bounds__(128, 8) knn_merge_kernel(Knn k) {
             kk = ((unsigned long long)(raw & 0x3FFFFFFFu) << 34) | ((unsigned long long)(raw >> 31) << 32) | f2ord(k.dis[(size_t)v * kK + t]);
         } else if (t - kK < (int)np) {
             const uint2 p = k.prop[(size_t)v * kPropCap + (t - kK)];
-            if (p.y != v) kk = ((unsigned long long)(p.y & 0x3FFFFFFFu) << 34) | (2ull << 32) | f2ord(__uint_as_float(p.x));
+            if (k.det) { if ((p.x & p.y) != kEmpty && p.x != v) kk = ((unsigned long long)(p.x & 0x3FFFFFFFu) << 34) | (2ull << 32) | p.y; }
+            else if (p.y != v) kk = ((unsigned long long)(p.y & 0x3FFFFFFFu) << 34) | (2ull << 32) | f2ord(__uint_as_float(p.x));
         }
         key[t] = kk;
     }
@@ -789,8 +829,7 @@ __global__ void knn_reverse_kernel(Knn k) {
     const float d = k.dis[i];
     if (u >= k.n || u == v || !(d < kInfDis)) return;
     if (!(d < k.dis[(size_t)u * kK + kK - 1])) return;           // cannot enter u's list
-    const uint32_t t = atomicAdd(&k.propn[u], 1u);
-    if (t < kPropCap) k.prop[(size_t)u * kPropCap + t] = make_uint2(__float_as_uint(d), v);
+    offer_proposal(k.det, k.prop, k.propn, nullptr, u, d, v);
 }
 
 __global__ void knn_finish_kernel(Knn k, uint32_t *out_ids) {  // strip flags; unfilled slots point at a valid id
@@ -1681,6 +1720,7 @@ static int seed_run(ap_index *ix, const Knn &k, uint32_t take, uint32_t shared_p
     if (smem > ix->smem_per_block) return AP_OK;   // rows too long for per-warp tables: random start only
     AP_CUDA(cudaFuncSetAttribute(seed_dist_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
+    if (k.det) AP_CUDA(cudaMemsetAsync(k.prop, 0xFF, (size_t)n * kPropCap * sizeof(uint2)));
     seed_dist_kernel<<<(n + kSeedWarps - 1) / kSeedWarps, kSeedWarps * 32, smem>>>(k, ix->meta, ix->rec_build, cand, tabn - 1, 32 - log2u(tabn), shared_pairs);
     knn_merge_kernel<<<(n + 3) / 4, 128>>>(k);
     AP_CUDA(cudaGetLastError());
@@ -1708,6 +1748,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     AP_TRY(db.alloc(&k.prop, (size_t)n * kPropCap)); AP_TRY(db.alloc(&k.propn, n));
     AP_TRY(db.alloc(&k.stats, 4));
     AP_CUDA(cudaMemset(k.stats, 0, 32));
+    k.det = (o.flags & AP_BUILD_DETERMINISTIC) ? 1u : 0u;
     float *power = ix->power;
     if (!power) { AP_CUDA(cudaMalloc(&ix->power, (size_t)n * 4)); power = ix->power; }
     uint32_t launches = 0;
@@ -1726,7 +1767,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     ja.plist = k.plist; ja.pcnt = k.pcnt; ja.meta = ix->meta; ja.rec = ix->rec_build; ja.D = D; ja.knn_dis = k.dis;
     ja.prop = k.prop; ja.propn = k.propn; ja.stats = k.stats; ja.err = err;
     ja.prop_per = std::min<uint32_t>(kPropPerMax, o.proposals ? o.proposals : 4);
-    ja.shared_pairs = shared_pairs;
+    ja.shared_pairs = shared_pairs; ja.det = k.det;
     const uint32_t tabn = pow2_at_least(2 * (ix->max_ns + ix->max_nb), 64);
     ja.tab_mask = tabn - 1; ja.tab_shift = 32 - log2u(tabn);
     // two CTAs per SM: tables for up to 4 hashed rows, the 32 x 64 distance tile, the rest is arena
@@ -1757,8 +1798,13 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     for (; it < iters; ++it) {
         AP_CUDA(cudaMemsetAsync(k.scnt, 0, (size_t)n * 16));
         AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
+        if (k.det) {
+            AP_CUDA(cudaMemsetAsync(k.prop, 0xFF, (size_t)n * kPropCap * sizeof(uint2)));
+            AP_CUDA(cudaMemsetAsync(k.samp, 0xFF, (size_t)n * 64 * 4));
+        }
         AP_CUDA(cudaEventRecord(ev[0]));
         knn_sample_kernel<<<wblocks, 256>>>(k, it);
+        if (k.det) { knn_rev_decode_kernel<<<(uint32_t)(((size_t)n * 32 + 255) / 256), 256>>>(k, it); ++launches; }
         knn_plist_kernel<<<wblocks, 256>>>(k, ix->meta, ja.arena_bytes);
         launches += 2;
         AP_CUDA(cudaEventRecord(ev[1]));
@@ -1786,6 +1832,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     }
     if (shared_pairs && (o.flags & AP_BUILD_REVERSE_PASS)) {
         AP_CUDA(cudaMemsetAsync(k.propn, 0, (size_t)n * 4));
+        if (k.det) AP_CUDA(cudaMemsetAsync(k.prop, 0xFF, (size_t)n * kPropCap * sizeof(uint2)));
         knn_reverse_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k);
         knn_merge_kernel<<<(n + 3) / 4, 128>>>(k);
         launches += 2;

@@ -225,3 +225,28 @@ def test_reverse_pass_and_random_start_options():
     assert st_r.iterations_run >= 4                               # no head start: more rounds before the lists settle
     assert _graph_recall(ix, ds, gt) >= base - 0.08
     ix.close()
+
+
+def test_deterministic_build_gives_one_graph_per_seed():
+    """AP_BUILD_DETERMINISTIC: two builds with one seed give the same lists and the same graph, bit for bit (the default
+    build keeps proposals in arrival order and may differ from run to run); another seed gives another graph; the
+    graph searches about as well as the default one."""
+    ds = helpers.make_dataset(6000, 100, seed=21, with_graph=False)
+    eff, qdh, qs, qb, qd = helpers.scaled_queries(ds)
+    gt, _, _ = orc.bruteforce(ds.D, ds.S, ds.B, qd, qs, qb, 7, 10)
+    ix = apoe.Index.from_host(ds.D, ds.S, ds.B, for_build=True)
+    ix.build(flags=apoe.BUILD_KEEP_KNN, seed=3)
+    base = _graph_recall(ix, ds, gt)
+    runs = []
+    for seed in (3, 3, 4):
+        st = ix.build(flags=apoe.BUILD_KEEP_KNN | apoe.BUILD_DETERMINISTIC, seed=seed)
+        ids, dis, _ = ix.get_knn()
+        rows, ep = ix.get_graph()
+        runs.append((ids.copy(), dis.copy(), rows.copy(), ep.copy(), st.distance_evals, _graph_recall(ix, ds, gt)))
+        assert st.proposal_overflows == 0
+    a, b, c = runs
+    assert np.array_equal(a[0], b[0]) and np.array_equal(a[1].view(np.uint32), b[1].view(np.uint32))
+    assert np.array_equal(a[2], b[2]) and np.array_equal(a[3], b[3]) and a[4] == b[4]
+    assert not np.array_equal(a[2], c[2])
+    assert a[5] >= base - 0.05, (a[5], base)
+    ix.close()
