@@ -69,6 +69,12 @@ class Queries(C.Structure):
                 ("ent_idx", C.c_void_p), ("max_sparse_nnz", C.c_uint32), ("max_bm25_nnz", C.c_uint32)]
 
 
+class ExactStats(C.Structure):
+    _fields_ = [("seconds_total", C.c_double), ("seconds_index", C.c_double), ("sparse_ms", C.c_float), ("dense_ms", C.c_float),
+                ("dense_flops", C.c_uint64), ("postings", C.c_uint64), ("batch_queries", C.c_uint32), ("slices", C.c_uint32),
+                ("reserved", C.c_uint32 * 2)]
+
+
 class SearchStats(C.Structure):
     _fields_ = [("eff_sparse", C.c_float), ("eff_bm25", C.c_float), ("eff_dense", C.c_float), ("path", C.c_uint32),
                 ("kernel_ms", C.c_double), ("total_ms", C.c_double), ("expansions", C.c_uint64),
@@ -379,6 +385,25 @@ class Index:
         _check(lib().ap_search_device(self._h, C.byref(q), C.byref(o), _ptr(out_ids), _ptr(out_dis),
                                       C.c_void_p(stream or 0), C.byref(st) if stats else None))
         return st
+
+    def exact_topk(self, queries, weights, top_k: int = 10, stream=None):
+        """Exact top-k of the fused score over all documents (ground truth), on device tensors.  queries: object with
+        CUDA .dense and .sparse/.bm25 CSRs; weights = (sparse, bm25, dense), used as given.  Returns (ids int32
+        [nq, top_k], distances float32 [nq, top_k], ExactStats) as CUDA tensors."""
+        import torch
+        nq = queries.dense.shape[0]
+        q = Queries(nq=nq, dense=_ptr(queries.dense),
+                    sparse=_Csr(_ptr(queries.sparse.off), _ptr(queries.sparse.idx), _ptr(queries.sparse.val)),
+                    bm25=_Csr(_ptr(queries.bm25.off), _ptr(queries.bm25.idx), _ptr(queries.bm25.val)))
+        ids = torch.empty(nq, top_k, dtype=torch.int32, device=queries.dense.device)
+        dis = torch.empty(nq, top_k, dtype=torch.float32, device=queries.dense.device)
+        st = ExactStats()
+        _check(lib().ap_exact_topk_device(self._h, C.byref(q), C.c_float(weights[0]), C.c_float(weights[1]), C.c_float(weights[2]),
+                                          C.c_uint32(top_k), _ptr(ids), _ptr(dis), C.c_void_p(stream or 0), C.byref(st)))
+        return ids, dis, st
+
+    def exact_release(self) -> None:
+        _check(lib().ap_exact_release(self._h))
 
     def check_status(self) -> None:
         """Raises ApoeError(6) when a kernel of an earlier asynchronous call raised its error word."""

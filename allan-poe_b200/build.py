@@ -11,7 +11,7 @@ CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-Xcompiler", "-fPIC"]
-CU_SOURCES = ["apoe_index.cu", "apoe_search.cu", "apoe_build.cu", "apoe_join_tc.cu", "apoe_prep.cu", "apoe_files.cpp"]
+CU_SOURCES = ["apoe_index.cu", "apoe_search.cu", "apoe_build.cu", "apoe_join_tc.cu", "apoe_prep.cu", "apoe_exact.cu", "apoe_files.cpp"]
 
 
 def _nvcc() -> str:

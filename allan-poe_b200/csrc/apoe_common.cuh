@@ -111,6 +111,8 @@ struct ap_index {
     uint32_t *d_ctl = nullptr;     // [0] next query, [1] error word
     unsigned long long *d_cnt = nullptr;  // [0] expansions [1] evaluations [2] bytes
 
+    void *exact = nullptr;         // inverted index + contiguous dense copy of the exact scorer (made on first use)
+
     apoe::HostSample sample;
     apoe::Workspace ws;
     cudaEvent_t ev0 = nullptr, ev1 = nullptr;
@@ -161,6 +163,7 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
               uint32_t *d_kw, uint32_t *launches, uint32_t flags);
 int norms_run(ap_index *ix, float *d_power);
 int ensure_build_copy(ap_index *ix, float scale);
+void exact_release(ap_index *ix);   // frees what the exact scorer keeps on the index
 
 // ---------------------------------------------------------------------------------------
 // device helpers

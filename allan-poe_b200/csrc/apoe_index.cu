@@ -489,6 +489,7 @@ int ap_index_create_device(ap_index **out, int device, uint32_t n, const float *
 int ap_index_destroy(ap_index *ix) {
     if (!ix) return AP_OK;
     cudaSetDevice(ix->device);
+    exact_release(ix);
     void *ptrs[] = {ix->rec, ix->rec_build, ix->meta, ix->graph, ix->fat, ix->ep, ix->ep_fat, ix->knn_ids, ix->knn_dis, ix->power,
                     ix->e2e_off, ix->e2e_idx, ix->e2d_off, ix->e2d_idx, ix->d_ctl, ix->d_cnt};
     for (void *p : ptrs) if (p) cudaFree(p);

@@ -309,6 +309,28 @@ int ap_file_read_kg(const char *path, uint32_t *n_off, uint32_t *nnz, uint32_t *
  * off: rows + 1 entries; ids (capacity cap, may be NULL): the ids of all rows back to back; *total their number. */
 int ap_file_read_id_lines(const char *path, uint32_t rows, uint32_t *off, uint32_t *ids, size_t cap, size_t *total);
 
+/* ---- exact scoring (ground truth) ---------------------------------------------------------------------- */
+/* Exact top-k of the fused score over every document of the index, on the device: the brute force that the score
+ * definition of compute_hybrid_dis (src/query.cu:148-178) implies, over the documents as stored (dense halves, fp32
+ * sparse values) and the queries as the search sees them (weights folded in, dense rounded to half), accumulated in
+ * fp32.  Used as the ground truth of recall; the reference has no such call (it prints nDCG against a file).
+ * Query pointers are device memory; the weights are used as given (pass the effective ones).  top_k <= 16.
+ * out_ids / out_dis: nq x top_k, device, ascending (distance, id).  The first call on an index builds an inverted
+ * index of its sparse and BM25 rows and a contiguous copy of its dense rows (kept until ap_exact_release or destroy). */
+typedef struct {
+    double seconds_total;   /* the call, including the one-time index below on the first call */
+    double seconds_index;   /* inverted index + dense copy (0 when they were cached) */
+    float sparse_ms;        /* sparse + BM25 accumulation kernels (CUDA events) */
+    float dense_ms;         /* tensor-core contraction with the top-k epilogue */
+    uint64_t dense_flops;   /* 2 x queries x documents x 1024 */
+    uint64_t postings;
+    uint32_t batch_queries, slices;
+    uint32_t reserved[2];
+} ap_exact_stats;
+int ap_exact_topk_device(ap_index *ix, const ap_queries *q, float sparse_weight, float bm25_weight, float dense_weight,
+                         uint32_t top_k, uint32_t *out_ids, float *out_dis, void *stream, ap_exact_stats *stats);
+int ap_exact_release(ap_index *ix);
+
 /* ---- corpus-sharded search ------------------------------------------------------------------------------ */
 /* No counterpart in the reference (one GPU, one index).  Documents [start, start + count) of an n-document corpus belong to
  * shard `shard` of `shards`: contiguous ranges whose sizes differ by at most one. */

@@ -203,18 +203,20 @@ def test_reverse_pass_and_random_start_options():
     def list_recall(ids):
         return float(np.mean([len(set(ids[i].tolist()) & set(knn_exact[i, :32].tolist())) / 32 for i in range(0, ds.n, 9)]))
 
-    # classic NN-Descent without and with the closing reverse merge
-    ix.build(flags=apoe.BUILD_KEEP_KNN | apoe.BUILD_SHARED_PAIRS, seed=3)
+    # classic NN-Descent without and with the closing reverse merge (deterministic builds, so that the reverse merge is
+    # the only difference between the two)
+    classic = apoe.BUILD_KEEP_KNN | apoe.BUILD_SHARED_PAIRS | apoe.BUILD_DETERMINISTIC
+    ix.build(flags=classic, seed=3)
     ids0, dis0, _ = ix.get_knn()
-    st = ix.build(flags=apoe.BUILD_KEEP_KNN | apoe.BUILD_SHARED_PAIRS | apoe.BUILD_REVERSE_PASS, seed=3)
+    st = ix.build(flags=classic | apoe.BUILD_REVERSE_PASS, seed=3)
     ids1, dis1, power = ix.get_knn()
     assert np.all(np.diff(dis1, axis=1) >= 0) and ids1.max() < ds.n
     for i in range(0, ds.n, 11):                                  # no self loops, no repeated neighbour
         row = ids1[i][dis1[i] < 1e5]
         assert i not in row and len(set(row.tolist())) == len(row)
-    # the reverse merge can only improve a list: its 64th distance does not grow (up to run-to-run proposal order)
-    assert np.mean(dis1[:, -1] <= dis0[:, -1] + 1e-3) > 0.9
-    assert list_recall(ids1) >= list_recall(ids0) - 0.02
+    # the reverse merge can only improve a list: no distance in it grows, and some lists do gain entries
+    assert np.all(dis1 <= dis0) and np.mean(dis1[:, -1] < dis0[:, -1]) > 0.01
+    assert list_recall(ids1) >= list_recall(ids0)
     rows, _ = ix.get_graph()
     assert np.array_equal(rows, orc.prune(ds.D7h, ds.S, ds.B, ids1, dis1, power)[2])
     assert _graph_recall(ix, ds, gt) >= base - 0.08
