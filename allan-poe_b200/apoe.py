@@ -386,10 +386,11 @@ class Index:
                                       C.c_void_p(stream or 0), C.byref(st) if stats else None))
         return st
 
-    def exact_topk(self, queries, weights, top_k: int = 10, stream=None):
+    def exact_topk(self, queries, weights, top_k: int = 10, stream=None, keyword: bool = False):
         """Exact top-k of the fused score over all documents (ground truth), on device tensors.  queries: object with
         CUDA .dense and .sparse/.bm25 CSRs; weights = (sparse, bm25, dense), used as given.  Returns (ids int32
-        [nq, top_k], distances float32 [nq, top_k], ExactStats) as CUDA tensors."""
+        [nq, top_k], distances float32 [nq, top_k], ExactStats) as CUDA tensors.  keyword: only documents holding one of
+        the query's required BM25 terms (bit 31) are eligible."""
         import torch
         nq = queries.dense.shape[0]
         q = Queries(nq=nq, dense=_ptr(queries.dense),
@@ -399,7 +400,8 @@ class Index:
         dis = torch.empty(nq, top_k, dtype=torch.float32, device=queries.dense.device)
         st = ExactStats()
         _check(lib().ap_exact_topk_device(self._h, C.byref(q), C.c_float(weights[0]), C.c_float(weights[1]), C.c_float(weights[2]),
-                                          C.c_uint32(top_k), _ptr(ids), _ptr(dis), C.c_void_p(stream or 0), C.byref(st)))
+                                          C.c_uint32(1 if keyword else 0), C.c_uint32(top_k), _ptr(ids), _ptr(dis), C.c_void_p(stream or 0),
+                                          C.byref(st)))
         return ids, dis, st
 
     def exact_release(self) -> None:

@@ -206,7 +206,9 @@ struct SparseArgs {
     uint32_t vocab_s, vocab;
     const uint32_t *toff; const uint2 *post;
     float *S;                      // [batch rows][ld]
+    uint32_t keyword;              // only documents holding a flagged (bit 31) BM25 term of the query stay eligible
 };
+constexpr float kIneligible = -3.0e38f;   // S entry of a document the keyword filter excludes
 constexpr int kSpThreads = 256, kSpTerms = 64;
 
 __device__ __forceinline__ uint32_t lower_bound_doc(const uint2 *__restrict__ post, uint32_t lo, uint32_t hi, uint32_t doc) {
@@ -219,17 +221,18 @@ __device__ __forceinline__ uint32_t lower_bound_doc(const uint2 *__restrict__ po
 
 __global__ void __launch_bounds__(kSpThreads) exact_sparse_kernel(const SparseArgs a) {
     __shared__ float win[kWindow];
-    __shared__ uint32_t s_lo[kSpTerms], s_hi[kSpTerms];
+    __shared__ uint8_t hit[kWindow];
+    __shared__ uint32_t s_lo[kSpTerms], s_hi[kSpTerms], s_flag[kSpTerms];
     __shared__ float s_w[kSpTerms];
     const int tid = threadIdx.x;
     const uint32_t row = blockIdx.y, q = a.q0 + row;
     const uint32_t x0 = blockIdx.x * kWindow, x1 = min(x0 + kWindow, a.n);
-    for (uint32_t i = tid; i < kWindow; i += kSpThreads) win[i] = 0.0f;
+    for (uint32_t i = tid; i < kWindow; i += kSpThreads) { win[i] = 0.0f; hit[i] = 0; }
     for (int sec = 0; sec < 2; ++sec) {
         const uint32_t *qoff = sec == 0 ? a.qs_off : a.qb_off, *qidx = sec == 0 ? a.qs_idx : a.qb_idx;
         const float *qval = sec == 0 ? a.qs_val : a.qb_val;
         const float w = sec == 0 ? a.w_sparse : a.w_bm25;
-        if (w == 0.0f) continue;
+        if (w == 0.0f && !(sec == 1 && a.keyword)) continue;
         const uint32_t o = qoff[q], nt = qoff[q + 1] - o;
         for (uint32_t t0 = 0; t0 < nt; t0 += kSpTerms) {
             const uint32_t m = min((uint32_t)kSpTerms, nt - t0);
@@ -245,14 +248,17 @@ __global__ void __launch_bounds__(kSpThreads) exact_sparse_kernel(const SparseAr
                     hi = lower_bound_doc(a.post, lo, e, x1);
                 }
                 s_lo[tid] = lo; s_hi[tid] = hi;
+                s_flag[tid] = (sec == 1 && a.keyword) ? (qidx[o + t0 + tid] >> 31) : 0u;
                 s_w[tid] = __fmul_rn(qval[o + t0 + tid], w);
             }
             __syncthreads();
             for (uint32_t i = 0; i < m; ++i) {          // one term at a time: its postings name distinct documents
                 const float wq = s_w[i];
+                const bool flagged = s_flag[i] != 0;
                 for (uint32_t p = s_lo[i] + tid; p < s_hi[i]; p += kSpThreads) {
                     const uint2 e = __ldg(a.post + p);
                     win[e.x - x0] = __fmaf_rn(wq, __uint_as_float(e.y), win[e.x - x0]);
+                    if (flagged) hit[e.x - x0] = 1;
                 }
                 __syncthreads();
             }
@@ -260,7 +266,7 @@ __global__ void __launch_bounds__(kSpThreads) exact_sparse_kernel(const SparseAr
     }
     __syncthreads();
     float *dst = a.S + (size_t)row * a.ld + x0;
-    for (uint32_t i = tid; i < kWindow && x0 + i < a.ld; i += kSpThreads) dst[i] = win[i];
+    for (uint32_t i = tid; i < kWindow && x0 + i < a.ld; i += kSpThreads) dst[i] = (a.keyword && !hit[i]) ? kIneligible : win[i];
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -420,7 +426,7 @@ __global__ void __launch_bounds__(kExThreads, 1) exact_dense_topk_kernel(const _
                             const int j = j4 * 4 + u;
                             const float d = 1.0f - (__uint_as_float(r[j]) + sv[u]);
                             const uint32_t x = x0 + j;
-                            if (d <= thr && x < a.n) {
+                            if (d <= thr && x < a.n && sv[u] > -1.0e38f) {
                                 unsigned long long key = ((unsigned long long)ex_f2ord(d) << 32) | x;
                                 if (key < best[kTopMax - 1]) {
 #pragma unroll
@@ -494,7 +500,7 @@ static int make_map(CUtensorMap *map, const void *base, uint64_t rows, uint32_t 
 using namespace apoe;
 
 extern "C" int ap_exact_topk_device(ap_index *ix, const ap_queries *q, float sparse_weight, float bm25_weight, float dense_weight,
-                                    uint32_t top_k, uint32_t *out_ids, float *out_dis, void *stream_, ap_exact_stats *stats) {
+                                    uint32_t flags, uint32_t top_k, uint32_t *out_ids, float *out_dis, void *stream_, ap_exact_stats *stats) {
     if (!ix || !q || !out_ids || !out_dis) return fail(AP_ERR_ARG, "null argument");
     if (q->nq == 0 || !q->dense || !q->sparse.off || !q->bm25.off) return fail(AP_ERR_ARG, "no queries");
     if (top_k == 0 || top_k > (uint32_t)kTopMax) return fail(AP_ERR_ARG, "top_k = %u: the exact scorer keeps up to %d results per query", top_k, kTopMax);
@@ -527,7 +533,8 @@ extern "C" int ap_exact_topk_device(ap_index *ix, const ap_queries *q, float spa
     for (auto &e : ev) AP_CUDA(cudaEventCreate(&e));
     struct EvGuard { cudaEvent_t *e; ~EvGuard() { for (int i = 0; i < 3; ++i) cudaEventDestroy(e[i]); } } evg{ev};
     float sparse_ms = 0.f, dense_ms = 0.f;
-    const bool any_sparse = sparse_weight != 0.0f || bm25_weight != 0.0f;
+    const bool keyword = (flags & AP_EXACT_KEYWORD) != 0;
+    const bool any_sparse = sparse_weight != 0.0f || bm25_weight != 0.0f || keyword;
     // every batch uses the slice count of the first one, so that `part` is one [splits][nq][top_k] array for the merge
     for (uint32_t q0 = 0; q0 < nq; q0 += qb) {
         const uint32_t rows = std::min(qb, nq - q0), m_tiles = (rows + kBM - 1) / kBM;
@@ -540,6 +547,7 @@ extern "C" int ap_exact_topk_device(ap_index *ix, const ap_queries *q, float spa
             sa.qb_off = q->bm25.off; sa.qb_idx = q->bm25.idx; sa.qb_val = q->bm25.val;
             sa.w_sparse = sparse_weight; sa.w_bm25 = bm25_weight;
             sa.vocab_s = inv->vocab_s; sa.vocab = inv->vocab; sa.toff = inv->toff; sa.post = inv->post; sa.S = S;
+            sa.keyword = keyword ? 1u : 0u;
             const dim3 grid((ld + kWindow - 1) / kWindow, rows);
             exact_sparse_kernel<<<grid, kSpThreads, 0, st>>>(sa);
         } else {

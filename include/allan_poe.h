@@ -327,8 +327,11 @@ typedef struct {
     uint32_t batch_queries, slices;
     uint32_t reserved[2];
 } ap_exact_stats;
+#define AP_EXACT_KEYWORD 1u /* keyword-constrained ground truth: only documents that hold at least one of the query's required
+                               BM25 terms (bit 31 set, as for AP_SEARCH_KEYWORD) are eligible; queries with fewer than top_k
+                               such documents get 0xFFFFFFFF / 1e6 in the remaining slots */
 int ap_exact_topk_device(ap_index *ix, const ap_queries *q, float sparse_weight, float bm25_weight, float dense_weight,
-                         uint32_t top_k, uint32_t *out_ids, float *out_dis, void *stream, ap_exact_stats *stats);
+                         uint32_t flags, uint32_t top_k, uint32_t *out_ids, float *out_dis, void *stream, ap_exact_stats *stats);
 int ap_exact_release(ap_index *ix);
 
 /* ---- corpus-sharded search ------------------------------------------------------------------------------ */

@@ -183,3 +183,55 @@ def load_csr(path: str, rows: int):
     if rc != 0:
         raise RuntimeError(f"ref_load_csr failed with {rc}")
     return off, idx, val
+
+
+class Resident:
+    """The reference's search kernels over a corpus that stays on the device (see ref_open in ref_harness_query.cu):
+    uploads and converts the corpus once, then searches any number of query batches, optionally over several graphs."""
+
+    def __init__(self, dense, s, b, graph, ep):
+        self._keep = []
+        def arg(a, dt):
+            arr, ptr = _p(a, dt); self._keep.append(arr); return ptr
+        sec = C.c_double(0)
+        f = lib().ref_open
+        f.restype = C.c_void_p
+        self.n = dense.shape[0]
+        self._h = f(C.c_uint(self.n), arg(dense, np.float32), arg(s[0], np.uint32), arg(s[1], np.uint32), arg(s[2], np.float32),
+                    arg(b[0], np.uint32), arg(b[1], np.uint32), arg(b[2], np.float32), arg(graph, np.uint32), arg(ep, np.uint32), C.byref(sec))
+        self._keep = []
+        if not self._h:
+            raise RuntimeError("ref_open failed")
+        self.seconds_corpus_f2h = sec.value
+
+    def set_graph(self, graph, ep):
+        g, gp = _p(graph, np.uint32)
+        e, epp = _p(ep, np.uint32)
+        if lib().ref_set_graph(C.c_void_p(self._h), gp, epp) != 0:
+            raise RuntimeError("ref_set_graph failed")
+
+    def search(self, qdense_scaled, qs, qb, cands, mode):
+        """Queries already scaled by the effective weights.  Returns ids, dis, seconds (query f2h + search kernel)."""
+        keep = []
+        def arg(a, dt):
+            arr, ptr = _p(a, dt); keep.append(arr); return ptr
+        nq = qdense_scaled.shape[0]
+        ids, dis = np.empty((nq, cands), np.uint32), np.empty((nq, cands), np.float32)
+        sec = C.c_double(0)
+        rc = lib().ref_search_resident(C.c_void_p(self._h), C.c_uint(nq), arg(qdense_scaled, np.float32), arg(qs[0], np.uint32), arg(qs[1], np.uint32),
+                                       arg(qs[2], np.float32), arg(qb[0], np.uint32), arg(qb[1], np.uint32), arg(qb[2], np.float32), C.c_uint(cands),
+                                       C.c_int(mode), C.c_void_p(ids.ctypes.data), C.c_void_p(dis.ctypes.data), C.byref(sec))
+        if rc != 0:
+            raise RuntimeError(f"ref_search_resident failed with {rc}")
+        return ids, dis, sec.value
+
+    def close(self):
+        if self._h:
+            lib().ref_close(C.c_void_p(self._h))
+            self._h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

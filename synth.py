@@ -174,6 +174,120 @@ def make_queries(nq: int, corpus_idf: torch.Tensor, seed: int = 20261126, device
                    Csr(b_off.to(torch.int32), b_idx.to(torch.int32), b_val))
 
 
+# ---------------------------------------------------------------------------
+# Supplementary corpus with neighbourhoods.  The benchmark's prescribed dense vectors are i.i.d. points on the unit
+# sphere: no document has real neighbours, and no graph index reaches a high recall on them.  This generator keeps
+# every shape and value distribution of the prescribed one (unit 1024-d dense rows; Zipf term ids, log-normal sparse
+# values, BM25 weights from tf / df with k1 = 1.2, b = 0.75; the same row lengths) but draws documents from a mixture:
+# a document belongs to one of n / cluster_size topics, its dense row is the topic's centre plus noise, and a share of
+# its sparse and BM25 terms comes from the topic's own term list.  Queries are perturbed documents: the dense row of
+# a random document plus noise, 30 of its sparse terms and 8 of its BM25 terms.
+# ---------------------------------------------------------------------------
+def _subsample_rows(row_of: torch.Tensor, rows: int, keep: torch.Tensor, gen: torch.Generator) -> torch.Tensor:
+    """Boolean mask over items (grouped by `row_of`, ascending) that keeps `keep[row]` random items of every row."""
+    device = row_of.device
+    n_items = torch.bincount(row_of, minlength=rows)
+    pr = torch.rand(row_of.numel(), generator=gen, device=device, dtype=torch.float64)
+    order = torch.argsort(row_of.to(torch.float64) + pr * 0.999999)
+    start = torch.cumsum(n_items, 0) - n_items
+    rank = torch.empty_like(order)
+    rank[order] = torch.arange(row_of.numel(), device=device) - start[row_of[order]]
+    return rank < keep[row_of]
+
+
+def _topic_rows(counts, topic_of_row, topic_terms, share, vocab, s, gen, oversample=2.5):
+    """Like _zipf_rows, but a `share` of every row's draws comes from its topic's term list."""
+    device = counts.device
+    rows = counts.numel()
+    cdf = _zipf_cdf(vocab, s, device)
+    draws = (counts.to(torch.float64) * oversample).ceil().to(torch.int64) + 8
+    total = int(draws.sum())
+    row_of = torch.repeat_interleave(torch.arange(rows, device=device), draws)
+    u = torch.rand(total, generator=gen, device=device, dtype=torch.float64)
+    term = torch.searchsorted(cdf, u).clamp_(max=vocab - 1)
+    from_topic = torch.rand(total, generator=gen, device=device) < share
+    pick = torch.randint(0, topic_terms.shape[1], (total,), generator=gen, device=device)
+    term = torch.where(from_topic, topic_terms[topic_of_row[row_of], pick], term)
+    key = torch.unique(row_of * vocab + term)
+    row_u = key // vocab
+    keep = _subsample_rows(row_u, rows, counts, gen)
+    key = key[keep]
+    n_k = torch.bincount(key // vocab, minlength=rows)
+    off = torch.zeros(rows + 1, dtype=torch.int64, device=device)
+    off[1:] = torch.cumsum(n_k, 0)
+    return off, key % vocab
+
+
+def make_clustered_corpus(n: int, seed: int = 20261201, device="cpu", cluster_size: int = 100, dense_noise: float = 0.6,
+                          topic_share: float = 0.6, topic_terms: int = 256, mean_sparse: float = 120.0, mean_bm25: float = 60.0,
+                          chunk: int = 100_000) -> Corpus:
+    device = torch.device(device)
+    g = _gen(seed, device)
+    topics = max(1, n // cluster_size)
+    centres = torch.randn(topics, DIM, generator=g, device=device)
+    centres = centres / centres.norm(dim=1, keepdim=True)
+    topic_of = torch.randint(0, topics, (n,), generator=g, device=device)
+    dense = torch.empty(n, DIM, dtype=torch.float32, device=device)
+    for a, b in _chunks(n, chunk):
+        e = torch.randn(b - a, DIM, generator=g, device=device)
+        x = centres[topic_of[a:b]] + dense_noise * e / e.norm(dim=1, keepdim=True)
+        dense[a:b] = x / x.norm(dim=1, keepdim=True)
+
+    def rows(mean, vocab, s, cap):
+        tt = torch.searchsorted(_zipf_cdf(vocab, s, device), torch.rand(topics, topic_terms, generator=g, device=device, dtype=torch.float64)).clamp_(max=vocab - 1)
+        offs, idxs, base = [], [], 0
+        for a, b in _chunks(n, chunk):
+            cnt = torch.poisson(torch.full((b - a,), mean, device=device), generator=g).to(torch.int64).clamp_(1, cap)
+            off, idx = _topic_rows(cnt, topic_of[a:b], tt, topic_share, vocab, s, g)
+            offs.append(off[:-1] + base)
+            base += int(off[-1])
+            idxs.append(idx)
+        return torch.cat(offs + [torch.tensor([base], device=device)]), torch.cat(idxs)
+
+    s_off, s_idx = rows(mean_sparse, SPARSE_VOCAB, 1.1, MAX_SPARSE)
+    s_val = torch.exp(torch.randn(s_idx.numel(), generator=g, device=device) * 0.8 - 1.0).to(torch.float32)
+    b_off, b_idx = rows(mean_bm25, BM25_VOCAB, 1.0, MAX_BM25)
+    uu = torch.rand(b_idx.numel(), generator=g, device=device, dtype=torch.float64).clamp_(min=1e-12)
+    tf = 1.0 + torch.floor(torch.log(uu) / math.log(1.0 - 0.6))
+    row_of = torch.repeat_interleave(torch.arange(n, device=device), (b_off[1:] - b_off[:-1]))
+    length = torch.zeros(n, dtype=torch.float64, device=device).index_add_(0, row_of, tf)
+    df = torch.bincount(b_idx, minlength=BM25_VOCAB).to(torch.float64)
+    idf = torch.log(1.0 + (n - df + 0.5) / (df + 0.5))
+    k1, bb = 1.2, 0.75
+    w = idf[b_idx] * tf * (k1 + 1.0) / (tf + k1 * (1.0 - bb + bb * length[row_of] / length.mean()))
+    return Corpus(dense, Csr(s_off.to(torch.int32), s_idx.to(torch.int32), s_val),
+                  Csr(b_off.to(torch.int32), b_idx.to(torch.int32), w.to(torch.float32)), idf.to(torch.float32),
+                  extra={"topic_of": topic_of, "topics": topics})
+
+
+def make_clustered_queries(nq: int, corpus: Corpus, seed: int = 20261202, device=None, nnz_sparse: int = 30, nnz_bm25: int = 8,
+                           dense_noise: float = 0.3) -> Queries:
+    """Queries as perturbed documents of `corpus` (see make_clustered_corpus)."""
+    device = corpus.dense.device if device is None else torch.device(device)
+    g = _gen(seed, device)
+    src = torch.randint(0, corpus.n, (nq,), generator=g, device=device)
+    e = torch.randn(nq, DIM, generator=g, device=device)
+    x = corpus.dense[src] + dense_noise * e / e.norm(dim=1, keepdim=True)
+    dense = x / x.norm(dim=1, keepdim=True)
+
+    def take(csr: Csr, k: int, values):
+        off = csr.off.to(torch.int64)
+        lens = off[src + 1] - off[src]
+        row_of = torch.repeat_interleave(torch.arange(nq, device=device), lens)
+        pos = torch.arange(int(lens.sum()), device=device) - torch.repeat_interleave(torch.cumsum(lens, 0) - lens, lens) + off[src][row_of]
+        keep = _subsample_rows(row_of, nq, torch.full((nq,), k, dtype=torch.int64, device=device), g)
+        pos, row_k = pos[keep], row_of[keep]
+        n_k = torch.bincount(row_k, minlength=nq)
+        qoff = torch.zeros(nq + 1, dtype=torch.int64, device=device)
+        qoff[1:] = torch.cumsum(n_k, 0)
+        idx = csr.idx[pos]
+        return Csr(qoff.to(torch.int32), idx.contiguous(), values(pos, idx).to(torch.float32).contiguous())
+
+    sparse = take(corpus.sparse, nnz_sparse, lambda pos, idx: corpus.sparse.val[pos])
+    bm25 = take(corpus.bm25, nnz_bm25, lambda pos, idx: corpus.idf.to(device)[idx.to(torch.int64)])
+    return Queries(dense, sparse, bm25)
+
+
 @dataclass
 class KnowledgeGraph:
     e2e_off: torch.Tensor   # int32 [entities + 1]
