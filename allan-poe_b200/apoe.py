@@ -40,7 +40,8 @@ class BuildOpts(C.Structure):
 class BuildStats(C.Structure):
     _fields_ = [("seconds_total", C.c_double), ("seconds_knn", C.c_double), ("seconds_prune", C.c_double),
                 ("distance_evals", C.c_uint64), ("list_updates", C.c_uint64), ("iterations_run", C.c_uint32),
-                ("launches", C.c_uint32), ("proposal_overflows", C.c_uint32), ("phase_10us", C.c_uint32 * 3)]
+                ("launches", C.c_uint32), ("proposal_overflows", C.c_uint32), ("phase_10us", C.c_uint32 * 3), ("reserved0", C.c_uint32),
+                ("rows_gathered", C.c_uint64)]
 
 
 class IngestStats(C.Structure):

@@ -83,7 +83,7 @@ struct Knn {
     uint32_t *pcnt;  // n x 2: rows that are new, rows in total
     uint2 *prop;     // n x kPropCap (distance bits, id)
     uint32_t *propn; // n
-    unsigned long long *stats;  // [0] distance evaluations, [1] list updates, [2] proposal overflows
+    unsigned long long *stats;  // [0] distance evaluations, [1] list updates, [2] proposal overflows, [3] records gathered by the joins
     uint32_t det;    // deterministic mode: reverse samples and proposals are kept by key, not by arrival (see offer_proposal)
 };
 
@@ -740,6 +740,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
         if (mine != ~0ull) offer_proposal(a.det, a.prop, a.propn, a.stats, me, ord2f((uint32_t)(mine >> 32)), s_id[(uint32_t)mine & 63u]);
     }
     if (evals) atomicAdd(a.stats + 0, evals);
+    if (tid == 0) atomicAdd(a.stats + 3, (unsigned long long)rows);   // records this join gathered
 }
 
 // ---------------------------------------------------------------------------------------------------------
@@ -1859,6 +1860,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
         stats->seconds_total = std::chrono::duration<double>(t2 - t0).count();
         stats->distance_evals = st[0]; stats->list_updates = st[1]; stats->iterations_run = it; stats->launches = launches;
         stats->proposal_overflows = (uint32_t)st[2];
+        stats->rows_gathered = st[3];
         // phase times in 10 us units: sample + lists, dense tiles (first batch), sparse + proposals, merge
         for (int ph = 0; ph < 3; ++ph) stats->phase_10us[ph] = (uint32_t)(phase_ms[ph + 1] * 100.f);
     }

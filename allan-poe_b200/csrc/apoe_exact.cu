@@ -325,6 +325,7 @@ __global__ void __launch_bounds__(kExThreads, 1) exact_dense_topk_kernel(const _
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(ex_smem_raw) + 1023) & ~uintptr_t(1023));
     __shared__ uint64_t full_bar[kExStages], empty_bar[kExStages], tfull_bar[2], tempty_bar[2];
     __shared__ uint32_t tmem_base_s;
+    float *scratch = reinterpret_cast<float *>(smem + (size_t)kExStages * kExStageBytes);   // 32 x 128 distances of the epilogue
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const uint32_t m_tile = blockIdx.x / a.splits, split = blockIdx.x % a.splits;
     const uint32_t t0 = (uint32_t)((uint64_t)a.tiles_n * split / a.splits), t1 = (uint32_t)((uint64_t)a.tiles_n * (split + 1) / a.splits);
@@ -391,16 +392,26 @@ __global__ void __launch_bounds__(kExThreads, 1) exact_dense_topk_kernel(const _
         unsigned long long best[kTopMax];
 #pragma unroll
         for (int i = 0; i < kTopMax; ++i) best[i] = ~0ull;
-        float thr = 3.0e38f;                                        // distance of the last kept entry
+        constexpr float kOpen = 2.9e38f;                             // below the 3.0e38 that marks an ineligible column
+        float thr = kOpen;                                          // distance of the last kept entry
         const float *srow = a.S + (size_t)row * a.ld;
         uint32_t it = 0;
         bool ok = true;
+        // The tile of S a row needs is read 32 columns (one 128-byte line) ahead of its use: the loads of the next chunk
+        // are in flight while the current one is scored, the first chunk of the next tile while the last one is.
+        float4 sbuf[2][8];
+        auto fetch = [&](float4 (&dst)[8], uint32_t x0) {
+            const float4 *sp = reinterpret_cast<const float4 *>(srow + x0);
+#pragma unroll
+            for (int j4 = 0; j4 < 8; ++j4) dst[j4] = valid_row ? __ldg(sp + j4) : make_float4(0.f, 0.f, 0.f, 0.f);
+        };
+        if (t0 < t1) fetch(sbuf[0], t0 * kBN);
         for (uint32_t t = t0; t < t1 && ok; ++t, ++it) {
             const uint32_t acc = it & 1u;
             ok = ex_wait(&tfull_bar[acc], (it >> 1) & 1u, a.err, 23u);
             if (!ok) break;
             ex_fence_after();
-#pragma unroll 1
+#pragma unroll
             for (int c = 0; c < kBN / 32; ++c) {
                 uint32_t r[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(32 * warp) << 16) + acc * 256 + c * 32;
@@ -413,28 +424,40 @@ __global__ void __launch_bounds__(kExThreads, 1) exact_dense_topk_kernel(const _
                       "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                     : "r"(taddr)
                     : "memory");
+                if (c + 1 < kBN / 32) fetch(sbuf[(c + 1) & 1], t * kBN + (c + 1) * 32);
+                else if (t + 1 < t1) fetch(sbuf[0], (t + 1) * kBN);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const uint32_t x0 = t * kBN + c * 32;
                 if (valid_row) {
-                    const float4 *sp = reinterpret_cast<const float4 *>(srow + x0);
+                    // pass 1, branch-free: distances of the 32 columns to this thread's scratch column, a mask of the
+                    // ones that beat the current threshold; pass 2 (rare): insert those -- one copy of the insertion
+                    // code per chunk instead of one per column keeps the loop inside the instruction cache
+                    const uint32_t lim = a.n - min(a.n, x0);      // columns of this chunk that are documents
+                    uint32_t mask = 0;
 #pragma unroll
                     for (int j4 = 0; j4 < 8; ++j4) {
-                        const float4 s4 = __ldg(sp + j4);
+                        const float4 s4 = sbuf[c & 1][j4];
                         const float sv[4] = {s4.x, s4.y, s4.z, s4.w};
 #pragma unroll
                         for (int u = 0; u < 4; ++u) {
                             const int j = j4 * 4 + u;
-                            const float d = 1.0f - (__uint_as_float(r[j]) + sv[u]);
-                            const uint32_t x = x0 + j;
-                            if (d <= thr && x < a.n && sv[u] > -1.0e38f) {
-                                unsigned long long key = ((unsigned long long)ex_f2ord(d) << 32) | x;
-                                if (key < best[kTopMax - 1]) {
+                            const float d = sv[u] > -1.0e38f ? 1.0f - (__uint_as_float(r[j]) + sv[u]) : 3.0e38f;
+                            scratch[j * 128 + warp * 32 + lane] = d;
+                            mask |= (d <= thr && (uint32_t)j < lim) ? (1u << j) : 0u;
+                        }
+                    }
+                    while (mask) {
+                        const int j = __ffs(mask) - 1;
+                        mask &= mask - 1;
+                        const float d = scratch[j * 128 + warp * 32 + lane];
+                        if (d <= thr) {
+                            unsigned long long key = ((unsigned long long)ex_f2ord(d) << 32) | (x0 + j);
+                            if (key < best[kTopMax - 1]) {
 #pragma unroll
-                                    for (int i = 0; i < kTopMax; ++i)
-                                        if (key < best[i]) { const unsigned long long tmp = best[i]; best[i] = key; key = tmp; }
-                                    const uint32_t o = (uint32_t)(best[kTopMax - 1] >> 32);
-                                    thr = best[kTopMax - 1] == ~0ull ? 3.0e38f : __uint_as_float((o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o);
-                                }
+                                for (int i = 0; i < kTopMax; ++i)
+                                    if (key < best[i]) { const unsigned long long tmp = best[i]; best[i] = key; key = tmp; }
+                                const uint32_t o = (uint32_t)(best[kTopMax - 1] >> 32);
+                                thr = best[kTopMax - 1] == ~0ull ? kOpen : __uint_as_float((o & 0x80000000u) ? (o & 0x7FFFFFFFu) : ~o);
                             }
                         }
                     }
@@ -527,7 +550,7 @@ extern "C" int ap_exact_topk_device(ap_index *ix, const ap_queries *q, float spa
     CUtensorMap map_q, map_x;
     AP_TRY(make_map(&map_q, qh, qb, kBM));
     AP_TRY(make_map(&map_x, inv->dense, n, kBN));
-    const size_t smem = (size_t)kExStages * kExStageBytes + 1024;
+    const size_t smem = (size_t)kExStages * kExStageBytes + 32 * 128 * sizeof(float) + 1024;
     AP_CUDA(cudaFuncSetAttribute(exact_dense_topk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     cudaEvent_t ev[3];
     for (auto &e : ev) AP_CUDA(cudaEventCreate(&e));

@@ -20,8 +20,15 @@
 
 namespace apoe {
 
-constexpr int kSearchThreads = 128;
+#ifndef AP_SEARCH_THREADS
+#define AP_SEARCH_THREADS 96    // threads of one CTA = one query in flight (a multiple of 32, at least 32)
+#endif
+#ifndef AP_SEARCH_CTAS
+#define AP_SEARCH_CTAS 5        // CTAs the kernel is compiled to fit on one SM (registers) and the arena is sized for (shared memory)
+#endif
+constexpr int kSearchThreads = AP_SEARCH_THREADS;
 constexpr int kSearchWarps = kSearchThreads / 32;
+constexpr int kSearchCtas = AP_SEARCH_CTAS;
 constexpr uint32_t kFull = 0xFFFFFFFFu;
 constexpr int kMaxIter = 1000;    // ref: MAX_ITER, src/query.cu:7
 constexpr int kHashReset = 4;     // ref: HASH_RESET, src/query.cu:16
@@ -438,7 +445,7 @@ __device__ __forceinline__ void block_sort_kg(float *dis, uint32_t *id, uint32_t
 // the search kernel
 // ---------------------------------------------------------------------------------------------------------
 template <int F>
-__global__ void __launch_bounds__(kSearchThreads, 4) search_kernel(const SearchArgs a) {
+__global__ void __launch_bounds__(kSearchThreads, kSearchCtas) search_kernel(const SearchArgs a) {
     constexpr bool D = (F & PF_DENSE) != 0, S = (F & PF_SPARSE) != 0, B = (F & PF_BM25) != 0;
     constexpr bool KW = (F & PF_KEYWORD) != 0, KG = (F & PF_KG) != 0;
     constexpr uint32_t IDMASK = KW ? 0x3FFFFFFFu : 0x7FFFFFFFu;
@@ -947,7 +954,7 @@ template <int F>
 static int launch_one(ap_index *ix, SearchArgs &a, uint32_t fixed, uint32_t want_ctas, uint32_t arena_req,
                       uint32_t need_bytes, cudaStream_t stream) {
     // arena: as large as lets `want_ctas` CTAs share one SM, never smaller than the largest record
-    uint32_t ctas = want_ctas ? want_ctas : 4;
+    uint32_t ctas = want_ctas ? want_ctas : (uint32_t)kSearchCtas;
     uint32_t arena = 0;
     for (;; --ctas) {
         const size_t per = std::min(ix->smem_per_sm / ctas - 1024, ix->smem_per_block);

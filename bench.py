@@ -508,17 +508,25 @@ def section_supplementary(dev, n, nq):
 
 
 def build_roofline(bst, corpus, n, hbm_peak, tc_peak, peak_kind):
-    """Roofline figures of the build: every evaluated distance reads one record of the other end (dense halves +
-    8 bytes per stored term); the dense half of the local join is 2 x 1024 flops per evaluated pair on the tensor pipe."""
+    """Roofline figures of the build.  A local join stages the record of each of its (up to 64) participants once --
+    dense halves for the tensor-core tile, 8 bytes per stored term for the sparse part -- and evaluates up to 32 distances
+    per staged record, so the bytes the k-NN phase gathers are `rows_gathered` records, not one record per distance; the
+    per-distance formula (one ~3.5 KB record per evaluated distance) is reported beside it.  The dense half of the joins
+    is 2 x 1024 flops per evaluated pair on the tensor pipe."""
     nnz = int(corpus.sparse.off[-1]) + int(corpus.bm25.off[-1])
     rec_bytes = 2 * DIM + 8.0 * nnz / n
-    evals = int(bst.distance_evals)
-    hbm = evals * rec_bytes / max(bst.seconds_knn, 1e-9) / 1e9
+    evals, rows = int(bst.distance_evals), int(bst.rows_gathered)
+    gathered = rows * rec_bytes
+    hbm = gathered / max(bst.seconds_knn, 1e-9) / 1e9
+    per_distance = evals * rec_bytes / max(bst.seconds_knn, 1e-9) / 1e9
     batches = (n + (1 << 18) - 1) // (1 << 18)          # the dense-tile phase timer covers the first node batch of every round
     dense_s = bst.phase_10us[0] * 1e-5 * batches
     tf = evals * 2.0 * DIM / max(dense_s, 1e-9) / 1e12
     return {"knn": {"bound": "hbm", "achieved": round(hbm, 1), "peak": hbm_peak, "unit": "GB/s", "frac": round(hbm / hbm_peak, 4),
-                    "algorithmic_bytes": int(evals * rec_bytes), "mean_record_bytes": round(rec_bytes, 1), "seconds": round(bst.seconds_knn, 3),
+                    "algorithmic_bytes": int(gathered), "records_gathered": rows, "mean_record_bytes": round(rec_bytes, 1),
+                    "distances_per_gathered_record": round(evals / max(rows, 1), 2), "seconds": round(bst.seconds_knn, 3),
+                    "by_per_distance_formula": {"gb_per_s": round(per_distance, 1), "frac": round(per_distance / hbm_peak, 4),
+                                                "what": "one record per evaluated distance; above the copy peak because a staged record serves many distances"},
                     "limiter": "shared-memory data pipe of the term-probing kernels (ncu: LSU pipe 81 % / 61 %, DRAM 3 %; profiles/build_kernels_200k_docs.md), not HBM"},
             "dense_join": {"bound": "tensor", "achieved": round(tf, 1), "peak": tc_peak, "unit": "TFLOP/s", "frac": round(tf / tc_peak, 4),
                            "useful_flops": int(evals * 2.0 * DIM), "seconds": round(dense_s, 4),
@@ -607,7 +615,7 @@ def bench_config(n, nq, cands):
 # DRAM bytes / algorithmic bytes of the search kernel: dram__bytes_read.sum + dram__bytes_write.sum of one launch over the
 # kernel's counted bytes in the 3-metric ncu capture summarised under profiles/ (the full-size launch is too large to
 # capture; both grow with the number of fused distances, the L2-served share shrinks with the corpus)
-TRAFFIC = {"ratio": 0.864, "from": "ncu capture of the 200k-doc / 4k-query case (records pool 0.7 GB), profiles/search_kernel_200k_docs_4k_queries.md"}
+TRAFFIC = {"ratio": 0.9616, "from": "ncu capture of the 500k-doc / 4k-query case (records pool 1.75 GB), profiles/search_kernel_traffic_500k_docs_4k_queries.md"}
 
 
 def traffic_ratio():

@@ -85,6 +85,9 @@ typedef struct {
     uint32_t proposal_overflows; /* proposals dropped because a document's inbox (192 per round) was full */
     uint32_t phase_10us[3];    /* summed over rounds, in 10 us: dense tiles of the first node batch, the remaining
                                   join work (sparse / BM25 parts, proposals), list merge */
+    uint32_t reserved0;
+    uint64_t rows_gathered;    /* participant records the local joins staged (each once for the dense tile, once for the
+                                  sparse part); a join of r rows evaluates up to 32 x r distances from them */
 } ap_build_stats;
 
 /* ---- search --------------------------------------------------------- */

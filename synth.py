@@ -220,21 +220,59 @@ def _topic_rows(counts, topic_of_row, topic_terms, share, vocab, s, gen, oversam
 
 def make_clustered_corpus(n: int, seed: int = 20261201, device="cpu", cluster_size: int = 100, dense_noise: float = 0.6,
                           topic_share: float = 0.6, topic_terms: int = 256, mean_sparse: float = 120.0, mean_bm25: float = 60.0,
-                          chunk: int = 100_000) -> Corpus:
+                          chunk: int = 100_000, group_size: int = 0, group_noise: float = 0.5, group_share: float = 0.5,
+                          latent_dim: int = 0) -> Corpus:
+    """latent_dim > 0: documents lie near a low-dimensional manifold instead of around isolated centres -- a latent
+    point z ~ N(0, I) of that dimension is mapped into the 1024-d space by a fixed random matrix and perturbed by
+    `dense_noise`; a document's topic is the nearest of n / cluster_size anchor points in the latent space and topics
+    are grouped by the nearest of n / group_size coarser anchors, so neighbouring topics are neighbours in the dense
+    space too (neighbourhoods overlap, as they do in real collections).
+    group_size > 0 adds a level: topics come in groups of group_size / cluster_size siblings whose centres are a group
+    centre plus noise and whose term lists share `group_share` of their terms with the group's list (a hierarchy, as
+    real collections have: it is what lets a greedy search descend from far away)."""
     device = torch.device(device)
     g = _gen(seed, device)
     topics = max(1, n // cluster_size)
     centres = torch.randn(topics, DIM, generator=g, device=device)
     centres = centres / centres.norm(dim=1, keepdim=True)
+    groups, group_of_topic = 0, None
+    if group_size > 0:
+        groups = max(1, n // group_size)
+        gc = torch.randn(groups, DIM, generator=g, device=device)
+        gc = gc / gc.norm(dim=1, keepdim=True)
+        group_of_topic = torch.randint(0, groups, (topics,), generator=g, device=device)
+        centres = gc[group_of_topic] + group_noise * centres
+        centres = centres / centres.norm(dim=1, keepdim=True)
     topic_of = torch.randint(0, topics, (n,), generator=g, device=device)
     dense = torch.empty(n, DIM, dtype=torch.float32, device=device)
-    for a, b in _chunks(n, chunk):
-        e = torch.randn(b - a, DIM, generator=g, device=device)
-        x = centres[topic_of[a:b]] + dense_noise * e / e.norm(dim=1, keepdim=True)
-        dense[a:b] = x / x.norm(dim=1, keepdim=True)
+    if latent_dim > 0:
+        lift = torch.randn(latent_dim, DIM, generator=g, device=device) / math.sqrt(DIM)
+        anchors = torch.randn(topics, latent_dim, generator=g, device=device)
+        anchors = anchors / anchors.norm(dim=1, keepdim=True)
+        if group_size > 0:
+            coarse = torch.randn(groups, latent_dim, generator=g, device=device)
+            group_of_topic = torch.argmax(anchors @ (coarse / coarse.norm(dim=1, keepdim=True)).T, dim=1)
+        for a, b in _chunks(n, min(chunk, 20_000)):
+            z = torch.randn(b - a, latent_dim, generator=g, device=device)
+            zn = z / z.norm(dim=1, keepdim=True)
+            topic_of[a:b] = torch.argmax(zn @ anchors.T, dim=1)
+            x = zn @ lift
+            x = x / x.norm(dim=1, keepdim=True)
+            e = torch.randn(b - a, DIM, generator=g, device=device)
+            x = x + dense_noise * e / e.norm(dim=1, keepdim=True)
+            dense[a:b] = x / x.norm(dim=1, keepdim=True)
+    else:
+        for a, b in _chunks(n, chunk):
+            e = torch.randn(b - a, DIM, generator=g, device=device)
+            x = centres[topic_of[a:b]] + dense_noise * e / e.norm(dim=1, keepdim=True)
+            dense[a:b] = x / x.norm(dim=1, keepdim=True)
 
     def rows(mean, vocab, s, cap):
-        tt = torch.searchsorted(_zipf_cdf(vocab, s, device), torch.rand(topics, topic_terms, generator=g, device=device, dtype=torch.float64)).clamp_(max=vocab - 1)
+        draw = lambda r: torch.searchsorted(_zipf_cdf(vocab, s, device), torch.rand(r, topic_terms, generator=g, device=device, dtype=torch.float64)).clamp_(max=vocab - 1)
+        tt = draw(topics)
+        if groups:
+            shared = torch.rand(topics, topic_terms, generator=g, device=device) < group_share
+            tt = torch.where(shared, draw(groups)[group_of_topic], tt)
         offs, idxs, base = [], [], 0
         for a, b in _chunks(n, chunk):
             cnt = torch.poisson(torch.full((b - a,), mean, device=device), generator=g).to(torch.int64).clamp_(1, cap)
