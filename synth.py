@@ -195,8 +195,9 @@ def _subsample_rows(row_of: torch.Tensor, rows: int, keep: torch.Tensor, gen: to
     return rank < keep[row_of]
 
 
-def _topic_rows(counts, topic_of_row, topic_terms, share, vocab, s, gen, oversample=2.5):
-    """Like _zipf_rows, but a `share` of every row's draws comes from its topic's term list."""
+def _topic_rows(counts, topic_of_row, topic_terms, share, vocab, s, gen, oversample=2.5, second_topic=None, second_share=0.0):
+    """Like _zipf_rows, but a `share` of every row's draws comes from its topic's term list (a `second_share` of those
+    from the list of the row's second topic, when it has one)."""
     device = counts.device
     rows = counts.numel()
     cdf = _zipf_cdf(vocab, s, device)
@@ -207,7 +208,10 @@ def _topic_rows(counts, topic_of_row, topic_terms, share, vocab, s, gen, oversam
     term = torch.searchsorted(cdf, u).clamp_(max=vocab - 1)
     from_topic = torch.rand(total, generator=gen, device=device) < share
     pick = torch.randint(0, topic_terms.shape[1], (total,), generator=gen, device=device)
-    term = torch.where(from_topic, topic_terms[topic_of_row[row_of], pick], term)
+    which = topic_of_row[row_of]
+    if second_topic is not None and second_share > 0:
+        which = torch.where(torch.rand(total, generator=gen, device=device) < second_share, second_topic[row_of], which)
+    term = torch.where(from_topic, topic_terms[which, pick], term)
     key = torch.unique(row_of * vocab + term)
     row_u = key // vocab
     keep = _subsample_rows(row_u, rows, counts, gen)
@@ -221,8 +225,12 @@ def _topic_rows(counts, topic_of_row, topic_terms, share, vocab, s, gen, oversam
 def make_clustered_corpus(n: int, seed: int = 20261201, device="cpu", cluster_size: int = 100, dense_noise: float = 0.6,
                           topic_share: float = 0.6, topic_terms: int = 256, mean_sparse: float = 120.0, mean_bm25: float = 60.0,
                           chunk: int = 100_000, group_size: int = 0, group_noise: float = 0.5, group_share: float = 0.5,
-                          latent_dim: int = 0) -> Corpus:
-    """latent_dim > 0: documents lie near a low-dimensional manifold instead of around isolated centres -- a latent
+                          latent_dim: int = 0, mix: float = 0.0) -> Corpus:
+    """mix > 0: every document also belongs, with that weight, to a second topic (a sibling of its group when topics are
+    grouped): its dense row is centre + mix x second centre + noise and a share mix / (1 + mix) of its topic terms comes
+    from the second topic's list.  Documents that span two topics are what ties the neighbourhoods of a real
+    collection together; without them every topic is an island in the k-NN graph.
+    latent_dim > 0: documents lie near a low-dimensional manifold instead of around isolated centres -- a latent
     point z ~ N(0, I) of that dimension is mapped into the 1024-d space by a fixed random matrix and perturbed by
     `dense_noise`; a document's topic is the nearest of n / cluster_size anchor points in the latent space and topics
     are grouped by the nearest of n / group_size coarser anchors, so neighbouring topics are neighbours in the dense
@@ -244,6 +252,7 @@ def make_clustered_corpus(n: int, seed: int = 20261201, device="cpu", cluster_si
         centres = gc[group_of_topic] + group_noise * centres
         centres = centres / centres.norm(dim=1, keepdim=True)
     topic_of = torch.randint(0, topics, (n,), generator=g, device=device)
+    second_of = None
     dense = torch.empty(n, DIM, dtype=torch.float32, device=device)
     if latent_dim > 0:
         lift = torch.randn(latent_dim, DIM, generator=g, device=device) / math.sqrt(DIM)
@@ -262,9 +271,21 @@ def make_clustered_corpus(n: int, seed: int = 20261201, device="cpu", cluster_si
             x = x + dense_noise * e / e.norm(dim=1, keepdim=True)
             dense[a:b] = x / x.norm(dim=1, keepdim=True)
     else:
+        if mix > 0:
+            if groups:   # a sibling: a random topic of the same group (topics sorted by group, one draw inside the group's span)
+                order = torch.argsort(group_of_topic)
+                gcount = torch.bincount(group_of_topic, minlength=groups)
+                gstart = torch.cumsum(gcount, 0) - gcount
+                gt = group_of_topic[topic_of]
+                r = (torch.rand(n, generator=g, device=device) * gcount[gt].to(torch.float32)).to(torch.int64).clamp_(max=int(gcount.max()) - 1)
+                second_of = order[gstart[gt] + torch.minimum(r, gcount[gt] - 1)]
+            else:
+                second_of = torch.randint(0, topics, (n,), generator=g, device=device)
         for a, b in _chunks(n, chunk):
             e = torch.randn(b - a, DIM, generator=g, device=device)
             x = centres[topic_of[a:b]] + dense_noise * e / e.norm(dim=1, keepdim=True)
+            if second_of is not None:
+                x = x + mix * centres[second_of[a:b]]
             dense[a:b] = x / x.norm(dim=1, keepdim=True)
 
     def rows(mean, vocab, s, cap):
@@ -276,7 +297,8 @@ def make_clustered_corpus(n: int, seed: int = 20261201, device="cpu", cluster_si
         offs, idxs, base = [], [], 0
         for a, b in _chunks(n, chunk):
             cnt = torch.poisson(torch.full((b - a,), mean, device=device), generator=g).to(torch.int64).clamp_(1, cap)
-            off, idx = _topic_rows(cnt, topic_of[a:b], tt, topic_share, vocab, s, g)
+            off, idx = _topic_rows(cnt, topic_of[a:b], tt, topic_share, vocab, s, g,
+                                   second_topic=None if second_of is None else second_of[a:b], second_share=mix / (1.0 + mix))
             offs.append(off[:-1] + base)
             base += int(off[-1])
             idxs.append(idx)
