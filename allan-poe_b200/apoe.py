@@ -415,6 +415,12 @@ class Index:
     def debug_wait_timeout(self, polls: int = 64) -> None:
         _check(lib().ap_debug_wait_timeout(self._h, C.c_uint32(polls)))
 
+    def debug_gather_probe(self, batches: int = 0):
+        """(GB/s, ms, bytes) of the fetch-only probe: random whole records into shared memory with the search kernel's footprint."""
+        g, ms, b = C.c_double(0), C.c_double(0), C.c_ulonglong(0)
+        _check(lib().ap_debug_gather_probe(self._h, C.c_uint32(batches), C.byref(g), C.byref(ms), C.byref(b)))
+        return g.value, ms.value, b.value
+
     def debug_counters(self):
         out = np.zeros(8, dtype=np.uint64)
         _check(lib().ap_debug_counters(self._h, _ptr(out)))

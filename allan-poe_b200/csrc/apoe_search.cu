@@ -120,7 +120,10 @@ __device__ __forceinline__ unsigned long long shard_key(uint32_t local_id, float
     return local_id < n ? (((unsigned long long)f2ord_s(dis) << 32) | (unsigned long long)(local_id + id_base)) : ~0ull;
 }
 
-constexpr int kScoreBatch = 2;  // records a warp scores side by side (independent instruction streams)
+#ifndef AP_SCORE_BATCH
+#define AP_SCORE_BATCH 2
+#endif
+constexpr int kScoreBatch = AP_SCORE_BATCH;  // records a warp scores side by side (independent instruction streams)
 constexpr int kPerfectMax = 32; // query rows up to this many terms get a collision-free hash table
 
 // One section of R staged records against the query row's collision-free table: every lane takes the pairs
@@ -1055,6 +1058,64 @@ int distances_launch(ap_index *ix, const SearchLaunch &L, size_t n_pairs, const 
 }
 
 // ---------------------------------------------------------------------------------------------------------
+// Gather probe: what the memory system gives this access pattern when nothing else is done with the data.  Same CTA
+// count and the same shared-memory budget as the search kernel; warp 0 of every CTA keeps both arena halves filled with
+// bulk copies of whole records of pseudo-random documents (the other warps, which would be scoring, idle), for a fixed
+// number of batches.  The bytes moved / the kernel time is the ceiling a search over this index can reach in gathered
+// bytes: random ~3.5 KB reads do not reach the streaming-copy bandwidth.
+// ---------------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kSearchThreads, kSearchCtas) gather_probe_kernel(const uint8_t *__restrict__ rec, const uint64_t *__restrict__ meta,
+                                                                                  uint32_t n, uint32_t batches, uint32_t per_batch, uint32_t half_bytes,
+                                                                                  uint32_t halves, unsigned long long *bytes_out, uint32_t *err) {
+    extern __shared__ __align__(128) uint8_t smem[];
+    uint64_t *mbar = reinterpret_cast<uint64_t *>(smem);
+    uint8_t *arena = smem + 128;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) { mbar_init(mbar, 1); mbar_init(mbar + 1, 1); mbar_fence_init(); }
+    __syncthreads();
+    if (warp != 0) return;
+    unsigned long long moved = 0;
+    uint32_t phase = 0, counter = blockIdx.x * 0x9E3779B1u;
+    auto issue = [&](int h) {
+        uint32_t sz = 0;
+        const uint8_t *src = nullptr;
+        if ((uint32_t)lane < per_batch) {
+            uint32_t x = (counter + (uint32_t)lane) * 0x85EBCA6Bu; x ^= x >> 15; x *= 0x2C1B3C6Du; x ^= x >> 13;
+            const uint64_t m = meta[x % n];
+            sz = kDenseBytes + 8u * (pad2(meta_ns(m)) + pad2(meta_nb(m)));
+            src = rec + meta_off16(m) * 16ull;
+        }
+        counter += 32;
+        uint32_t incl = sz;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
+        const bool fits = sz != 0 && incl <= half_bytes;     // records past the half's capacity are left out of this batch
+        const uint32_t bm = __ballot_sync(kFull, fits);
+        const uint32_t total = bm ? __shfl_sync(kFull, incl, 31 - __clz(bm)) : 0u;
+        if (lane == 0 && total) { mbar_arrive_expect_tx(mbar + h, total); moved += total; }
+        __syncwarp();
+        if (fits) bulk_g2s(arena + (size_t)h * half_bytes + (incl - sz), src, sz, mbar + h);
+        return total != 0;
+    };
+    bool live[2] = {false, false};
+    live[0] = issue(0);
+    if (halves == 2) live[1] = issue(1);
+    for (uint32_t b = 0; b < batches; ++b) {
+        const int h = halves == 2 ? (int)(b & 1u) : 0;
+        if (live[h]) {
+            bool ok = true;
+            if (lane == 0) ok = mbar_wait_bounded(mbar + h, (phase >> h) & 1u, err, 1u);
+            ok = __shfl_sync(kFull, ok ? 1 : 0, 0) != 0;
+            if (!ok) return;
+            phase ^= 1u << h;
+        }
+        fence_proxy_async();
+        live[h] = (b + halves < batches) ? issue(h) : false;
+    }
+    if (lane == 0) atomicAdd(bytes_out, moved);
+}
+
+// ---------------------------------------------------------------------------------------------------------
 // Corpus-sharded search: merge the per-shard result lists of every query into a global top-k.  One warp per
 // query; the k smallest (distance, id) keys are extracted in ascending order, each round taking the smallest key
 // above the previous one (document ids are unique across shards, so keys are distinct).
@@ -1128,6 +1189,44 @@ extern "C" int ap_merge_shard_keys(int device, uint32_t shards, uint32_t nq, uin
     const size_t threads = (size_t)nq * shards * per_shard;
     merge_shard_keys_kernel<<<(uint32_t)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(shards, nq, per_shard, keys, top_k, out_ids, out_dis);
     AP_CUDA(cudaGetLastError());
+    return AP_OK;
+}
+
+extern "C" int ap_debug_gather_probe(ap_index *ix, uint32_t batches, double *gb_per_s, double *ms_out, unsigned long long *bytes_out) {
+    using namespace apoe;
+    if (!ix || !gb_per_s) return fail(AP_ERR_ARG, "null argument");
+    AP_CUDA(cudaSetDevice(ix->device));
+    // the search kernel's shared-memory budget for the three-path search with short query rows
+    SearchArgs a{};
+    const uint32_t fixed = layout(a, ix, kSearchWarps, 128, 7, 32, 8);
+    const uint32_t need = record_bytes(ix->max_ns, ix->max_nb);
+    const size_t per = std::min(ix->smem_per_sm / kSearchCtas - 1024, ix->smem_per_block);
+    if (per <= fixed + need) return fail(AP_ERR_LIMIT, "records of %u bytes leave no room for the probe's arena", need);
+    const uint32_t arena = (uint32_t)std::min<size_t>((per - fixed) / 128 * 128, 512u * 1024u);
+    const uint32_t halves = (arena / 2) / 128 * 128 >= need ? 2u : 1u;
+    const uint32_t half_bytes = halves == 2 ? (arena / 2) / 128 * 128 : arena;
+    const size_t smem = 128 + (size_t)halves * half_bytes;
+    AP_CUDA(cudaFuncSetAttribute(gather_probe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(smem, (size_t)fixed + arena)));
+    unsigned long long *d_bytes = ix->d_cnt + 7;
+    AP_CUDA(cudaMemset(d_bytes, 0, 8));
+    const uint32_t grid = (uint32_t)kSearchCtas * (uint32_t)ix->num_sms;
+    AP_CUDA(cudaEventRecord(ix->ev0, 0));
+    // the launch asks for the search kernel's full footprint, so the same number of CTAs shares an SM
+    gather_probe_kernel<<<grid, kSearchThreads, std::max(smem, (size_t)fixed + arena)>>>(ix->rec, ix->meta, ix->n, batches ? batches : 2000u, 32u, half_bytes, halves,
+                                                                                         d_bytes, ix->d_ctl + 1);
+    AP_CUDA(cudaGetLastError());
+    AP_CUDA(cudaEventRecord(ix->ev1, 0));
+    AP_CUDA(cudaEventSynchronize(ix->ev1));
+    float ms = 0.f;
+    AP_CUDA(cudaEventElapsedTime(&ms, ix->ev0, ix->ev1));
+    unsigned long long moved = 0;
+    AP_CUDA(cudaMemcpy(&moved, d_bytes, 8, cudaMemcpyDeviceToHost));
+    uint32_t ew = 0;
+    AP_CUDA(cudaMemcpy(&ew, ix->d_ctl + 1, 4, cudaMemcpyDeviceToHost));
+    if (ew) { cudaMemset(ix->d_ctl + 1, 0, 4); return fail(AP_ERR_DEVICE, "the gather probe raised error word %u (a bounded wait ran out)", ew); }
+    *gb_per_s = (double)moved / (ms * 1e-3) / 1e9;
+    if (ms_out) *ms_out = ms;
+    if (bytes_out) *bytes_out = moved;
     return AP_OK;
 }
 

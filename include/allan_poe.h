@@ -390,6 +390,12 @@ int ap_debug_join_dense(ap_index *ix, uint32_t nodes, const uint32_t *plist, con
  * normally and the context stays usable.  ap_index_check_status then returns AP_ERR_DEVICE once. */
 int ap_debug_wait_timeout(ap_index *ix, uint32_t polls);
 
+/* Profiling hook: the bandwidth the memory system gives the search's access pattern when the data is only fetched --
+ * whole records of pseudo-random documents brought into shared memory by bulk copies, with the search kernel's CTA
+ * count and shared-memory budget, `batches` batches per CTA (0 = 2000).  The ceiling, in gathered bytes per second, of
+ * a search over this index; random ~3.5 KB reads stay below the streaming-copy bandwidth. */
+int ap_debug_gather_probe(ap_index *ix, uint32_t batches, double *gb_per_s, double *ms, unsigned long long *bytes);
+
 /* Profiling hook: counters of the last search on this index -- expansions, evaluations, gathered bytes, then clock
  * cycles (thread 0 of every CTA, summed) spent in control, waiting for copies, scoring, sorting, merging. */
 int ap_debug_counters(ap_index *ix, uint64_t *out8);

@@ -224,7 +224,7 @@ def _topic_rows(counts, topic_of_row, topic_terms, share, vocab, s, gen, oversam
 
 def make_clustered_corpus(n: int, seed: int = 20261201, device="cpu", cluster_size: int = 100, dense_noise: float = 0.6,
                           topic_share: float = 0.6, topic_terms: int = 256, mean_sparse: float = 120.0, mean_bm25: float = 60.0,
-                          chunk: int = 100_000, group_size: int = 0, group_noise: float = 0.5, group_share: float = 0.5,
+                          chunk: int = 100_000, group_size: int = 10_000, group_noise: float = 0.7, group_share: float = 0.5,
                           latent_dim: int = 0, mix: float = 0.0) -> Corpus:
     """mix > 0: every document also belongs, with that weight, to a second topic (a sibling of its group when topics are
     grouped): its dense row is centre + mix x second centre + noise and a share mix / (1 + mix) of its topic terms comes

@@ -127,3 +127,17 @@ def test_full_size_properties():
     got = ix.fused_distances(qhost.dense.numpy(), qhost.sparse, qhost.bm25, pq, pd, weights=eff)
     assert np.array_equal(got.view(np.uint32), dis[pq, slot].view(np.uint32))
     ix.close()
+
+
+def test_fetch_only_probe_reports_a_bandwidth():
+    """The profiling hook that only fetches random records (no scoring) runs to completion, moves the bytes it reports
+    and leaves the index usable."""
+    ds = helpers.make_dataset(3000, 16, seed=71)
+    ix = apoe.Index.from_host(ds.D, ds.S, ds.B)
+    gbs, ms, moved = ix.debug_gather_probe(batches=50)
+    assert gbs > 0 and ms > 0 and moved > 50 * 2048
+    ix.set_graph(ds.graph, ds.ep)
+    ids, _, _ = ix.search(ds.QD, ds.QS, ds.QB, cands=64)
+    assert ids.shape == (16, 64)
+    ix.check_status()
+    ix.close()
