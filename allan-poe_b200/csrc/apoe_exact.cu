@@ -17,7 +17,7 @@
 //      A CTA owns one block of 128 queries and one slice of the documents; the per-slice lists are merged afterwards
 //      by the key merge of the sharded search.
 //
-// No cluster multicast is used; the tensor maps cover this GPU's own memory only.  Every wait is bounded and raises
+// Every load is issued by one CTA for itself alone; the tensor maps cover this GPU's own memory only.  Every wait is bounded and raises
 // the index's error word instead of spinning.
 #include <cuda.h>
 
@@ -293,7 +293,7 @@ __device__ __forceinline__ uint64_t ex_desc_sw128(uint32_t smem_addr) {
 constexpr uint32_t kExIdesc = (1u << 4) | ((256u >> 3) << 17) | ((128u >> 4) << 24);
 
 // Tiled TMA load of one box (inner coordinate x in elements: a multiple of 64 halves = 128 bytes, so always 16-byte
-// aligned; y = row) into shared memory, completing on an mbarrier.  No multicast.
+// aligned; y = row) into shared memory, completing on an mbarrier; one CTA, one destination.
 __device__ __forceinline__ void tma_load_2d(void *dst_smem, const CUtensorMap *map, int x, int y, uint64_t *bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
                  ::"r"(smem_u32(dst_smem)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
