@@ -26,14 +26,18 @@ namespace apoe {
 #ifndef AP_SEARCH_CTAS
 #define AP_SEARCH_CTAS 5        // CTAs the kernel is compiled to fit on one SM (registers) and the arena is sized for (shared memory)
 #endif
-constexpr int kSearchThreads = AP_SEARCH_THREADS;
+constexpr int kSearchThreads = AP_SEARCH_THREADS;   // the throughput shape: batches that fill the GPU
 constexpr int kSearchWarps = kSearchThreads / 32;
 constexpr int kSearchCtas = AP_SEARCH_CTAS;
+// The latency shape, for batches too small to fill the SMs (a single query is the extreme): more warps score the
+// records of one expansion, fewer CTAs share an SM.  Same code, same results; only the mapping of work to warps differs.
+constexpr int kLatencyThreads = 256;
+constexpr int kLatencyCtas = 2;
+constexpr int ctas_for_shape(int threads) { return threads == kSearchThreads ? kSearchCtas : kLatencyCtas; }
 constexpr uint32_t kFull = 0xFFFFFFFFu;
 constexpr int kMaxIter = 1000;    // ref: MAX_ITER, src/query.cu:7
 constexpr int kHashReset = 4;     // ref: HASH_RESET, src/query.cu:16
 constexpr int kKeywordRing = 32;  // ref: KEYWORD, src/query.cu:18
-constexpr int kMergeMax = (AP_MAX_CANDS + 32 + kSearchThreads - 1) / kSearchThreads;
 
 enum : int { PF_DENSE = 1, PF_SPARSE = 2, PF_BM25 = 4, PF_KEYWORD = 8, PF_KG = 16, PF_UNFUSED = 32 };
 enum : int { CTL_QUERY = 0, CTL_SEL = 1, CTL_BATCH = 2 /* and 3: one word per arena half */, CTL_MERGE = 4, CTL_SLOT = 5, CTL_KWNUM = 6, CTL_M = 7, CTL_MULT_S = 8, CTL_MULT_B = 9 };
@@ -312,7 +316,7 @@ __device__ __forceinline__ uint32_t count_lt(const float *arr, uint32_t n, float
 // bulk copy per record and arms the mbarrier with the batch's byte count; every warp then scores its share.
 // pool_dis[base + j] receives the distance; keyword hits set bit 30 of pool_id[base + j].
 // Called by all threads of the CTA; ends with the CTA synchronised.
-template <int F>
+template <int F, int NT>
 __device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const uint32_t (&qreg)[16], uint32_t base,
                                             uint64_t my_meta, bool my_need) {
     constexpr bool D = (F & PF_DENSE) != 0, S = (F & PF_SPARSE) != 0, B = (F & PF_BM25) != 0, KW = (F & PF_KEYWORD) != 0;
@@ -392,7 +396,7 @@ __device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const u
         if (c.tid == 0) { tw1 = clock64(); c.t_wait += tw1 - tw0; }
         const int nb_batch = __popc(bm);
         // groups of records round-robin over the warps, warp 0 last: it is the one that issues the refills
-        for (int g = (c.warp + kSearchWarps - 1) % kSearchWarps; g * kScoreBatch < nb_batch; g += kSearchWarps) {
+        for (int g = (c.warp + NT / 32 - 1) % (NT / 32); g * kScoreBatch < nb_batch; g += NT / 32) {
             const uint8_t *rec[kScoreBatch];
             uint32_t rns[kScoreBatch], rnb[kScoreBatch], hit[kScoreBatch];
             int slot[kScoreBatch];
@@ -426,10 +430,11 @@ __device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const u
 
 // Block-wide restatement of the reference's shared-memory bitonic network for an arbitrary length
 // (include/utils.cuh:261-280), used once per query by the KG variant to order the seeded pool prefix.
+template <int NT>
 __device__ __forceinline__ void block_sort_kg(float *dis, uint32_t *id, uint32_t *ent, uint32_t *hop, uint32_t len, int tid) {
     for (uint32_t stride = 1; stride < len; stride <<= 1) {
         for (uint32_t step = stride; step > 0; step >>= 1) {
-            for (uint32_t k = tid; k < len / 2; k += kSearchThreads) {
+            for (uint32_t k = tid; k < len / 2; k += NT) {
                 const uint32_t aa = 2 * step * (k / step), bb = k % step;
                 const uint32_t u = (step == stride) ? (aa + step - 1 - bb) : (aa + bb), d = aa + bb + step;
                 if (d < len && dis[u] > dis[d]) {
@@ -447,8 +452,9 @@ __device__ __forceinline__ void block_sort_kg(float *dis, uint32_t *id, uint32_t
 // ---------------------------------------------------------------------------------------------------------
 // the search kernel
 // ---------------------------------------------------------------------------------------------------------
-template <int F>
-__global__ void __launch_bounds__(kSearchThreads, kSearchCtas) search_kernel(const SearchArgs a) {
+template <int F, int NT>
+__global__ void __launch_bounds__(NT, ctas_for_shape(NT)) search_kernel(const SearchArgs a) {
+    constexpr int kMergeMax = (AP_MAX_CANDS + 32 + NT - 1) / NT;
     constexpr bool D = (F & PF_DENSE) != 0, S = (F & PF_SPARSE) != 0, B = (F & PF_BM25) != 0;
     constexpr bool KW = (F & PF_KEYWORD) != 0, KG = (F & PF_KG) != 0;
     constexpr uint32_t IDMASK = KW ? 0x3FFFFFFFu : 0x7FFFFFFFu;
@@ -492,8 +498,8 @@ __global__ void __launch_bounds__(kSearchThreads, kSearchCtas) search_kernel(con
         if (qi >= a.nq) break;
 
         // ---- per-query state -----------------------------------------------------------------------------
-        for (uint32_t i = tid; i <= a.vis_mask; i += kSearchThreads) c.vis[i] = kEmpty;
-        for (uint32_t i = tid; i < topm + 32; i += kSearchThreads) {
+        for (uint32_t i = tid; i <= a.vis_mask; i += NT) c.vis[i] = kEmpty;
+        for (uint32_t i = tid; i < topm + 32; i += NT) {
             pool_id[i] = kEmpty; pool_dis[i] = kInfDis;
             if (KG) { c.pool_ent[i] = kEmpty; c.pool_hop[i] = 0; }
         }
@@ -517,16 +523,16 @@ __global__ void __launch_bounds__(kSearchThreads, kSearchCtas) search_kernel(con
         if (S) {
             const uint32_t o = a.qs_off[qi];
             c.qs.n = a.qs_off[qi + 1] - o;
-            for (uint32_t j = tid; j < c.qs.n; j += kSearchThreads)
+            for (uint32_t j = tid; j < c.qs.n; j += NT)
                 c.sq[j] = make_uint2(a.qs_idx[o + j], __float_as_uint(__fmul_rn(a.qs_val[o + j], a.w_sparse)));
-            for (uint32_t j = tid; j < a.ts_slots; j += kSearchThreads) c.ts[j] = make_uint2(kEmpty, 0u);
+            for (uint32_t j = tid; j < a.ts_slots; j += NT) c.ts[j] = make_uint2(kEmpty, 0u);
         }
         if (B) {
             const uint32_t o = a.qb_off[qi];
             c.qb.n = a.qb_off[qi + 1] - o;
-            for (uint32_t j = tid; j < c.qb.n; j += kSearchThreads)
+            for (uint32_t j = tid; j < c.qb.n; j += NT)
                 c.bq[j] = make_uint2(a.qb_idx[o + j], __float_as_uint(__fmul_rn(a.qb_val[o + j], a.w_bm25)));
-            for (uint32_t j = tid; j < a.tb_slots; j += kSearchThreads) c.tb[j] = make_uint2(kEmpty, 0u);
+            for (uint32_t j = tid; j < a.tb_slots; j += NT) c.tb[j] = make_uint2(kEmpty, 0u);
         }
         __syncthreads();
         if (warp == 0) {
@@ -548,7 +554,7 @@ __global__ void __launch_bounds__(kSearchThreads, kSearchCtas) search_kernel(con
                 stg_id[lane] = e.id;
                 meta = (uint64_t)e.meta_lo | ((uint64_t)e.meta_hi << 32);
             }
-            score_slots<F>(a, c, qreg, topm, meta, true);
+            score_slots<F, NT>(a, c, qreg, topm, meta, true);
             if (warp == 0) {
                 float d = stg_dis[lane];
                 uint32_t id = stg_id[lane], e0 = 0, e1 = 0;
@@ -593,12 +599,12 @@ __global__ void __launch_bounds__(kSearchThreads, kSearchCtas) search_kernel(con
                     need = cb + lane < m;
                     if (need) meta = a.meta[pool_id[cb + lane]];
                 }
-                score_slots<F>(a, c, qreg, cb, meta, need);
+                score_slots<F, NT>(a, c, qreg, cb, meta, need);
             }
-            for (uint32_t i = tid; i < m; i += kSearchThreads)
+            for (uint32_t i = tid; i < m; i += NT)
                 if (c.pool_ent[i] != kEmpty) pool_dis[i] = __fsub_rn(pool_dis[i], a.kg_weight);
             __syncthreads();
-            block_sort_kg(pool_dis, pool_id, c.pool_ent, c.pool_hop, m, tid);
+            block_sort_kg<NT>(pool_dis, pool_id, c.pool_ent, c.pool_hop, m, tid);
             __syncthreads();
         }
 
@@ -606,9 +612,9 @@ __global__ void __launch_bounds__(kSearchThreads, kSearchCtas) search_kernel(con
         for (int it = 0; it < kMaxIter; ++it) {
             if (tid == 0) c.t_mark = clock64();
             if ((it + 1) % kHashReset == 0) {
-                for (uint32_t i = tid; i <= a.vis_mask; i += kSearchThreads) c.vis[i] = kEmpty;
+                for (uint32_t i = tid; i <= a.vis_mask; i += NT) c.vis[i] = kEmpty;
                 __syncthreads();
-                for (uint32_t i = tid; i < topm + 32; i += kSearchThreads) vis_insert(c.vis, a.vis_mask, pool_id[i] & IDMASK);
+                for (uint32_t i = tid; i < topm + 32; i += NT) vis_insert(c.vis, a.vis_mask, pool_id[i] & IDMASK);
                 __syncthreads();
             }
             // first pool entry whose explored bit is clear
@@ -726,7 +732,7 @@ __global__ void __launch_bounds__(kSearchThreads, kSearchCtas) search_kernel(con
                 }
             }
             if (tid == 0) { const long long t = clock64(); c.t_ctl += t - c.t_mark; }
-            score_slots<F>(a, c, qreg, topm, my_meta, my_need);
+            score_slots<F, NT>(a, c, qreg, topm, my_meta, my_need);
             if (tid == 0) c.t_mark = clock64();
 
             // Order the staged entries for the merge.  Only entries that can enter the pool (distance <= the pool's
@@ -768,7 +774,7 @@ __global__ void __launch_bounds__(kSearchThreads, kSearchCtas) search_kernel(con
                 float r_dis[kMergeMax];
 #pragma unroll
                 for (int e = 0; e < kMergeMax; ++e) {
-                    const uint32_t idx = tid + e * kSearchThreads;
+                    const uint32_t idx = tid + e * NT;
                     r_pos[e] = kEmpty;
                     if (idx < topm + 32) {
                         r_dis[e] = pool_dis[idx]; r_id[e] = pool_id[idx];
@@ -807,7 +813,7 @@ __global__ void __launch_bounds__(kSearchThreads, kSearchCtas) search_kernel(con
 
         // ---- results (ref: src/query.cu:566-569; keyword ordering :1465-1481) ---------------------------------
         if (!KW) {
-            for (uint32_t i = tid; i < topm; i += kSearchThreads) {
+            for (uint32_t i = tid; i < topm; i += NT) {
                 const uint32_t id = pool_id[i] & 0x7FFFFFFFu;
                 const float d = pool_dis[i];
                 if (a.out_ids) { a.out_ids[(size_t)qi * topm + i] = id; a.out_dis[(size_t)qi * topm + i] = d; }
@@ -953,11 +959,11 @@ static uint32_t layout(SearchArgs &a, const ap_index *ix, uint32_t warps, uint32
     return a.o_arena;  // fixed bytes before the arena
 }
 
-template <int F>
-static int launch_one(ap_index *ix, SearchArgs &a, uint32_t fixed, uint32_t want_ctas, uint32_t arena_req,
-                      uint32_t need_bytes, cudaStream_t stream) {
+template <int F, int NT>
+static int launch_shape(ap_index *ix, SearchArgs &a, uint32_t fixed, uint32_t want_ctas, uint32_t arena_req,
+                        uint32_t need_bytes, cudaStream_t stream) {
     // arena: as large as lets `want_ctas` CTAs share one SM, never smaller than the largest record
-    uint32_t ctas = want_ctas ? want_ctas : (uint32_t)kSearchCtas;
+    uint32_t ctas = want_ctas ? want_ctas : (uint32_t)(NT == kSearchThreads ? kSearchCtas : kLatencyCtas);
     uint32_t arena = 0;
     for (;; --ctas) {
         const size_t per = std::min(ix->smem_per_sm / ctas - 1024, ix->smem_per_block);
@@ -974,14 +980,23 @@ static int launch_one(ap_index *ix, SearchArgs &a, uint32_t fixed, uint32_t want
     a.halves = (arena / 2) / 128 * 128 >= need_bytes ? 2u : 1u;
     a.half_bytes = a.halves == 2 ? (arena / 2) / 128 * 128 : arena;
     const size_t smem = fixed + arena;
-    AP_CUDA(cudaFuncSetAttribute(search_kernel<F>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    AP_CUDA(cudaFuncSetAttribute(search_kernel<F, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int occ = 0;
-    AP_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, search_kernel<F>, kSearchThreads, smem));
+    AP_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, search_kernel<F, NT>, NT, smem));
     if (occ < 1) return fail(AP_ERR_LIMIT, "search kernel does not fit on an SM (%zu bytes of shared memory)", smem);
     const uint32_t grid = (uint32_t)std::min<uint64_t>(a.nq, (uint64_t)occ * ix->num_sms);
-    search_kernel<F><<<grid, kSearchThreads, smem, stream>>>(a);
+    search_kernel<F, NT><<<grid, NT, smem, stream>>>(a);
     AP_CUDA(cudaGetLastError());
     return AP_OK;
+}
+
+// Batches that leave SMs empty with one query per CTA take the latency shape (unless the caller fixes the CTA count).
+template <int F>
+static int launch_one(ap_index *ix, SearchArgs &a, uint32_t fixed, uint32_t want_ctas, uint32_t arena_req,
+                      uint32_t need_bytes, cudaStream_t stream) {
+    if (kLatencyThreads != kSearchThreads && want_ctas == 0 && a.nq <= (uint32_t)ix->num_sms * kLatencyCtas)
+        return launch_shape<F, kLatencyThreads>(ix, a, fixed, 0, arena_req, need_bytes, stream);
+    return launch_shape<F, kSearchThreads>(ix, a, fixed, want_ctas, arena_req, need_bytes, stream);
 }
 
 static void fill_args(ap_index *ix, const SearchLaunch &L, SearchArgs &a) {

@@ -55,7 +55,7 @@ def parse():
     ap.add_argument("--docs", type=int, default=1_000_000)
     ap.add_argument("--queries", type=int, default=10_000)
     ap.add_argument("--cands", type=int, default=128)
-    ap.add_argument("--cpu-queries", type=int, default=256, help="queries of the bounded CPU brute-force sample")
+    ap.add_argument("--cpu-queries", type=int, default=1000, help="queries of the bounded CPU brute-force sample (about 17 s on 16 cores at 1M docs)")
     ap.add_argument("--ref-queries", type=int, default=0, help="queries per step of the reference arm (0 = as the own arm)")
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--quick", action="store_true", help="headline only: skip the side measurements (sweep, curve, keyword, kg, ...)")
