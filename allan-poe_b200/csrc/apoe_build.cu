@@ -1557,13 +1557,22 @@ __global__ void ep_take_kernel(uint32_t n, const unsigned long long *__restrict_
 static uint32_t pow2_at_least(uint32_t v, uint32_t lo) { uint32_t p = lo; while (p < v) p <<= 1; return p; }
 static uint32_t log2u(uint32_t p) { uint32_t l = 0; while ((1u << l) < p) ++l; return l; }
 
+// Device scratch of one build step.  Memory handed over with donate() (buffers of an earlier phase that are dead by
+// now) is carved up first, so a later phase does not go back to cudaMalloc, whose cost on a busy allocator varies
+// from microseconds to hundreds of milliseconds; what does not fit is allocated and freed with the object.
 struct DevBuf {
     std::vector<void *> ptrs;
+    struct Slab { uint8_t *p; size_t left; };
+    std::vector<Slab> slabs;
     ~DevBuf() { for (void *p : ptrs) cudaFree(p); }
+    void donate(void *p, size_t bytes) { if (p && bytes) slabs.push_back(Slab{(uint8_t *)p, bytes}); }
     template <class T> int alloc(T **out, size_t count) {
+        const size_t bytes = (std::max<size_t>(count * sizeof(T), 16) + 255) / 256 * 256;
+        for (Slab &sl : slabs)
+            if (sl.left >= bytes) { *out = (T *)sl.p; sl.p += bytes; sl.left -= bytes; return AP_OK; }
         void *p = nullptr;
-        cudaError_t e = cudaMalloc(&p, std::max<size_t>(count * sizeof(T), 16));
-        if (e != cudaSuccess) return fail(AP_ERR_CUDA, "cudaMalloc of %zu bytes failed: %s", count * sizeof(T), cudaGetErrorString(e));
+        cudaError_t e = cudaMalloc(&p, bytes);
+        if (e != cudaSuccess) return fail(AP_ERR_CUDA, "cudaMalloc of %zu bytes failed: %s", bytes, cudaGetErrorString(e));
         ptrs.push_back(p); *out = (T *)p; return AP_OK;
     }
 };
@@ -1591,8 +1600,8 @@ int norms_run(ap_index *ix, float *d_power) {
 }
 
 // prune + reverse edges + final rows + entry points, on device k-NN lists; installs the graph.
-int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const float *d_power, uint32_t *d_new_list,
-              uint32_t *d_kw, uint32_t *launches, uint32_t flags) {
+static int prune_run_in(DevBuf &db, ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const float *d_power, uint32_t *d_new_list,
+                        uint32_t *d_kw, uint32_t *launches, uint32_t flags) {
     const uint32_t n = ix->n;
     if (n >= (1u << 27)) return fail(AP_ERR_LIMIT, "pruning supports up to 2^27 documents per index");
     const bool trace = (flags & AP_BUILD_TRACE) != 0;
@@ -1602,7 +1611,6 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
         cudaDeviceSynchronize();
         fprintf(stderr, "prune: %.1f ms after %s\n", std::chrono::duration<double, std::milli>(std::chrono::high_resolution_clock::now() - tr0).count(), what);
     };
-    DevBuf db;
     uint32_t *detour, *nl = d_new_list, *kw = d_kw;
     AP_TRY(db.alloc(&detour, (size_t)n * AP_DEGREE));
     if (!nl) AP_TRY(db.alloc(&nl, (size_t)n * AP_DEGREE));
@@ -1689,14 +1697,21 @@ int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const
     return rc_install;
 }
 
+int prune_run(ap_index *ix, const uint32_t *d_knn, const float *d_knn_dis, const float *d_power, uint32_t *d_new_list,
+              uint32_t *d_kw, uint32_t *launches, uint32_t flags) {
+    DevBuf db;
+    return prune_run_in(db, ix, d_knn, d_knn_dis, d_power, d_new_list, d_kw, launches, flags);
+}
+
 int join_dense_tc_launch(ap_index *ix, uint32_t node0, uint32_t nodes, const uint32_t *plist, const uint32_t *pcnt, float *D,
                          cudaStream_t stream);  // apoe_join_tc.cu
 
 // Term-seeded first lists (see seed_cand_kernel).  Skipped when the corpus has no BM25 postings or 2^31 and more
 // (about 35 M documents of the benchmark's shape): the build then starts from the random lists alone.
-static int seed_run(ap_index *ix, const Knn &k, uint32_t take, uint32_t shared_pairs, uint32_t *launches) {
+static int seed_run(ap_index *ix, const Knn &k, uint32_t take, uint32_t shared_pairs, uint32_t *launches, void *scratch, size_t scratch_bytes) {
     const uint32_t n = ix->n;
     DevBuf db;
+    db.donate(scratch, scratch_bytes);   // memory the rounds use later
     uint32_t *cnt, *off, *cand;
     unsigned long long *total64;
     AP_TRY(db.alloc(&cnt, (size_t)n + 1)); AP_TRY(db.alloc(&off, (size_t)n + 1)); AP_TRY(db.alloc(&total64, 1));
@@ -1733,7 +1748,7 @@ static int seed_run(ap_index *ix, const Knn &k, uint32_t take, uint32_t shared_p
 int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats) {
     ap_build_opts o{};
     if (opts_in) o = *opts_in;
-    const uint32_t iters = o.iterations ? o.iterations : 8;
+    const uint32_t iters = o.iterations ? o.iterations : 6;
     const float scale = o.dense_scale != 0.f ? o.dense_scale : 7.0f;
     const uint32_t n = ix->n;
     if (n < 2) return fail(AP_ERR_ARG, "a graph needs at least 2 documents");
@@ -1743,6 +1758,17 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     DevBuf db;
     Knn k{};
     k.n = n;
+    // one allocation for the whole k-NN phase (lists, samples, participant lists, inboxes, dense tiles)
+    const uint32_t batch = std::min<uint32_t>(n, 1u << 18);   // nodes per batch of dense tiles
+    {
+        auto r256 = [](size_t b) { return (std::max<size_t>(b, 16) + 255) / 256 * 256; };
+        const size_t total = 2 * r256((size_t)n * kK * 4) + r256((size_t)n * 64 * 4) + r256((size_t)n * 16) + r256((size_t)n * kPart * 4) +
+                             r256((size_t)n * 8) + r256((size_t)n * kPropCap * sizeof(uint2)) + r256((size_t)n * 4) + r256(32) +
+                             r256((size_t)batch * kPart * kNewMax * 4);
+        uint8_t *slab;
+        AP_TRY(db.alloc(&slab, total));
+        db.donate(slab, total);
+    }
     AP_TRY(db.alloc(&k.ids, (size_t)n * kK)); AP_TRY(db.alloc(&k.dis, (size_t)n * kK));
     AP_TRY(db.alloc(&k.samp, (size_t)n * 64)); AP_TRY(db.alloc(&k.scnt, (size_t)n * 4));
     AP_TRY(db.alloc(&k.plist, (size_t)n * kPart)); AP_TRY(db.alloc(&k.pcnt, (size_t)n * 2));
@@ -1756,12 +1782,11 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     AP_TRY(norms_run(ix, power)); ++launches;
     knn_init_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k, o.seed ? o.seed : 20261125u); ++launches;
     const uint32_t shared_pairs = (o.flags & AP_BUILD_SHARED_PAIRS) ? 1u : 0u;
-    if (!(o.flags & AP_BUILD_RANDOM_START)) AP_TRY(seed_run(ix, k, o.seed_take ? std::min<uint32_t>(o.seed_take, 32u) : 4u, shared_pairs, &launches));
-
-    // scratch for the dense tiles, in batches of nodes
-    const uint32_t batch = std::min<uint32_t>(n, 1u << 18);
-    float *D;
+    float *D;   // dense tiles of a node batch; the seeded start borrows the memory for its posting lists
     AP_TRY(db.alloc(&D, (size_t)batch * kPart * kNewMax));
+    if (!(o.flags & AP_BUILD_RANDOM_START))
+        AP_TRY(seed_run(ix, k, o.seed_take ? std::min<uint32_t>(o.seed_take, 32u) : 4u, shared_pairs, &launches, D, (size_t)batch * kPart * kNewMax * sizeof(float)));
+
     uint32_t *err = ix->d_ctl + 1;
 
     JoinArgs ja{};
@@ -1841,12 +1866,25 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     AP_CUDA(cudaDeviceSynchronize());
     const auto t1 = std::chrono::high_resolution_clock::now();
 
-    uint32_t *knn_ids = ix->knn_ids;
-    if (!knn_ids) { AP_CUDA(cudaMalloc(&ix->knn_ids, (size_t)n * kK * 4)); knn_ids = ix->knn_ids; }
-    if (!ix->knn_dis) AP_CUDA(cudaMalloc(&ix->knn_dis, (size_t)n * kK * 4));
+    // The lists go to the pruning step where they lie unless the caller wants them kept; its scratch is carved out of
+    // the k-NN phase's dead buffers (the sample lists take the cleaned ids, the inboxes and the dense tiles the rest).
+    const bool keep = (o.flags & AP_BUILD_KEEP_KNN) != 0;
+    uint32_t *knn_ids = k.samp;
+    const float *knn_dis = k.dis;
+    if (keep) {
+        if (!ix->knn_ids) AP_CUDA(cudaMalloc(&ix->knn_ids, (size_t)n * kK * 4));
+        if (!ix->knn_dis) AP_CUDA(cudaMalloc(&ix->knn_dis, (size_t)n * kK * 4));
+        knn_ids = ix->knn_ids; knn_dis = ix->knn_dis;
+        AP_CUDA(cudaMemcpyAsync(ix->knn_dis, k.dis, (size_t)n * kK * 4, cudaMemcpyDeviceToDevice));
+    }
     knn_finish_kernel<<<(uint32_t)(((size_t)n * kK + 255) / 256), 256>>>(k, knn_ids); ++launches;
-    AP_CUDA(cudaMemcpyAsync(ix->knn_dis, k.dis, (size_t)n * kK * 4, cudaMemcpyDeviceToDevice));
-    AP_TRY(prune_run(ix, knn_ids, ix->knn_dis, power, nullptr, nullptr, &launches, o.flags));
+    {
+        DevBuf pdb;
+        pdb.donate(k.prop, (size_t)n * kPropCap * sizeof(uint2));
+        pdb.donate(D, (size_t)batch * kPart * kNewMax * sizeof(float));
+        pdb.donate(k.plist, (size_t)n * kPart * 4);
+        AP_TRY(prune_run_in(pdb, ix, knn_ids, knn_dis, power, nullptr, nullptr, &launches, o.flags));
+    }
     const auto t2 = std::chrono::high_resolution_clock::now();
 
     uint32_t ew = 0;
@@ -1864,9 +1902,7 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
         // phase times in 10 us units: sample + lists, dense tiles (first batch), sparse + proposals, merge
         for (int ph = 0; ph < 3; ++ph) stats->phase_10us[ph] = (uint32_t)(phase_ms[ph + 1] * 100.f);
     }
-    if (!(o.flags & AP_BUILD_KEEP_KNN)) {
-        cudaFree(ix->knn_ids); cudaFree(ix->knn_dis); ix->knn_ids = nullptr; ix->knn_dis = nullptr;
-    }
+    if (!keep) { cudaFree(ix->knn_ids); cudaFree(ix->knn_dis); ix->knn_ids = nullptr; ix->knn_dis = nullptr; }   // lists of an earlier build
     // the build-time copy is no longer needed once the graph exists
     if (!(o.flags & AP_BUILD_KEEP_KNN)) { cudaFree(ix->rec_build); ix->rec_build = nullptr; ix->build_scale = 0.f; ix->dense_src = nullptr; }
     return AP_OK;

@@ -503,10 +503,15 @@ def section_supplementary(dev, n, nq):
     gt, _, _ = ix.exact_topk(queries, eff, top_k=10)
     sr = Searcher(ix, dev)
     curve = recall_search(sr, queries, eff, t2u(gt), (32, 64, 128, 256, 512))
+    # the sweep's dense-only preset over the same graph: the one preset whose exact top-10 this corpus lets a graph reach
+    eff_d = ix.effective_weights(q100.dense.numpy(), q100.sparse, q100.bm25, 0.0, 0.0, 1.0)
+    gt_d, _, _ = ix.exact_topk(queries, eff_d, top_k=10)
+    curve_d = recall_search(sr, queries, eff_d, t2u(gt_d), (32, 64, 96, 128, 256, 512))
     ix.close()
     return {"corpus": SUPPLEMENTARY_LABEL.format(n=n, nq=nq), "build_seconds": round(bst.seconds_total, 3), "curve": curve,
             "qps_at_recall_0.95": first_reaching(curve), "qps_at_recall_0.90": first_reaching(curve, 0.90), "qps_at_recall_0.75": first_reaching(curve, 0.75),
-            "effective_weights": {"sparse": eff[0], "bm25": eff[1], "dense": eff[2]}}
+            "effective_weights": {"sparse": eff[0], "bm25": eff[1], "dense": eff[2]},
+            "dense_only": {"weights_dense_sparse_bm25": "1/0/0", "graph": "the same hybrid graph", "curve": curve_d, "qps_at_recall_0.95": first_reaching(curve_d)}}
 
 
 def build_roofline(bst, corpus, n, hbm_peak, tc_peak, peak_kind):
@@ -1091,6 +1096,14 @@ def run_reference(args):
             for cc in (32, 64, 128, 256, 512):
                 i_c, _, t_c = rs.search(s1, c3(s2), c3(s3), cc, 7)
                 curve.append({"cands": cc, "qps": round(nq / t_c, 1), "recall_at_10": round(recall_at_10(i_c, gs), 4)})
+            ed = orc.effective_weights(Ds, Ss, Bs, QDs, QSs, QBs, 0.0, 0.0, 1.0)
+            d1, d2, d3 = orc.scale_queries(QDs, QSs, QBs, *ed)
+            gd = exact_gt(cs, qs_, ed)
+            curve_d = []
+            for cc in (32, 64, 96, 128, 256, 512):
+                i_c, _, t_c = rs.search(d1, c3(d2), c3(d3), cc, 1)
+                curve_d.append({"cands": cc, "qps": round(nq / t_c, 1), "recall_at_10": round(recall_at_10(i_c, gd), 4)})
+            sup["dense_only"] = {"weights_dense_sparse_bm25": "1/0/0", "graph": "the same hybrid graph", "curve": curve_d, "qps_at_recall_0.95": first_reaching(curve_d)}
             rs.close()
             sup["curve"] = curve
             sup["qps_at_recall_0.95"] = first_reaching(curve)

@@ -65,7 +65,7 @@ typedef struct {
                                      rule (smallest key per hashed slot) instead of first come, first served */
 
 typedef struct {
-    uint32_t iterations;   /* NN-Descent rounds; 0 = library default (8) */
+    uint32_t iterations;   /* NN-Descent rounds; 0 = library default (6) */
     uint32_t seed;         /* random initial graph; the reference seeds from clock() (src/index.cu:102) */
     uint32_t flags;        /* AP_BUILD_* */
     float dense_scale;     /* build-time dense weight; 0 = 7.0 as in src/index.cu:836-840 */
