@@ -17,7 +17,7 @@ _LIB = None
 AP_OK = 0
 CREATE_FOR_BUILD = 1
 BUILD_SIMT_JOIN, BUILD_KEEP_KNN, BUILD_RANDOM_START, BUILD_SHARED_PAIRS, BUILD_REVERSE_PASS = 1, 2, 4, 8, 16
-BUILD_PRUNE_STEPWISE, BUILD_TRACE, BUILD_DETERMINISTIC = 32, 64, 128
+BUILD_PRUNE_STEPWISE, BUILD_TRACE, BUILD_DETERMINISTIC, BUILD_WIPE_TABLES = 32, 64, 128, 256
 SEARCH_KEYWORD, SEARCH_KG, SEARCH_RAW_WEIGHTS, SEARCH_UNFUSED_DENSE = 1, 2, 4, 8
 DIM, ROW, DEGREE, KNN, ENTRY_POINTS = 1024, 40, 32, 64, 32
 

@@ -70,6 +70,21 @@ __global__ void norms_kernel(uint32_t n, const uint64_t *__restrict__ meta, cons
     if (lane == 0) power[d] = acc;
 }
 
+// Largest sparse / BM25 term id of the corpus (warp per document): decides whether the join and pruning tables can
+// carry a generation number in the spare high bits of their keys.
+__global__ void max_term_kernel(uint32_t n, const uint64_t *__restrict__ meta, const uint8_t *__restrict__ rec, uint32_t *__restrict__ out) {
+    const uint32_t d = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
+    if (d >= n) return;
+    const uint64_t m = meta[d];
+    const uint2 *pairs = reinterpret_cast<const uint2 *>(rec + meta_off16(m) * 16ull + kDenseBytes);
+    const uint32_t ns = meta_ns(m), nb = meta_nb(m), pns = pad2(ns);
+    uint32_t mx = 0;
+    for (uint32_t j = lane; j < ns; j += 32) mx = max(mx, pairs[j].x);
+    for (uint32_t j = lane; j < nb; j += 32) mx = max(mx, pairs[pns + j].x);
+    mx = __reduce_max_sync(kFull, mx);
+    if (lane == 0 && mx) atomicMax(out, mx);
+}
+
 // ---------------------------------------------------------------------------------------------------------
 // NN-Descent state
 // ---------------------------------------------------------------------------------------------------------
@@ -490,12 +505,17 @@ __global__ void __launch_bounds__(256, 2) join_dense_simt_kernel(uint32_t node0,
 __device__ __forceinline__ uint32_t ck_h1(uint32_t key, uint32_t shift) { return (key * 2654435761u) >> shift; }
 __device__ __forceinline__ uint32_t ck_h2(uint32_t key, uint32_t shift) { return ((key ^ 0x5bd1e995u) * 0x85ebca6bu + 0x1b873593u) >> shift; }
 // Lock-free key insertion by eviction into table g; false when the kick budget runs out (the caller gives the row up).
+// Generations: when the ids leave their high bits free, the keys of one pass carry the pass number there (gen_mask
+// selects those bits, the key holds the current number).  A slot whose key carries another number is left over
+// from an earlier pass: an insertion takes it as if it were empty and no probe can match it, so the tables are
+// never emptied between passes.  gen_mask = 0: plain keys, tables wiped by the caller.
 template <int G>
-__device__ __forceinline__ bool ck_insert_key(uint32_t *K, uint32_t g, uint32_t shift, uint32_t key) {
+__device__ __forceinline__ bool ck_insert_key(uint32_t *K, uint32_t g, uint32_t shift, uint32_t key, uint32_t gen_mask = 0u) {
+    const uint32_t gen = key & gen_mask;
     uint32_t h = ck_h1(key, shift);
     for (int kick = 0; kick < 48; ++kick) {
         const uint32_t old = atomicExch(K + h * G + g, key);
-        if (old == kEmpty) return true;
+        if (old == kEmpty || (old & gen_mask) != gen) return true;
         key = old;
         const uint32_t a1 = ck_h1(key, shift), a2 = ck_h2(key, shift);
         h = h == a1 ? a2 : a1;
@@ -543,6 +563,7 @@ struct JoinArgs {
     uint32_t prop_per;                     // partners proposed to each participant (<= kPropPerMax)
     uint32_t shared_pairs;                 // see pair_owned
     uint32_t det;                          // see offer_proposal
+    uint32_t gen_shift;                    // pass number goes to key bits gen_shift .. 30 (see ck_insert_key); 0 = tables are wiped
     uint32_t o_tab, o_dm, o_arena;
 };
 constexpr int kJoinThreads = 512;
@@ -564,7 +585,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     __shared__ uint64_t mbar;
     __shared__ uint32_t s_off[kPart + 1], s_id[kPart], s_ns[kPart], s_nb[kPart];
     __shared__ float s_kth[kPart];
-    __shared__ uint32_t s_rows, s_new, s_bad;
+    __shared__ uint32_t s_rows, s_new, s_bad[2];   // s_bad: one word per pass parity, reset a pass ahead
     const uint32_t tabn = a.tab_mask + 1;
     uint32_t *K = reinterpret_cast<uint32_t *>(smem + a.o_tab);   // [slot][G] keys, then [slot][G] value words
     uint32_t *V = K + (size_t)tabn * G;
@@ -576,7 +597,7 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     const uint32_t v = a.node0 + local;
     uint32_t n_new = a.pcnt[(size_t)v * 2], rows = a.pcnt[(size_t)v * 2 + 1];
     if (rows <= 1) return;
-    if (tid == 0) { mbar_init(&mbar, 1); mbar_fence_init(); s_bad = 0; }
+    if (tid == 0) { mbar_init(&mbar, 1); mbar_fence_init(); s_bad[0] = 0; s_bad[1] = 0; }
     if (tid < kPart) {
         const uint32_t id = tid < (int)rows ? a.plist[(size_t)v * kPart + tid] : kEmpty;
         s_id[tid] = id;
@@ -617,8 +638,10 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
     __syncthreads();
     const float *D = s_D;
     unsigned long long evals = 0;
+    const uint32_t gen_mask = a.gen_shift ? (0x7FFFFFFFu >> a.gen_shift) << a.gen_shift : 0u;
     for (uint32_t i0 = 0; i0 < n_new; i0 += G) {
         const uint32_t g_cnt = min((uint32_t)G, n_new - i0);
+        const uint32_t gen = a.gen_shift ? (i0 / G) << a.gen_shift : 0u;   // this pass's number, in the keys' spare bits
         // hash the terms of rows i0 .. i0+g_cnt-1 (BM25 ids get bit 31 so both vocabularies share one table), a
         // quarter of the CTA per row: keys first, then every value to the slot its key settled in
         constexpr uint32_t kSlice = kJoinThreads / 4;
@@ -627,22 +650,23 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
             const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[i]);
             const uint32_t ns = s_ns[i], nb = s_nb[i], pns = pad2(ns);
             for (uint32_t j = tid % kSlice; j < ns + nb; j += kSlice) {
-                const uint32_t id = j < ns ? pr[j].x : (pr[pns + (j - ns)].x | 0x80000000u);
-                if (!ck_insert_key<G>(K, g, a.tab_shift, id)) atomicOr(&s_bad, 1u << g);
+                const uint32_t id = (j < ns ? pr[j].x : (pr[pns + (j - ns)].x | 0x80000000u)) | gen;
+                if (!ck_insert_key<G>(K, g, a.tab_shift, id, gen_mask)) atomicOr(&s_bad[(i0 / G) & 1u], 1u << g);
             }
         }
         __syncthreads();
+        const uint32_t bad = s_bad[(i0 / G) & 1u];   // rows whose table could not be built sit this join out
+        if (tid == 0) s_bad[((i0 / G) & 1u) ^ 1u] = 0;   // the next pass's word: nobody touches it before the barrier after the probing
         for (uint32_t g = tid / kSlice; g < g_cnt; g += 4) {
             const uint32_t i = i0 + g;
             const uint2 *pr = reinterpret_cast<const uint2 *>(arena + s_off[i]);
             const uint32_t ns = s_ns[i], nb = s_nb[i], pns = pad2(ns);
             for (uint32_t j = tid % kSlice; j < ns + nb; j += kSlice) {
                 const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
-                ck_store_value<G>(K, V, g, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y);
+                ck_store_value<G>(K, V, g, a.tab_shift, (j < ns ? p.x : (p.x | 0x80000000u)) | gen, p.y);
             }
         }
         __syncthreads();
-        const uint32_t bad = s_bad;   // rows whose table could not be built sit this join out
         // One warp per participant j: its terms pass through registers 64 at a time (the two slot indices of each
         // computed once -- every table uses the same hashes) and are probed against the key lines of the group.
         for (uint32_t j = warp; j < rows; j += kJoinThreads / 32) {
@@ -655,8 +679,8 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
 #pragma unroll
                 for (int t = 0; t < kJoinSlots; ++t) {
                     const uint32_t q = base + t * 32 + lane;
-                    uint2 p = make_uint2(kEmpty, 0u);   // padding: matches only an empty slot, whose value is 0
-                    if (q < nt) { p = q < ns ? pr[q] : pr[pns + (q - ns)]; if (q >= ns) p.x |= 0x80000000u; }
+                    uint2 p = make_uint2(kEmpty, 0u);   // padding: matches only an empty slot, and its own value is 0
+                    if (q < nt) { p = q < ns ? pr[q] : pr[pns + (q - ns)]; if (q >= ns) p.x |= 0x80000000u; p.x |= gen; }
                     key[t] = p.x; val[t] = __uint_as_float(p.y);
                     h1[t] = ck_h1(p.x, a.tab_shift); h2[t] = ck_h2(p.x, a.tab_shift);
                 }
@@ -688,7 +712,8 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
                 if ((lane & 7) == 0 && g < g_cnt && i < j) { dm[i * kPart + j] = ((bad >> g) & 1u) ? kInfDis : 1.0f - D[(size_t)j * kNewMax + i] - r; ++evals; }
             }
         }
-        __syncthreads();
+        __syncthreads();   // every warp is done with this pass's tables
+        if (gen_mask && !bad) continue;   // the next pass's keys carry another number: nothing to empty
         // empty the tables again: every term wipes the slots that hold its key
         if (bad) { for (uint32_t q = tid; q < tabn * G; q += kJoinThreads) { K[q] = kEmpty; V[q] = 0u; } }
         else {
@@ -704,7 +729,6 @@ __global__ void __launch_bounds__(kJoinThreads, 2) join_sparse_kernel(const Join
                 }
             }
         }
-        if (tid == 0) s_bad = 0;
         __syncthreads();
     }
 
@@ -1105,6 +1129,7 @@ constexpr int kP2Groups = 4;   // candidate rows hashed per pass
 struct Prune2Args {
     PruneArgs p;
     uint32_t groups;                       // <= kP2Groups
+    uint32_t gen_shift;                    // pass number in key bits gen_shift .. 30 (see ck_insert_key); 0 = tables are wiped
     uint32_t o_ip, o_kw, o_region, region_bytes;
     uint32_t *ovf_list, *ovf_cnt, *err;
 };
@@ -1114,7 +1139,7 @@ struct Prune2Args {
 // when the candidate lacks the term, which leaves the running sum as it is) -- the reference's per-lane order.
 template <int NS, bool BM, int G>
 __device__ __forceinline__ void p2_section(const uint2 *__restrict__ row, uint32_t cnt, const uint32_t *__restrict__ K, const uint32_t *__restrict__ V,
-                                           uint32_t shift, int lane, float (&part)[kP2Groups], uint32_t &kwm) {
+                                           uint32_t shift, uint32_t gen, int lane, float (&part)[kP2Groups], uint32_t &kwm) {
     for (uint32_t j0 = 0; j0 < cnt; j0 += 32 * NS) {
         uint32_t key[NS], h1[NS], h2[NS], ownbit = 0;
         float val[NS];
@@ -1125,6 +1150,7 @@ __device__ __forceinline__ void p2_section(const uint2 *__restrict__ row, uint32
             if (j < cnt) {
                 pv = row[j];
                 if (BM) { ownbit |= (pv.x >> 31) << t; pv.x |= 0x80000000u; }
+                pv.x |= gen;
             }
             key[t] = pv.x; val[t] = __uint_as_float(pv.y);
             h1[t] = ck_h1(pv.x, shift); h2[t] = ck_h2(pv.x, shift);
@@ -1319,8 +1345,10 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
     }
     __syncthreads();
 
+    const uint32_t gen_mask = q.gen_shift ? (0x7FFFFFFFu >> q.gen_shift) << q.gen_shift : 0u;
     for (uint32_t b0 = 0; b0 < (uint32_t)kK; b0 += G) {
         const uint32_t g_cnt = min((uint32_t)G, (uint32_t)kK - b0);
+        const uint32_t gen = q.gen_shift ? (b0 / G) << q.gen_shift : 0u;   // this pass's number, in the keys' spare bits
         // the G candidate rows are hashed side by side: a quarter of the CTA per row
         constexpr uint32_t kSlice = kP2Threads / 4;
         for (uint32_t gi = tid / kSlice; gi < g_cnt; gi += 4) {
@@ -1329,8 +1357,8 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
             const uint2 *pr = reinterpret_cast<const uint2 *>(region + s_off[b]);
             const uint32_t ns = meta_ns(meta0[b]), nb = meta_nb(meta0[b]), pns = pad2(ns);
             for (uint32_t j = tid % kSlice; j < ns + nb; j += kSlice) {
-                const uint32_t id = j < ns ? pr[j].x : (pr[pns + (j - ns)].x | 0x80000000u);
-                if (!ck_insert_key<G>(K, gi, a.tab_shift, id)) s_fit = 0;
+                const uint32_t id = (j < ns ? pr[j].x : (pr[pns + (j - ns)].x | 0x80000000u)) | gen;
+                if (!ck_insert_key<G>(K, gi, a.tab_shift, id, gen_mask)) s_fit = 0;
             }
         }
         __syncthreads();
@@ -1345,7 +1373,7 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
             const uint32_t ns = meta_ns(meta0[b]), nb = meta_nb(meta0[b]), pns = pad2(ns);
             for (uint32_t j = tid % kSlice; j < ns + nb; j += kSlice) {
                 const uint2 p = j < ns ? pr[j] : pr[pns + (j - ns)];
-                ck_store_value<G>(K, V, gi, a.tab_shift, j < ns ? p.x : (p.x | 0x80000000u), p.y);
+                ck_store_value<G>(K, V, gi, a.tab_shift, (j < ns ? p.x : (p.x | 0x80000000u)) | gen, p.y);
             }
         }
         __syncthreads();
@@ -1355,8 +1383,8 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
             const uint32_t ns = meta_ns(meta0[ar]), nb = meta_nb(meta0[ar]), pns = pad2(ns);
             float sp[kP2Groups] = {0.f, 0.f, 0.f, 0.f}, bm[kP2Groups] = {0.f, 0.f, 0.f, 0.f};
             uint32_t kwm = 0;   // bit g: a BM25 term of row a that the node owns and candidate g lacks
-            p2_section<4, false, G>(pr, ns, K, V, a.tab_shift, lane, sp, kwm);
-            p2_section<2, true, G>(pr + pns, nb, K, V, a.tab_shift, lane, bm, kwm);
+            p2_section<4, false, G>(pr, ns, K, V, a.tab_shift, gen, lane, sp, kwm);
+            p2_section<2, true, G>(pr + pns, nb, K, V, a.tab_shift, gen, lane, bm, kwm);
             float tot[kP2Groups];
 #pragma unroll
             for (int gi = 0; gi < kP2Groups; ++gi) tot[gi] = __fadd_rn(sp[gi], bm[gi]);
@@ -1379,7 +1407,8 @@ __global__ void __launch_bounds__(kP2Threads, 1) prune_pairs_kernel(const Prune2
                 KW[b * kK + ar] = (kw_any >> gi) & 1u;
             }
         }
-        __syncthreads();
+        __syncthreads();   // every warp is done with this pass's tables
+        if (gen_mask) continue;   // the next pass's keys carry another number: nothing to empty
         // empty the tables again: every term wipes the slots that hold its key
         for (uint32_t gi = tid / kSlice; gi < g_cnt; gi += 4) {
             const uint32_t b = b0 + gi;
@@ -1592,6 +1621,29 @@ static int sort_u64_pairs(DevBuf &db, unsigned long long *keys, uint32_t *vals, 
     return AP_OK;
 }
 
+// Largest term id of the corpus, computed once per index.
+static int max_term_run(ap_index *ix, uint32_t *out) {
+    if (!ix->max_term_known) {
+        if (!ix->rec_build) return fail(AP_ERR_STATE, "the index was created without AP_CREATE_FOR_BUILD");
+        uint32_t *d = ix->d_ctl + 3;   // spare control word
+        AP_CUDA(cudaMemsetAsync(d, 0, 4));
+        max_term_kernel<<<(ix->n + 7) / 8, 256>>>(ix->n, ix->meta, ix->rec_build, d);
+        AP_CUDA(cudaGetLastError());
+        AP_CUDA(cudaMemcpy(&ix->max_term, d, 4, cudaMemcpyDeviceToHost));
+        ix->max_term_known = true;
+    }
+    *out = ix->max_term;
+    return AP_OK;
+}
+// Key bit from which the pass number of a table is stored (see ck_insert_key), or 0 when the ids leave no room for
+// `passes` numbers below bit 31.
+static uint32_t gen_shift_for(uint32_t max_term, uint32_t passes) {
+    uint32_t bits = 0;
+    while ((1u << bits) < passes) ++bits;
+    const uint32_t shift = 31u - bits;
+    return (bits > 0 && max_term < (1u << shift) - 1u) ? shift : 0u;
+}
+
 int norms_run(ap_index *ix, float *d_power) {
     if (!ix->rec_build) return fail(AP_ERR_STATE, "the index was created without AP_CREATE_FOR_BUILD");
     norms_kernel<<<(ix->n + 7) / 8, 256>>>(ix->n, ix->meta, ix->rec_build, d_power);
@@ -1636,6 +1688,11 @@ static int prune_run_in(DevBuf &db, ap_index *ix, const uint32_t *d_knn, const f
     uint32_t groups = kP2Groups;
     while (groups > 1 && q.p.o_tab + (size_t)groups * tabn * 8 + 96 * 1024 > avail) groups >>= 1;   // key lines are 1, 2 or 4 wide
     q.groups = groups;
+    {
+        uint32_t max_term = 0;
+        AP_TRY(max_term_run(ix, &max_term));
+        q.gen_shift = (flags & AP_BUILD_WIPE_TABLES) ? 0u : gen_shift_for(max_term, (kK + groups - 1) / groups);
+    }
     q.o_region = (uint32_t)((q.p.o_tab + (size_t)groups * tabn * 8 + 127) / 128 * 128);
     const bool pairs_ok = avail >= (size_t)q.o_region + 64 * 1024 && !(flags & AP_BUILD_PRUNE_STEPWISE);
     uint32_t n_step = n;
@@ -1800,6 +1857,11 @@ int build_run(ap_index *ix, const ap_build_opts *opts_in, ap_build_stats *stats)
     const size_t per_cta = ix->smem_per_sm / 2 - 1024 - 10240 /* static: dense tile + bookkeeping */;
     // key lines of a group are 1, 2 or 4 wide; four tables may take up to 40 % of the CTA's shared memory
     ja.groups = 8 * (size_t)tabn * 4 <= per_cta * 2 / 5 ? 4u : (8 * (size_t)tabn * 2 <= per_cta / 3 ? 2u : 1u);
+    {
+        uint32_t max_term = 0;
+        AP_TRY(max_term_run(ix, &max_term));
+        ja.gen_shift = (o.flags & AP_BUILD_WIPE_TABLES) ? 0u : gen_shift_for(max_term, (kNewMax + ja.groups - 1) / ja.groups);
+    }
     ja.o_tab = 0; ja.o_dm = 8 * tabn * ja.groups; ja.o_arena = (ja.o_dm + 4 * kNewMax * kPart + 127) / 128 * 128;
     if (per_cta <= ja.o_arena + 8u * (pad2(ix->max_ns) + pad2(ix->max_nb)) * 2)
         return fail(AP_ERR_LIMIT, "rows of %u + %u terms leave no room for a local join in shared memory", ix->max_ns, ix->max_nb);

@@ -94,6 +94,8 @@ struct ap_index {
     size_t rec_total = 0;          // bytes of one pool
     uint64_t *meta = nullptr;      // n locator words
     uint32_t max_rec_bytes = 0, max_ns = 0, max_nb = 0;
+    uint32_t max_term = 0;         // largest sparse / BM25 term id, found by the first build or pruning call
+    bool max_term_known = false;
 
     uint32_t *graph = nullptr;     // n x 40, index.poe rows
     apoe::FatEdge *fat = nullptr;  // n x 40

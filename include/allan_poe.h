@@ -63,6 +63,9 @@ typedef struct {
 #define AP_BUILD_TRACE 64u        /* per-round and per-phase progress lines on stderr */
 #define AP_BUILD_DETERMINISTIC 128u /* one seed, one graph: reverse samples and proposals are kept by an order-independent
                                      rule (smallest key per hashed slot) instead of first come, first served */
+#define AP_BUILD_WIPE_TABLES 256u /* empty the shared-memory term tables of the joins and of the pruning between passes.
+                                     Default: where the term ids leave high bits free the keys carry the pass number
+                                     instead and nothing is emptied; same results either way (debug / cross-check) */
 
 typedef struct {
     uint32_t iterations;   /* NN-Descent rounds; 0 = library default (6) */
@@ -247,7 +250,7 @@ int ap_index_norms(ap_index *ix, float *out);
  * (n x 33: count + 32 ids) and final rows (n x 40) to host memory; any output may be NULL.  Also installs the rows
  * and the entry points derived from `power` as the index's graph. */
 int ap_index_prune(ap_index *ix, const uint32_t *knn_ids, const float *knn_dis, const float *power,
-                   uint32_t flags /* AP_BUILD_PRUNE_STEPWISE | AP_BUILD_TRACE */, uint32_t *new_list,
+                   uint32_t flags /* AP_BUILD_PRUNE_STEPWISE | AP_BUILD_TRACE | AP_BUILD_WIPE_TABLES */, uint32_t *new_list,
                    uint32_t *keyword_edges, uint32_t *rows);
 
 /* Knowledge graph for AP_SEARCH_KG (ref: load_kg_graph src/query.cu:89-108 and the uploads of :1963-1980).

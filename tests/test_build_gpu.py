@@ -23,11 +23,11 @@ def test_norms_match_oracle_bitwise(tiny, bix):
     assert np.array_equal(got.view(np.uint32), tiny.power.view(np.uint32))
 
 
-@pytest.fixture(params=["pairs", "stepwise"])
+@pytest.fixture(params=["pairs", "pairs_wiped_tables", "stepwise"])
 def prune_kernel(request):
-    """Both pruning kernels: the all-pairs one (default) and the step-wise one it falls back to; the value is the
-    build-flag word that selects it."""
-    return apoe.BUILD_PRUNE_STEPWISE if request.param == "stepwise" else 0
+    """The pruning kernels: the all-pairs one (default; its term tables numbered by pass or emptied between passes) and
+    the step-wise one it falls back to; the value is the build-flag word that selects it."""
+    return {"pairs": 0, "pairs_wiped_tables": apoe.BUILD_WIPE_TABLES, "stepwise": apoe.BUILD_PRUNE_STEPWISE}[request.param]
 
 
 def test_prune_and_rows_match_oracle_bitwise(tiny, bix, prune_kernel):
@@ -251,4 +251,30 @@ def test_deterministic_build_gives_one_graph_per_seed():
     assert np.array_equal(a[2], b[2]) and np.array_equal(a[3], b[3]) and a[4] == b[4]
     assert not np.array_equal(a[2], c[2])
     assert a[5] >= base - 0.05, (a[5], base)
+    ix.close()
+
+
+def test_numbered_and_wiped_term_tables_give_the_same_distances():
+    """The joins either number the keys of their shared-memory term tables by pass (default where the term ids leave
+    high bits free) or empty the tables between passes (AP_BUILD_WIPE_TABLES).  The numbering changes the hash slots,
+    so the rare rows whose two-choice table cannot be built -- they sit one join out -- are not the same rows and the
+    two builds drift apart a little: the lists have to agree almost everywhere, and a pair both hold has to carry the
+    same distance up to the order of the float sums (which of the two rows was hashed and which streamed) -- a term
+    product lost or added by a wrong slot would show as a difference of 0.01 and more.  (The pruning kernel is
+    compared output for output by the prune_kernel fixture above.)"""
+    ds = helpers.make_dataset(6000, 4, seed=22, with_graph=False)
+    ix = apoe.Index.from_host(ds.D, ds.S, ds.B, for_build=True)
+    out = []
+    for extra in (0, apoe.BUILD_WIPE_TABLES):
+        st = ix.build(flags=apoe.BUILD_KEEP_KNN | apoe.BUILD_DETERMINISTIC | extra, seed=9)
+        ids, dis, _ = ix.get_knn()
+        key = (np.arange(ids.shape[0], dtype=np.uint64)[:, None] << np.uint64(32)) | ids.astype(np.uint64)
+        out.append((key.ravel(), dis.ravel().copy(), st.distance_evals))
+    (ka, da, ea), (kb, db, eb) = out
+    assert abs(int(ea) - int(eb)) <= 0.001 * ea, (ea, eb)
+    common, ia, ib = np.intersect1d(ka, kb, return_indices=True)
+    assert common.size >= 0.995 * ka.size, common.size / ka.size
+    diff = np.abs(da[ia] - db[ib])
+    assert float(diff.max()) <= 2e-4, float(diff.max())
+    assert float(np.mean(diff == 0)) >= 0.98, float(np.mean(diff == 0))
     ix.close()
