@@ -129,6 +129,10 @@ __device__ __forceinline__ unsigned long long shard_key(uint32_t local_id, float
 #endif
 constexpr int kScoreBatch = AP_SCORE_BATCH;  // records a warp scores side by side (independent instruction streams)
 constexpr int kPerfectMax = 32; // query rows up to this many terms get a collision-free hash table
+#ifndef AP_SLOTS_PER_TERM
+#define AP_SLOTS_PER_TERM 8
+#endif
+constexpr uint32_t kSlotsPerTerm = AP_SLOTS_PER_TERM;  // table slots per query term: fewer slots leave more of the CTA's shared memory to the arena
 
 // One section of R staged records against the query row's collision-free table: every lane takes the pairs
 // j = lane, lane + 32, ... in ascending order, NS per pass with all loads of a pass in flight together; a miss adds a
@@ -261,7 +265,7 @@ __device__ __forceinline__ void score_records(const uint8_t *const (&rec)[R], co
 }
 
 // Collision-free multiplier for a query row of up to 32 terms (one per lane of the calling warp): the first of a
-// fixed sequence of odd constants under which all slots differ.  0 when none of 64 candidates works (or the row is
+// fixed sequence of odd constants under which all slots differ.  0 when none of 128 candidates works (or the row is
 // longer, or holds a repeated id): the caller then scores through the terms.  Fills the (pre-cleared) table.
 __device__ __forceinline__ uint32_t build_perfect_table(const uint2 *terms, uint32_t n, uint2 *tab, uint32_t shift, int lane) {
     if (n == 0 || n > (uint32_t)kPerfectMax || shift == 0) return 0;
@@ -269,7 +273,7 @@ __device__ __forceinline__ uint32_t build_perfect_table(const uint2 *terms, uint
     const uint2 t = on ? terms[lane] : make_uint2(0u, 0u);
     const uint32_t key = t.x & 0x7FFFFFFFu;
     uint32_t found = 0, slot = 0;
-    for (uint32_t trial = 0; trial < 64 && !found; ++trial) {
+    for (uint32_t trial = 0; trial < 128 && !found; ++trial) {
         const uint32_t mult = (0x9E3779B1u + trial * 0x3C6EF372u) | 1u;
         slot = on ? ((key * mult) >> shift) : (0x80000000u | (uint32_t)lane);
         const uint32_t grp = __match_any_sync(kFull, slot);
@@ -947,9 +951,10 @@ static uint32_t layout(SearchArgs &a, const ap_index *ix, uint32_t warps, uint32
     a.o_info = take(8 * 64, 16);   // batch entries of the two arena halves
     a.o_sq = take((flags & PF_SPARSE) ? 8 * std::max(1u, max_qs) : 0, 16);
     a.o_bq = take((flags & PF_BM25) ? 8 * std::max(1u, max_qb) : 0, 16);
-    // collision-free tables for short query rows: 16 slots per term keeps the search for a multiplier short
-    a.ts_slots = ((flags & PF_SPARSE) && max_qs <= (uint32_t)kPerfectMax) ? pow2_at_least(16 * std::max(1u, max_qs)) : 0u;
-    a.tb_slots = ((flags & PF_BM25) && max_qb <= (uint32_t)kPerfectMax) ? pow2_at_least(16 * std::max(1u, max_qb)) : 0u;
+    // collision-free tables for short query rows: kSlotsPerTerm slots per term (a multiplier is found within a few
+    // trials: 30 terms in 256 slots are collision-free under one random multiplier in six)
+    a.ts_slots = ((flags & PF_SPARSE) && max_qs <= (uint32_t)kPerfectMax) ? pow2_at_least(kSlotsPerTerm * std::max(1u, max_qs)) : 0u;
+    a.tb_slots = ((flags & PF_BM25) && max_qb <= (uint32_t)kPerfectMax) ? pow2_at_least(kSlotsPerTerm * std::max(1u, max_qb)) : 0u;
     a.ts_shift = a.ts_slots ? 32 - log2u(a.ts_slots) : 0u;
     a.tb_shift = a.tb_slots ? 32 - log2u(a.tb_slots) : 0u;
     a.o_ts = take(8 * a.ts_slots, 16);
@@ -1076,8 +1081,9 @@ int distances_launch(ap_index *ix, const SearchLaunch &L, size_t n_pairs, const 
 // Gather probe: what the memory system gives this access pattern when nothing else is done with the data.  Same CTA
 // count and the same shared-memory budget as the search kernel; warp 0 of every CTA keeps both arena halves filled with
 // bulk copies of whole records of pseudo-random documents (the other warps, which would be scoring, idle), for a fixed
-// number of batches.  The bytes moved / the kernel time is the ceiling a search over this index can reach in gathered
-// bytes: random ~3.5 KB reads do not reach the streaming-copy bandwidth.
+// number of batches, refilling a half the moment it has landed.  The bytes moved / the kernel time is the ceiling a
+// search over this index can reach in gathered bytes with this footprint; the search itself holds a half while it
+// scores it, so it keeps fewer bytes in flight than the probe does.
 // ---------------------------------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kSearchThreads, kSearchCtas) gather_probe_kernel(const uint8_t *__restrict__ rec, const uint64_t *__restrict__ meta,
                                                                                   uint32_t n, uint32_t batches, uint32_t per_batch, uint32_t half_bytes,
@@ -1091,16 +1097,23 @@ __global__ void __launch_bounds__(kSearchThreads, kSearchCtas) gather_probe_kern
     if (warp != 0) return;
     unsigned long long moved = 0;
     uint32_t phase = 0, counter = blockIdx.x * 0x9E3779B1u;
+    // the locator of a lane's next document is read one batch ahead (the search gets it with the graph row), so the
+    // probe times the record copies and not a dependent lookup in front of each of them
+    auto locator = [&]() -> uint64_t {
+        uint32_t x = (counter + (uint32_t)lane) * 0x85EBCA6Bu; x ^= x >> 15; x *= 0x2C1B3C6Du; x ^= x >> 13;
+        return meta[x % n];
+    };
+    uint64_t m_next = (uint32_t)lane < per_batch ? locator() : 0ull;
     auto issue = [&](int h) {
         uint32_t sz = 0;
         const uint8_t *src = nullptr;
+        const uint64_t m = m_next;
+        counter += per_batch;
+        m_next = (uint32_t)lane < per_batch ? locator() : 0ull;
         if ((uint32_t)lane < per_batch) {
-            uint32_t x = (counter + (uint32_t)lane) * 0x85EBCA6Bu; x ^= x >> 15; x *= 0x2C1B3C6Du; x ^= x >> 13;
-            const uint64_t m = meta[x % n];
             sz = kDenseBytes + 8u * (pad2(meta_ns(m)) + pad2(meta_nb(m)));
             src = rec + meta_off16(m) * 16ull;
         }
-        counter += 32;
         uint32_t incl = sz;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
@@ -1226,8 +1239,12 @@ extern "C" int ap_debug_gather_probe(ap_index *ix, uint32_t batches, double *gb_
     AP_CUDA(cudaMemset(d_bytes, 0, 8));
     const uint32_t grid = (uint32_t)kSearchCtas * (uint32_t)ix->num_sms;
     AP_CUDA(cudaEventRecord(ix->ev0, 0));
+    // Lanes that look a locator up per batch: two more than records of average size fit a half.  Every lookup is a
+    // random 8-byte read, which costs the memory system far more than its size, and the search does not make them
+    // (a graph row brings the locators of its 32 neighbours in one 512-byte read).
+    const uint32_t per_batch = std::min<uint32_t>(32u, (uint32_t)(half_bytes / std::max<size_t>(ix->rec_total / ix->n, 1)) + 2u);
     // the launch asks for the search kernel's full footprint, so the same number of CTAs shares an SM
-    gather_probe_kernel<<<grid, kSearchThreads, std::max(smem, (size_t)fixed + arena)>>>(ix->rec, ix->meta, ix->n, batches ? batches : 2000u, 32u, half_bytes, halves,
+    gather_probe_kernel<<<grid, kSearchThreads, std::max(smem, (size_t)fixed + arena)>>>(ix->rec, ix->meta, ix->n, batches ? batches : 2000u, per_batch, half_bytes, halves,
                                                                                          d_bytes, ix->d_ctl + 1);
     AP_CUDA(cudaGetLastError());
     AP_CUDA(cudaEventRecord(ix->ev1, 0));
