@@ -24,7 +24,7 @@ namespace apoe {
 #define AP_SEARCH_THREADS 96    // threads of one CTA = one query in flight (a multiple of 32, at least 32)
 #endif
 #ifndef AP_SEARCH_CTAS
-#define AP_SEARCH_CTAS 5        // CTAs the kernel is compiled to fit on one SM (registers) and the arena is sized for (shared memory)
+#define AP_SEARCH_CTAS 6        // CTAs the kernel is compiled to fit on one SM (registers) and the arena is sized for (shared memory)
 #endif
 constexpr int kSearchThreads = AP_SEARCH_THREADS;   // the throughput shape: batches that fill the GPU
 constexpr int kSearchWarps = kSearchThreads / 32;
@@ -38,9 +38,11 @@ constexpr uint32_t kFull = 0xFFFFFFFFu;
 constexpr int kMaxIter = 1000;    // ref: MAX_ITER, src/query.cu:7
 constexpr int kHashReset = 4;     // ref: HASH_RESET, src/query.cu:16
 constexpr int kKeywordRing = 32;  // ref: KEYWORD, src/query.cu:18
+constexpr int kMaxSlots = 16;     // ring slots of the staging arena (a "filled" and a "free" mbarrier each)
+constexpr uint32_t kHeaderBytes = 16u * kMaxSlots + 64u;   // the mbarriers, then 16 control words
 
 enum : int { PF_DENSE = 1, PF_SPARSE = 2, PF_BM25 = 4, PF_KEYWORD = 8, PF_KG = 16, PF_UNFUSED = 32 };
-enum : int { CTL_QUERY = 0, CTL_SEL = 1, CTL_BATCH = 2 /* and 3: one word per arena half */, CTL_MERGE = 4, CTL_SLOT = 5, CTL_KWNUM = 6, CTL_M = 7, CTL_MULT_S = 8, CTL_MULT_B = 9 };
+enum : int { CTL_QUERY = 0, CTL_SEL = 1, CTL_NPAIRS = 2, CTL_NEXT = 3, CTL_MERGE = 4, CTL_SLOT = 5, CTL_KWNUM = 6, CTL_M = 7, CTL_MULT_S = 8, CTL_MULT_B = 9 };
 
 struct SearchArgs {
     const FatEdge *fat;
@@ -64,7 +66,8 @@ struct SearchArgs {
     uint32_t *ctl;            // [0] next query, [1] error word
     unsigned long long *cnt;  // [0] expansions, [1] evaluations, [2] gathered bytes
     uint32_t arena_bytes;
-    uint32_t half_bytes, halves;   // the arena as one staging area or as two halves filled alternately
+    uint32_t slot_bytes, slots;    // the arena as a ring of slots, each holding the records one warp scores side by side
+    uint32_t single;               // 1: a slot holds one record (records too large for two per slot)
     uint32_t vis_mask;           // visited table size - 1
     uint32_t ts_slots, ts_shift; // collision-free table of the query's sparse row (0 slots: not allocated)
     uint32_t tb_slots, tb_shift; // same for the BM25 row
@@ -94,7 +97,7 @@ struct Ctx {  // per-thread view of the CTA's shared state
     uint32_t *kw_id;
     float *kw_dis;
     uint8_t *arena;
-    uint32_t phase;
+    uint32_t gpair;     // slots filled so far by this CTA: slot = gpair % slots, barrier phase = gpair / slots
     unsigned long long c_exp, c_eval, c_bytes;
     long long t_wait, t_score, t_ctl, t_sort, t_merge, t_mark;   // clock64 phase totals (thread 0)
     int tid, lane, warp;
@@ -316,118 +319,159 @@ __device__ __forceinline__ uint32_t count_lt(const float *arr, uint32_t n, float
 }
 
 // Score the pool slots [base, base + 32) flagged by `need` (lane j of warp 0 owns slot base + j and that
-// document's locator word).  Warp 0 packs the needed records into the arena in as few batches as fit, issues one
-// bulk copy per record and arms the mbarrier with the batch's byte count; every warp then scores its share.
+// document's locator word).  The arena is a ring of slots, each holding the records one warp scores side by side
+// (kScoreBatch of them, one when the records are too large).  Warp 0 is the producer: for every group of needed
+// records, in lane order, it waits until the slot's previous content has been scored ("free" mbarrier), writes the
+// group's entry, arms the slot's "filled" mbarrier with the byte count and issues one bulk copy per record (the
+// groups that find a free slot at once are issued by all their lanes together).  A consumer warp waits for its
+// group's slot to be filled, scores the records out of shared memory and releases the slot.  No CTA-wide barrier
+// inside an expansion: slots are refilled one by one as they are released, so all but the slots being scored are in
+// flight.
 // pool_dis[base + j] receives the distance; keyword hits set bit 30 of pool_id[base + j].
 // Called by all threads of the CTA; ends with the CTA synchronised.
 template <int F, int NT>
 __device__ __forceinline__ void score_slots(const SearchArgs &a, Ctx &c, const uint32_t (&qreg)[16], uint32_t base,
                                             uint64_t my_meta, bool my_need) {
     constexpr bool D = (F & PF_DENSE) != 0, S = (F & PF_SPARSE) != 0, B = (F & PF_BM25) != 0, KW = (F & PF_KEYWORD) != 0;
-    uint32_t remaining = 0, pre_start = 0, pre_end = 0, ns = 0, nb = 0;
+    static_assert(NT >= 64, "the search CTA needs the producer warp and at least one more warp");
+    static_assert(kScoreBatch == 2, "a ring slot holds the two records a warp scores side by side");
     const int lane = c.lane;
+    uint32_t need_mask = 0, sz = 0, ns = 0, nb = 0;
     if (c.warp == 0) {
         ns = meta_ns(my_meta); nb = meta_nb(my_meta);
-        uint32_t sz = (D ? kDenseBytes : 0u) + (S ? 8u * pad2(ns) : 0u) + (B ? 8u * pad2(nb) : 0u);
-        if (!my_need) sz = 0;
-        uint32_t incl = sz;
-#pragma unroll
-        for (int o = 1; o < 32; o <<= 1) { const uint32_t t = __shfl_up_sync(kFull, incl, o); if (lane >= o) incl += t; }
-        pre_end = incl; pre_start = incl - sz;
-        remaining = __ballot_sync(kFull, my_need);
-    }
-    // Warp 0: the next records that fit one arena half go there, one bulk copy each, completing on that half's
-    // mbarrier; the half's batch mask (0 = nothing left) goes to its control word.
-    auto issue = [&](int h) {
-        uint32_t bm = 0;
-        if (remaining) {
-            const int first = __ffs(remaining) - 1;
-            const uint32_t b0 = __shfl_sync(kFull, pre_start, first);
-            const bool inb = ((remaining >> lane) & 1u) && (pre_end - b0 <= a.half_bytes);
-            bm = __ballot_sync(kFull, inb);
-            if (bm == 0) {  // a record larger than the staging area: the host sizes it so this cannot happen
-                if (lane == 0) atomicExch(a.ctl + 1, 2u);
-                remaining = 0;
-            } else {
-                const int hi = 31 - __clz(bm);
-                const uint32_t total = __shfl_sync(kFull, pre_end, hi) - b0;
-                uint64_t *bar = c.mbar + h;
-                if (lane == 0) {
-                    mbar_arrive_expect_tx(bar, total);
-                    c.c_bytes += total;
-                    c.c_eval += __popc(bm);
-                }
-                __syncwarp();
-                if (inb) {
-                    const uint32_t aoff = (uint32_t)h * a.half_bytes + (pre_start - b0);
-                    // entry k of the half's batch: arena offset and pool slot (lane) in one word, term counts in the other
-                    c.info[32 * h + __popc(bm & ((1u << lane) - 1u))] = make_uint2(aoff | ((uint32_t)lane << 24), ns | (nb << 16));
-                    const uint8_t *src = a.rec + meta_off16(my_meta) * 16ull;
-                    uint8_t *dst = c.arena + aoff;
-                    const uint32_t ps = 8u * pad2(ns), pb = 8u * pad2(nb);
-                    if (D && S && B) bulk_g2s(dst, src, kDenseBytes + ps + pb, bar);
-                    else if (D && S) bulk_g2s(dst, src, kDenseBytes + ps, bar);
-                    else if (D && B) { bulk_g2s(dst, src, kDenseBytes, bar); if (pb) bulk_g2s(dst + kDenseBytes, src + kDenseBytes + ps, pb, bar); }
-                    else if (D) bulk_g2s(dst, src, kDenseBytes, bar);
-                    else if (S && B) { if (ps + pb) bulk_g2s(dst, src + kDenseBytes, ps + pb, bar); }
-                    else if (S) { if (ps) bulk_g2s(dst, src + kDenseBytes, ps, bar); }
-                    else { if (pb) bulk_g2s(dst, src + kDenseBytes + ps, pb, bar); }
-                }
-                remaining &= ~bm;
-            }
-        }
-        if (lane == 0) c.ctl[CTL_BATCH + h] = bm;
-    };
-    if (c.warp == 0) {
-        issue(0);
-        if (a.halves == 2) issue(1);
-        else if (lane == 0) c.ctl[CTL_BATCH + 1] = 0;
+        sz = my_need ? (D ? kDenseBytes : 0u) + (S ? 8u * pad2(ns) : 0u) + (B ? 8u * pad2(nb) : 0u) : 0u;
+        need_mask = __ballot_sync(kFull, my_need);
+        const uint32_t cnt = __popc(need_mask);
+        if (lane == 0) { c.ctl[CTL_NPAIRS] = a.single ? cnt : (cnt + 1u) / 2u; c.ctl[CTL_NEXT] = 0; c.c_eval += cnt; }
     }
     __syncthreads();
-    // Batches are consumed in the order they were issued, halves alternating; while one half is scored the copies
-    // into the other are in flight.
-    for (int cur = 0;;) {
-        const uint32_t bm = c.ctl[CTL_BATCH + cur];
-        if (!bm) break;
-        // every warp waits for the half on its own (one polling lane), so a warp that comes late -- warp 0 after a
-        // refill -- holds nobody up; with two halves the copies have usually landed already
-        long long tw0 = 0;
-        if (c.tid == 0) tw0 = clock64();
-        if (lane == 0) mbar_wait_bounded(c.mbar + cur, (c.phase >> cur) & 1u, a.ctl + 1, 1u);
+    const uint32_t n_groups = c.ctl[CTL_NPAIRS];
+    const uint32_t g0 = c.gpair;
+    c.gpair = g0 + n_groups;   // the same in every thread
+    uint64_t *filled = c.mbar, *freed = c.mbar + kMaxSlots;
+    if (c.warp == 0) {
+        long long tw = 0;
+        if (c.tid == 0) tw = clock64();
+        // First wave: the groups that get a slot each without waiting -- whatever those slots held belongs to an
+        // earlier expansion, which ended with every group scored -- are armed and issued by all their lanes at once.
+        const uint32_t wave = min(n_groups, a.slots);
+        const uint32_t below = need_mask & ((1u << lane) - 1u), above = need_mask & ~((2u << lane) - 1u);
+        const uint32_t rank = __popc(below);
+        const uint32_t grp = a.single ? rank : rank >> 1, second = a.single ? 0u : (rank & 1u);
+        const int prev_lane = below ? 31 - __clz(below) : lane, next_lane = above ? __ffs(above) - 1 : lane;
+        const uint32_t sz_prev = __shfl_sync(kFull, sz, prev_lane), sz_next = __shfl_sync(kFull, sz, next_lane);
+        const bool in_wave = my_need && grp < wave;
+        const bool has_partner = !a.single && !second && above != 0u;
+        fence_proxy_async();   // the slots were last read by ordinary loads; the copies below write them through the async proxy
+        uint32_t w_slot = 0, w_aoff = 0;
+        if (in_wave) {
+            w_slot = (g0 + grp) % a.slots;
+            w_aoff = w_slot * a.slot_bytes + (second ? sz_prev : 0u);
+            c.info[2u * w_slot + second] = make_uint2(w_aoff | ((uint32_t)lane << 24), ns | (nb << 16));
+            if (!second && !has_partner) c.info[2u * w_slot + 1u] = make_uint2(0xFF000000u, 0u);   // no second record
+        }
         __syncwarp();
-        c.phase ^= 1u << cur;
-        long long tw1 = 0;
-        if (c.tid == 0) { tw1 = clock64(); c.t_wait += tw1 - tw0; }
-        const int nb_batch = __popc(bm);
-        // groups of records round-robin over the warps, warp 0 last: it is the one that issues the refills
-        for (int g = (c.warp + NT / 32 - 1) % (NT / 32); g * kScoreBatch < nb_batch; g += NT / 32) {
+        if (in_wave && !second) mbar_arrive_expect_tx(c.mbar + w_slot, sz + (has_partner ? sz_next : 0u));
+        const uint32_t wave_bytes = __reduce_add_sync(kFull, in_wave ? sz : 0u);
+        if (lane == 0) c.c_bytes += wave_bytes;
+        __syncwarp();
+        if (in_wave && sz) {
+            const uint8_t *src = a.rec + meta_off16(my_meta) * 16ull;
+            uint8_t *dst = c.arena + w_aoff;
+            uint64_t *bar = c.mbar + w_slot;
+            const uint32_t ps = 8u * pad2(ns), pb = 8u * pad2(nb);
+            if (D && S && B) bulk_g2s(dst, src, kDenseBytes + ps + pb, bar);
+            else if (D && S) bulk_g2s(dst, src, kDenseBytes + ps, bar);
+            else if (D && B) { bulk_g2s(dst, src, kDenseBytes, bar); if (pb) bulk_g2s(dst + kDenseBytes, src + kDenseBytes + ps, pb, bar); }
+            else if (D) bulk_g2s(dst, src, kDenseBytes, bar);
+            else if (S && B) { if (ps + pb) bulk_g2s(dst, src + kDenseBytes, ps + pb, bar); }
+            else if (S) { if (ps) bulk_g2s(dst, src + kDenseBytes, ps, bar); }
+            else { if (pb) bulk_g2s(dst, src + kDenseBytes + ps, pb, bar); }
+        }
+        // the rest goes slot by slot, as slots are released
+        uint32_t rem = need_mask & ~__ballot_sync(kFull, in_wave);
+        for (uint32_t p = wave; p < n_groups; ++p) {
+            const uint32_t g = g0 + p, slot = g % a.slots, round = g / a.slots;
+            const int l0 = __ffs(rem) - 1;
+            rem &= rem - 1u;
+            int l1 = -1;
+            if (!a.single && rem) { l1 = __ffs(rem) - 1; rem &= rem - 1u; }
+            const uint32_t sz0 = __shfl_sync(kFull, sz, l0);
+            const uint32_t sz1 = __shfl_sync(kFull, sz, l1 < 0 ? l0 : l1);
+            const uint32_t total = sz0 + (l1 < 0 ? 0u : sz1);
+            if (round != 0) {   // the slot's previous records have been scored
+                if (lane == 0) mbar_wait_bounded(freed + slot, (round - 1u) & 1u, a.ctl + 1, 1u);
+                __syncwarp();
+            }
+            fence_proxy_async();   // the slot was last read by ordinary loads; the copies below write it through the async proxy
+            const bool mine = lane == l0 || lane == l1;
+            const uint32_t aoff = slot * a.slot_bytes + (lane == l1 ? sz0 : 0u);
+            if (mine) c.info[2u * slot + (lane == l1 ? 1u : 0u)] = make_uint2(aoff | ((uint32_t)lane << 24), ns | (nb << 16));
+            if (l1 < 0 && lane == l0) c.info[2u * slot + 1u] = make_uint2(0xFF000000u, 0u);   // no second record
+            __syncwarp();
+            if (lane == 0) { mbar_arrive_expect_tx(filled + slot, total); c.c_bytes += total; }
+            __syncwarp();
+            if (mine && total) {
+                const uint8_t *src = a.rec + meta_off16(my_meta) * 16ull;
+                uint8_t *dst = c.arena + aoff;
+                uint64_t *bar = filled + slot;
+                const uint32_t ps = 8u * pad2(ns), pb = 8u * pad2(nb);
+                if (D && S && B) bulk_g2s(dst, src, kDenseBytes + ps + pb, bar);
+                else if (D && S) bulk_g2s(dst, src, kDenseBytes + ps, bar);
+                else if (D && B) { bulk_g2s(dst, src, kDenseBytes, bar); if (pb) bulk_g2s(dst + kDenseBytes, src + kDenseBytes + ps, pb, bar); }
+                else if (D) bulk_g2s(dst, src, kDenseBytes, bar);
+                else if (S && B) { if (ps + pb) bulk_g2s(dst, src + kDenseBytes, ps + pb, bar); }
+                else if (S) { if (ps) bulk_g2s(dst, src + kDenseBytes, ps, bar); }
+                else { if (pb) bulk_g2s(dst, src + kDenseBytes + ps, pb, bar); }
+            }
+        }
+        if (c.tid == 0) c.t_wait += clock64() - tw;
+    }
+    // Consumers.  Latency shape (many warps, an expansion mostly fits the ring): every warp takes the next group that
+    // nobody has taken yet -- warp 0 too, once it has issued the last copy.  Throughput shape: warp 0 stays the
+    // producer and the groups are dealt round robin to the other warps.
+    constexpr bool kDynamic = NT / 32 > 4;
+    constexpr uint32_t kConsumers = NT / 32 - 1;
+    if (kDynamic || c.warp != 0) {
+        for (uint32_t turn = 0;; ++turn) {
+            uint32_t p = ((uint32_t)c.warp - 1u) + turn * kConsumers;
+            if (kDynamic) {
+                if (lane == 0) p = atomicAdd(const_cast<uint32_t *>(&c.ctl[CTL_NEXT]), 1u);
+                p = __shfl_sync(kFull, p, 0);
+            }
+            if (p >= n_groups) break;
+            const uint32_t g = g0 + p, slot = g % a.slots, round = g / a.slots;
+            if (lane == 0) {
+                // the slot's previous round is over (a consumer that runs ahead must not take an earlier phase of the
+                // "filled" barrier for its own), then this round's records have landed
+                if (round != 0) mbar_wait_bounded(freed + slot, (round - 1u) & 1u, a.ctl + 1, 1u);
+                mbar_wait_bounded(filled + slot, round & 1u, a.ctl + 1, 1u);
+            }
+            __syncwarp();
             const uint8_t *rec[kScoreBatch];
             uint32_t rns[kScoreBatch], rnb[kScoreBatch], hit[kScoreBatch];
-            int slot[kScoreBatch];
+            int pslot[kScoreBatch];
             float d[kScoreBatch];
 #pragma unroll
             for (int r = 0; r < kScoreBatch; ++r) {
-                const int k = g * kScoreBatch + r;
-                const bool valid = k < nb_batch;
-                const uint2 inf = valid ? c.info[32 * cur + k] : make_uint2(0u, 0u);
-                slot[r] = valid ? (int)(inf.x >> 24) : -1;
-                rec[r] = c.arena + (inf.x & 0xFFFFFFu); rns[r] = inf.y & 0xFFFFu; rnb[r] = inf.y >> 16;
+                const uint2 inf = c.info[2u * slot + r];
+                const bool valid = (inf.x >> 24) < 32u;
+                pslot[r] = valid ? (int)(inf.x >> 24) : -1;
+                rec[r] = c.arena + (valid ? (inf.x & 0xFFFFFFu) : slot * a.slot_bytes);
+                rns[r] = valid ? (inf.y & 0xFFFFu) : 0u; rnb[r] = valid ? (inf.y >> 16) : 0u;
             }
             score_records<F, kScoreBatch>(rec, rns, rnb, qreg, c.qs, c.qb, lane, d, hit);
 #pragma unroll
             for (int r = 0; r < kScoreBatch; ++r) {
                 const uint32_t h = KW ? __ballot_sync(kFull, hit[r] != 0) : 0u;
-                if (lane == 0 && slot[r] >= 0) {
-                    c.pool_dis[base + slot[r]] = d[r];
-                    if (KW && h) c.pool_id[base + slot[r]] |= 0x40000000u;
+                if (lane == 0 && pslot[r] >= 0) {
+                    c.pool_dis[base + pslot[r]] = d[r];
+                    if (KW && h) c.pool_id[base + pslot[r]] |= 0x40000000u;
                 }
             }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(freed + slot);
         }
-        if (c.tid == 0) c.t_score += clock64() - tw1;
-        __syncthreads();                       // everyone is done with this half
-        if (c.warp == 0) issue(cur);           // refill it; the word is read again two turns from now
-        if (a.halves == 2) cur ^= 1;
-        else __syncthreads();                  // one staging area: the refill's word is read next
     }
     __syncthreads();
 }
@@ -466,7 +510,7 @@ __global__ void __launch_bounds__(NT, ctas_for_shape(NT)) search_kernel(const Se
     extern __shared__ __align__(128) uint8_t smem[];
     Ctx c;
     c.mbar = reinterpret_cast<uint64_t *>(smem);
-    c.ctl = reinterpret_cast<volatile uint32_t *>(smem + 16);
+    c.ctl = reinterpret_cast<volatile uint32_t *>(smem + 16 * kMaxSlots);
     c.pool_id = reinterpret_cast<uint32_t *>(smem + a.o_pool_id);
     c.pool_dis = reinterpret_cast<float *>(smem + a.o_pool_dis);
     c.pool_ent = reinterpret_cast<uint32_t *>(smem + a.o_pool_ent);
@@ -483,7 +527,7 @@ __global__ void __launch_bounds__(NT, ctas_for_shape(NT)) search_kernel(const Se
     c.kw_dis = reinterpret_cast<float *>(smem + a.o_kw + 4 * kKeywordRing);
     c.arena = smem + a.o_arena;
     c.tid = threadIdx.x; c.lane = c.tid & 31; c.warp = c.tid >> 5;
-    c.phase = 0; c.c_exp = 0; c.c_eval = 0; c.c_bytes = 0;
+    c.gpair = 0; c.c_exp = 0; c.c_eval = 0; c.c_bytes = 0;
     c.t_wait = c.t_score = c.t_ctl = c.t_sort = c.t_merge = c.t_mark = 0;
     const int tid = c.tid, lane = c.lane, warp = c.warp;
     const uint32_t topm = a.cands;
@@ -492,7 +536,7 @@ __global__ void __launch_bounds__(NT, ctas_for_shape(NT)) search_kernel(const Se
     uint32_t *stg_id = pool_id + topm;
     float *stg_dis = pool_dis + topm;
 
-    if (tid == 0) { mbar_init(c.mbar, 1); mbar_init(c.mbar + 1, 1); mbar_fence_init(); }
+    if (tid == 0) { for (int i = 0; i < 2 * kMaxSlots; ++i) mbar_init(c.mbar + i, 1); mbar_fence_init(); }
     __syncthreads();
 
     for (;;) {
@@ -939,7 +983,7 @@ static uint32_t log2u(uint32_t p) { uint32_t l = 0; while ((1u << l) < p) ++l; r
 
 static uint32_t layout(SearchArgs &a, const ap_index *ix, uint32_t warps, uint32_t cands, uint32_t flags, uint32_t max_qs, uint32_t max_qb) {
     (void)ix; (void)warps;
-    uint32_t o = 16 + 64;
+    uint32_t o = kHeaderBytes;
     auto take = [&](uint32_t bytes, uint32_t align) { o = (o + align - 1) / align * align; uint32_t r = o; o += bytes; return r; };
     a.o_pool_id = take(4 * (cands + 32), 16);
     a.o_pool_dis = take(4 * (cands + 32), 16);
@@ -948,7 +992,7 @@ static uint32_t layout(SearchArgs &a, const ap_index *ix, uint32_t warps, uint32
     const uint32_t vis = (cands + 32 + 3 * 32) * 2 <= 1024 ? 1024u : 2048u;
     a.vis_mask = vis - 1;
     a.o_vis = take(4 * vis, 16);
-    a.o_info = take(8 * 64, 16);   // batch entries of the two arena halves
+    a.o_info = take(8 * 2 * kMaxSlots, 16);   // two record entries per ring slot
     a.o_sq = take((flags & PF_SPARSE) ? 8 * std::max(1u, max_qs) : 0, 16);
     a.o_bq = take((flags & PF_BM25) ? 8 * std::max(1u, max_qb) : 0, 16);
     // collision-free tables for short query rows: kSlotsPerTerm slots per term (a multiplier is found within a few
@@ -981,9 +1025,14 @@ static int launch_shape(ap_index *ix, SearchArgs &a, uint32_t fixed, uint32_t wa
     }
     arena = std::min(arena, 512u * 1024u);  // the mbarrier transaction count is 20 bits wide
     a.arena_bytes = arena;
-    // two halves filled alternately when the largest record fits one of them, else one staging area
-    a.halves = (arena / 2) / 128 * 128 >= need_bytes ? 2u : 1u;
-    a.half_bytes = a.halves == 2 ? (arena / 2) / 128 * 128 : arena;
+    // ring slots: two records (the largest two fit) per slot when the arena holds at least two such slots, else one
+    // record per slot
+    {
+        const uint32_t pair = (2u * need_bytes + 127u) / 128u * 128u, one = (need_bytes + 127u) / 128u * 128u;
+        a.single = arena / pair >= 2u ? 0u : 1u;
+        a.slot_bytes = a.single ? one : pair;
+        a.slots = std::max(1u, std::min<uint32_t>((uint32_t)kMaxSlots, arena / a.slot_bytes));
+    }
     const size_t smem = fixed + arena;
     AP_CUDA(cudaFuncSetAttribute(search_kernel<F, NT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     int occ = 0;

@@ -771,7 +771,8 @@ def run_own(args):
                 "evaluations_per_query": round(st.evaluations / nq, 1)}
         roof["fetch_only_probe"] = {"gb_per_s": round(probe, 1), "frac_of_copy_peak": round(probe / hbm_peak, 4), "search_frac_of_probe": round(achieved / probe, 4),
                                     "what": "whole records of random documents brought into shared memory by bulk copies with the search kernel's CTA count and "
-                                            "shared-memory budget, nothing computed: the ceiling of this access pattern on this GPU"}
+                                            "shared-memory budget, every staging buffer refilled the moment it has landed and nothing computed: what the memory "
+                                            "system gives this access pattern when the whole arena is in flight (the search holds the records it is scoring)"}
         tr = traffic_ratio()
         if tr:
             roof["traffic"] = round(tr["ratio"] * algo)
