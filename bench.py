@@ -622,7 +622,7 @@ def bench_config(n, nq, cands):
 # DRAM bytes / algorithmic bytes of the search kernel: dram__bytes_read.sum + dram__bytes_write.sum of one launch over the
 # kernel's counted bytes in the 3-metric ncu capture summarised under profiles/ (the full-size launch is too large to
 # capture; both grow with the number of fused distances, the L2-served share shrinks with the corpus)
-TRAFFIC = {"ratio": 0.9616, "from": "ncu capture of the 500k-doc / 4k-query case (records pool 1.75 GB), profiles/search_kernel_traffic_500k_docs_4k_queries.md"}
+TRAFFIC = {"ratio": 0.9565, "from": "ncu capture of the 500k-doc / 4k-query case (records pool 1.75 GB), profiles/search_kernel_traffic_500k_docs_4k_queries.md"}
 
 
 def traffic_ratio():
