@@ -77,10 +77,13 @@ def _rows(c, k):
     return c.off[:k + 1], c.idx[:e], c.val[:e]
 
 
-def test_small_arena_batches_give_same_result(small, index):
-    """Forcing the record gathers through many small arena batches must not change anything."""
+@pytest.mark.parametrize("arena_bytes", [8192, 12288, 17920, 65536, 200000])
+def test_ring_shapes_give_same_result(small, index, arena_bytes):
+    """The staging arena is a ring of slots: one record per slot and a single slot (8 KB), one record per slot and two
+    slots (12 KB), two records per slot and two slots (17.5 KB), seven pair slots (64 KB), the cap of sixteen (200 KB).
+    None of it may change a result."""
     ids0, dis0, _ = index.search(small.QD, small.QS, small.QB, cands=128)
-    ids1, dis1, _ = index.search(small.QD, small.QS, small.QB, cands=128, arena_bytes=8192, ctas_per_sm=1)
+    ids1, dis1, _ = index.search(small.QD, small.QS, small.QB, cands=128, arena_bytes=arena_bytes, ctas_per_sm=1)
     assert np.array_equal(ids0, ids1) and np.array_equal(dis0.view(np.uint32), dis1.view(np.uint32))
 
 
