@@ -6,13 +6,13 @@
 // dense arithmetic (fp16 multiply-adds in the reference's lane/chunk association), so the pool contents match
 // it element for element.  What differs is how the work is mapped to the machine:
 //   * every document is one contiguous, 16-byte aligned record (dense halves + interleaved sparse and BM25
-//     pairs); an expansion fetches the records of all unvisited neighbours with cp.async.bulk copies into a
-//     shared-memory arena, all in flight at once, completing on one mbarrier;
+//     pairs); an expansion fetches the records of all unvisited neighbours with cp.async.bulk copies into a ring
+//     of shared-memory slots, each with a "filled" and a "free" mbarrier, fed by one warp and drained by the others;
 //   * graph rows carry each neighbour's record locator, so an expansion is two dependent memory round trips
 //     (row, records) instead of four (row, CSR offsets, CSR rows / dense row);
 //   * the query's sparse and BM25 rows are hashed into shared memory and probed with the document's terms;
 //   * selection, visited filtering, the 32-wide sort and the copy planning run in one warp on registers and
-//     shuffles; only scoring and the pool merge use the whole CTA.
+//     shuffles; scoring runs in the consumer warps and the pool merge in the whole CTA.
 #include <algorithm>
 #include <cstdio>
 
