@@ -877,6 +877,23 @@ def own_sections(args, line, ix, corpus, queries, hq, eff, out_ids, dev, hbm_pea
     line["latency_batch1"] = {"p50_ms": round(float(np.percentile(lat, 50)), 4), "p99_ms": round(float(np.percentile(lat, 99)), 4),
                               "kernel_p50_ms": round(float(np.median(kern[100:])), 4), "calls": int(lat.size), "what": "ap_search_host, host buffers in and out"}
     line["latency_batch1_ms"] = line["latency_batch1"]["kernel_p50_ms"]
+    # small batches through the same host call: up to 2 x SMs queries run in the latency shape of the kernel (8 warps per
+    # query), larger ones in the throughput shape
+    small = []
+    for bsz in (8, 64, 296, 297, 1000):
+        if bsz > nq:
+            break
+        s = (so[:bsz + 1].astype(np.uint32), si[:so[bsz]], sv[:so[bsz]])
+        b = (bo[:bsz + 1].astype(np.uint32), bi[:bo[bsz]], bv[:bo[bsz]])
+        ob = (np.empty((bsz, cands), dtype=np.uint32), np.empty((bsz, cands), dtype=np.float32))
+        lt, kn = [], []
+        for _ in range(40):
+            t0 = time.perf_counter()
+            _, _, s1 = ix.search(qd[:bsz], s, b, cands=cands, weights=eff, flags=apoe.SEARCH_RAW_WEIGHTS, out=ob)
+            lt.append((time.perf_counter() - t0) * 1e3)
+            kn.append(s1.kernel_ms)
+        small.append({"batch": bsz, "host_p50_ms": round(float(np.median(lt[10:])), 4), "kernel_p50_ms": round(float(np.median(kn[10:])), 4)})
+    line["latency_small_batches"] = small
     # recall over several builds (the default build keeps proposals in arrival order), and what the deterministic build costs
     ix.exact_release()
     rec, secs = [line["recall"]["at_10"]], [line["build"]["seconds"]]
