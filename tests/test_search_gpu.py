@@ -87,6 +87,30 @@ def test_ring_shapes_give_same_result(small, index, arena_bytes):
     assert np.array_equal(ids0, ids1) and np.array_equal(dis0.view(np.uint32), dis1.view(np.uint32))
 
 
+def test_both_kernel_shapes_give_the_same_pools(small, index):
+    """A batch this small runs in the latency shape of the kernel (8 warps per query, pairs of records dealt through a
+    shared counter); fixing the CTA count selects the throughput shape (3 warps, producer warp + round-robin
+    consumers).  Plain, keyword and knowledge-graph search: same pools bit for bit (the latency-shape results are
+    compared with the oracle by the tests above and below)."""
+    kws = synth.make_keywords(small.queries, seed=5)
+    qb_idx = small.QB.idx.copy()
+    for q, req in enumerate(kws):
+        row = qb_idx[small.QB.off[q]:small.QB.off[q + 1]]
+        row[np.isin(row, np.asarray(list(req), dtype=np.uint32))] |= np.uint32(0x80000000)
+    QBk = orc.CsrNp(small.QB.off, qb_idx, small.QB.val)
+    kg = synth.make_kg(small.n, small.nq, entities=5000, seed=9)
+    index.set_kg(kg.e2e_off, kg.e2e_idx, kg.e2d_off, kg.e2d_idx)
+    ent = (kg.qe_off.numpy().view(np.uint32), kg.qe_idx.numpy().view(np.uint32))
+    cases = {"plain": dict(qb=small.QB), "keyword": dict(qb=QBk, flags=apoe.SEARCH_KEYWORD), "kg": dict(qb=small.QB, kg_weight=40.0, ent=ent)}
+    for name, kw in cases.items():
+        qb = kw.pop("qb")
+        for cands in (32, 128, 512):
+            a_ids, a_dis, _ = index.search(small.QD, small.QS, qb, cands=cands, **kw)
+            b_ids, b_dis, _ = index.search(small.QD, small.QS, qb, cands=cands, ctas_per_sm=6, **kw)
+            assert np.array_equal(a_ids, b_ids), (name, cands)
+            assert np.array_equal(a_dis.view(np.uint32), b_dis.view(np.uint32)), (name, cands)
+
+
 def test_long_query_rows(small, index):
     """Query rows longer than 32 terms take the per-term lookup instead of the collision-free table; rows of mixed
     length in one batch take either, and both agree with the oracle bit for bit."""
